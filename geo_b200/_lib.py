@@ -1,0 +1,105 @@
+"""ctypes binding of ``libgeo_sc.so`` (the C ABI declared in ``include/geo_sc.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "lib", "libgeo_sc.so")
+
+MODE_1D, MODE_Z, MODE_YZ, MODE_FULL_OR = 0, 1, 2, 3
+MODES = {"1d_bin": MODE_1D, "z_bin": MODE_Z, "yz_bin": MODE_YZ, "full_or": MODE_FULL_OR}
+
+
+class GeoScError(RuntimeError):
+    def __init__(self, status, what, detail):
+        self.status = status
+        super().__init__(f"{what}: status {status} ({detail})")
+
+
+class ConvDesc(ctypes.Structure):
+    """Mirror of ``geo_sc_conv_desc``."""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "batch", "c_in", "h_in", "w_in", "pad_h", "pad_w", "c_out", "k_h", "k_w", "bit_length", "mode", "z_unit",
+        "total_width", "load_width", "load_wait_w", "load_wait_a")]
+
+
+_lib = None
+
+
+def lib():
+    """Load ``libgeo_sc.so`` (built by ``python -m geo_b200.build``) and declare its prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: run `python -m geo_b200.build` (there is no fallback path)")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, sz, i32 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    dp = ctypes.POINTER(ConvDesc)
+    szp = ctypes.POINTER(ctypes.c_size_t)
+    L.geo_sc_version.restype = i32
+    L.geo_sc_status_string.restype = ctypes.c_char_p
+    L.geo_sc_status_string.argtypes = [i32]
+    L.geo_sc_last_error.restype = ctypes.c_char_p
+    L.geo_sc_init.restype = i32
+    for n in ("geo_sc_conv2d_workspace_bytes", "geo_sc_weight_prep_bytes", "geo_sc_act_stream_bytes"):
+        getattr(L, n).argtypes = [dp, szp]
+        getattr(L, n).restype = i32
+    L.geo_sc_conv2d_forward.argtypes = [dp, vp, vp, vp, vp, sz, vp]
+    L.geo_sc_linear_forward.argtypes = [dp, vp, vp, vp, vp, sz, vp]
+    L.geo_sc_prepare_weights.argtypes = [dp, vp, vp, sz, vp]
+    L.geo_sc_generate_act_streams.argtypes = [dp, vp, vp, sz, vp]
+    L.geo_sc_accumulate.argtypes = [dp, vp, vp, vp, vp]
+    i32p = ctypes.POINTER(ctypes.c_int32)
+    L.geo_sc_group_geometry.argtypes = [dp, i32p, i32p, i32p, i32p]
+    L.geo_sc_host_stream.argtypes = [i32] * 7 + [vp]
+    L.geo_sc_measure_lop3_peak.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+    for n in ("geo_sc_conv2d_forward", "geo_sc_linear_forward", "geo_sc_prepare_weights",
+              "geo_sc_generate_act_streams", "geo_sc_accumulate", "geo_sc_group_geometry", "geo_sc_host_stream",
+              "geo_sc_measure_lop3_peak"):
+        getattr(L, n).restype = i32
+    _lib = L
+    return L
+
+
+def check(status, what):
+    if status != 0:
+        L = lib()
+        detail = L.geo_sc_last_error().decode() or L.geo_sc_status_string(status).decode()
+        raise GeoScError(status, what, detail)
+
+
+def make_desc(batch, c_in, h_in, w_in, c_out, k_h, k_w, bit_length, mode="1d_bin", pad_h=0, pad_w=0, z_unit=1 << 20,
+              total_width=7, load_width=8, load_wait_w=1, load_wait_a=None):
+    if load_wait_a is None:
+        load_wait_a = load_wait_w
+    m = MODES[mode] if isinstance(mode, str) else int(mode)
+    return ConvDesc(batch, c_in, h_in, w_in, pad_h, pad_w, c_out, k_h, k_w, bit_length, m, min(int(z_unit), 1 << 30),
+                    total_width, load_width, load_wait_w, load_wait_a)
+
+
+def size_query(fn_name, desc):
+    out = ctypes.c_size_t(0)
+    check(getattr(lib(), fn_name)(ctypes.byref(desc), ctypes.byref(out)), fn_name)
+    return out.value
+
+
+def group_geometry(desc):
+    g, k, nt, op = (ctypes.c_int32(0) for _ in range(4))
+    check(lib().geo_sc_group_geometry(ctypes.byref(desc), ctypes.byref(g), ctypes.byref(k), ctypes.byref(nt),
+                                      ctypes.byref(op)), "geo_sc_group_geometry")
+    return g.value, k.value, nt.value, op.value
+
+
+def host_stream(bit_length, value, seed_base, seed_index, total_width=7, load_width=8, load_wait=1):
+    """Packed stream words of one integer level, computed on the CPU with the kernels' own tables."""
+    P = (bit_length + 31) // 32
+    buf = (ctypes.c_uint32 * P)()
+    check(lib().geo_sc_host_stream(bit_length, value, seed_base, seed_index, total_width, load_width, load_wait,
+                                   ctypes.cast(buf, ctypes.c_void_p)), "geo_sc_host_stream")
+    return list(buf)

@@ -1,0 +1,228 @@
+// SC accumulation: out[m][o] = sum over packs p and groups g of
+//     popc( OR_k  A[m][g][k][p] & Wpos[g][k][o][p] ) - popc( OR_k A[m][g][k][p] & Wneg[g][k][o][p] )
+// where m runs over output positions (b, oy, ox), k over the OR-accumulated members of a
+// group and g over the binary-accumulated groups.  Replaces the reference's
+// stream_compute_add_direct_variable (sc_cuda_kernel.cu:694-1002) and matmul_outer (:43-86).
+//
+// Structure: an implicit-GEMM register-tiled kernel.  A CTA owns MT positions x NT output
+// channels; a thread owns 8 positions x 4 channels x 2 polarities = 64 OR-accumulators, so
+// every activation word loaded from shared memory feeds 8 LOP3 and every weight word 8.
+// The reduction is walked as a flat list of stages (pack, group, chunk of KC members); the
+// activation words of a stage are gathered from the packed stream image with 4-byte
+// cp.async (implicit im2col through the per-member offset table), the weight words with
+// 16-byte cp.async, through an NSTAGE-deep ring so that the copies of later stages overlap
+// the LOP3 work of the current one.  At the end of each group the 64 accumulators are
+// popcounted into 32 int32 sums that stay in registers until the final store.
+#include "sc_common.h"
+
+namespace geo {
+
+constexpr int KC = 16;      // members per stage
+constexpr int NSTAGE = 4;   // cp.async ring depth
+constexpr int TM = 8;       // positions per thread
+constexpr int TN = 4;       // output channels per thread
+
+struct AccParams {
+    const uint32_t *as;   // [B][P][C][Hp][Wp]
+    const uint32_t *ws;   // [P][G][K][Opad][2]
+    const int32_t *aoff;  // [G][K]
+    int32_t *out;         // [B][O][Ho][Wo]
+    int M, O, Opad, HoWo, Wo, Wp;
+    int P, G, K;
+    int img_words;        // P*C*Hp*Wp
+    int pack_words;       // C*Hp*Wp
+};
+
+__device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr));
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *gptr) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+template <int NT, int NTHREADS>
+struct Tile {
+    static constexpr int TY = NT / TN;          // thread rows over channels
+    static constexpr int TX = NTHREADS / TY;    // thread columns over positions
+    static constexpr int MT = TX * TM;          // positions per CTA
+    static constexpr int A_WORDS = KC * MT;
+    static constexpr int W_WORDS = KC * NT * 2;
+    static constexpr int STAGE_WORDS = A_WORDS + W_WORDS;
+    static constexpr size_t SMEM = (size_t)NSTAGE * STAGE_WORDS * 4;
+    static_assert(TX % 8 == 0 && TY % 4 == 0, "warps are 8 positions x 4 channel rows");
+};
+
+template <int NT, int NTHREADS>
+__global__ void __launch_bounds__(NTHREADS) accumulate_kernel(AccParams pr) {
+    using T = Tile<NT, NTHREADS>;
+    constexpr int MT = T::MT, TX = T::TX;
+    extern __shared__ __align__(16) uint32_t smem[];
+
+    const int t = threadIdx.x;
+    // A warp covers 8 thread columns x 4 thread rows, so that one 16-byte shared load of a
+    // warp touches 8 distinct activation chunks (128 B) or 4 distinct weight chunks.
+    const int lane = t & 31, warp = t >> 5;
+    constexpr int WX = TX / 8;
+    const int tx = (warp % WX) * 8 + (lane & 7);
+    const int ty = (warp / WX) * 4 + (lane >> 3);
+
+    const int m0 = blockIdx.x * MT;
+    const int o0 = blockIdx.y * NT;
+
+    // ---- gather assignment: this thread copies rows r = r0 + i*RSTEP of column(s) mcol ----
+    constexpr int MPT = MT > NTHREADS ? MT / NTHREADS : 1;     // columns per thread
+    constexpr int RSTEP = NTHREADS > MT ? NTHREADS / MT : 1;   // rows advanced per pass
+    const int r0 = NTHREADS > MT ? t / MT : 0;
+    int abase[MPT];
+#pragma unroll
+    for (int j = 0; j < MPT; j++) {
+        const int mcol = (t % MT) + j * NTHREADS;
+        int m = m0 + mcol;
+        if (m >= pr.M) m = pr.M - 1;
+        const int b = m / pr.HoWo, rem = m % pr.HoWo;
+        abase[j] = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+    }
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+
+    const int chunks = (pr.K + KC - 1) / KC;
+    const int nstages = pr.P * pr.G * chunks;
+
+    // stage cursor for the producer side
+    int ld_p = 0, ld_g = 0, ld_c = 0, ld_s = 0;
+    auto issue_stage = [&]() {
+        if (ld_s < nstages) {
+            const int buf = ld_s % NSTAGE;
+            const uint32_t a_s = smem_base + (uint32_t)buf * T::STAGE_WORDS * 4;
+            const uint32_t w_s = a_s + T::A_WORDS * 4;
+            const int k0 = ld_c * KC;
+            const int rows = min(KC, pr.K - k0);
+            const int32_t *aoff = pr.aoff + ld_g * pr.K + k0;
+            const uint32_t *asrc = pr.as + ld_p * pr.pack_words;
+#pragma unroll
+            for (int j = 0; j < MPT; j++) {
+                const int mcol = (t % MT) + j * NTHREADS;
+                for (int r = r0; r < rows; r += RSTEP)
+                    cp_async4(a_s + (uint32_t)(r * MT + mcol) * 4, asrc + abase[j] + __ldg(aoff + r));
+            }
+            // weights: `rows` rows of NT*2 words = NT/2 16-byte chunks each
+            constexpr int CPR = NT / 2;
+            const uint32_t *wsrc = pr.ws + ((size_t)(ld_p * pr.G + ld_g) * pr.K + k0) * pr.Opad * 2 + o0 * 2;
+            for (int i = t; i < rows * CPR; i += NTHREADS) {
+                const int r = i / CPR, ch = i % CPR;
+                cp_async16(w_s + (uint32_t)(r * NT * 2 + ch * 4) * 4, wsrc + (size_t)r * pr.Opad * 2 + ch * 4);
+            }
+            ld_s++;
+            if (++ld_c == chunks) {
+                ld_c = 0;
+                if (++ld_g == pr.G) { ld_g = 0; ld_p++; }
+            }
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int s = 0; s < NSTAGE - 1; s++) issue_stage();
+
+    uint32_t accp[TM][TN], accn[TM][TN];
+    int osum[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) { accp[i][j] = 0; accn[i][j] = 0; osum[i][j] = 0; }
+
+    int cs_c = 0;  // chunk index inside the current group (consumer side)
+    for (int s = 0; s < nstages; s++) {
+        cp_async_wait<NSTAGE - 2>();
+        __syncthreads();
+        issue_stage();  // refills the buffer that stage s-1 used; every thread is past it
+
+        const int buf = s % NSTAGE;
+        const uint32_t *a_s = smem + (size_t)buf * T::STAGE_WORDS;
+        const uint32_t *w_s = a_s + T::A_WORDS;
+        const int rows = min(KC, pr.K - cs_c * KC);
+        const uint4 *a4 = (const uint4 *)a_s + tx;
+        const uint4 *w4 = (const uint4 *)w_s + ty * 2;
+#pragma unroll 4
+        for (int r = 0; r < rows; r++) {
+            const uint4 a_lo = a4[r * (MT / 4)];
+            const uint4 a_hi = a4[r * (MT / 4) + MT / 8];
+            const uint4 w_a = w4[r * (NT / 2)];
+            const uint4 w_b = w4[r * (NT / 2) + 1];
+            const uint32_t a[TM] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+            const uint32_t wp[TN] = {w_a.x, w_a.z, w_b.x, w_b.z};
+            const uint32_t wn[TN] = {w_a.y, w_a.w, w_b.y, w_b.w};
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) {
+                    accp[i][j] |= a[i] & wp[j];
+                    accn[i][j] |= a[i] & wn[j];
+                }
+        }
+        if (++cs_c == chunks) {  // group finished: binary accumulation of its popcounts
+            cs_c = 0;
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) {
+                    osum[i][j] += __popc(accp[i][j]) - __popc(accn[i][j]);
+                    accp[i][j] = 0;
+                    accn[i][j] = 0;
+                }
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- store: thread positions are m0 + tx*4 + {0..3} and m0 + MT/2 + tx*4 + {0..3} ----
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const int m = m0 + (i < 4 ? tx * 4 + i : MT / 2 + tx * 4 + (i - 4));
+        if (m < pr.M) {
+            const int b = m / pr.HoWo, rem = m % pr.HoWo;
+#pragma unroll
+            for (int j = 0; j < TN; j++) {
+                const int o = o0 + ty * TN + j;
+                if (o < pr.O) pr.out[((size_t)b * pr.O + o) * pr.HoWo + rem] = osum[i][j];
+            }
+        }
+    }
+}
+
+template <int NT, int NTHREADS>
+static int launch_tile(const Geometry &g, const AccParams &pr, cudaStream_t s) {
+    using T = Tile<NT, NTHREADS>;
+    static bool configured[64] = {};
+    int dev = 0;
+    GEO_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_kernel<NT, NTHREADS>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
+        configured[dev] = true;
+    }
+    dim3 grid((unsigned)((g.M + T::MT - 1) / T::MT), (unsigned)(g.Opad / NT));
+    accumulate_kernel<NT, NTHREADS><<<grid, NTHREADS, T::SMEM, s>>>(pr);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t *wstream, const int32_t *aoff,
+                      int32_t *out, cudaStream_t s) {
+    AccParams pr;
+    pr.as = astream; pr.ws = wstream; pr.aoff = aoff; pr.out = out;
+    pr.M = (int)g.M; pr.O = g.O; pr.Opad = g.Opad; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
+    pr.P = g.P; pr.G = g.G; pr.K = g.K;
+    pr.pack_words = g.C * g.Hp * g.Wp;
+    pr.img_words = g.P * pr.pack_words;
+    switch (g.NT) {
+    case 16: return launch_tile<16, 128>(g, pr, s);
+    case 32: return launch_tile<32, 256>(g, pr, s);
+    default: return launch_tile<64, 256>(g, pr, s);
+    }
+}
+
+}  // namespace geo

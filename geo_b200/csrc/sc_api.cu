@@ -1,0 +1,250 @@
+// extern "C" entry points of libgeo_sc.so and the host-side geometry / planning logic.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "sc_common.h"
+
+namespace geo {
+
+static thread_local char g_err[512] = "";
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+static int lfsr_bits(int L) {
+    switch (L) {
+    case 8: return 3;
+    case 16: return 4;
+    case 32: return 5;
+    case 64: return 6;
+    case 128: return 7;
+    case 256: return 8;
+    default: return 0;
+    }
+}
+
+int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
+    if (!d || !g) return fail(GEO_SC_ERR_NULL, "descriptor is NULL");
+    memset(g, 0, sizeof(*g));
+    g->nbits = lfsr_bits(d->bit_length);
+    if (!g->nbits)
+        return fail(GEO_SC_ERR_BIT_LENGTH, "bit_length %d is not one of 8,16,32,64,128,256", d->bit_length);
+    if (d->mode < GEO_SC_MODE_1D || d->mode > GEO_SC_MODE_FULL_OR) return fail(GEO_SC_ERR_MODE, "mode %d", d->mode);
+    if (d->batch < 1 || d->c_in < 1 || d->h_in < 1 || d->w_in < 1 || d->c_out < 1 || d->k_h < 1 || d->k_w < 1 ||
+        d->pad_h < 0 || d->pad_w < 0)
+        return fail(GEO_SC_ERR_SHAPE, "non-positive dimension (batch %d c_in %d h %d w %d c_out %d k %dx%d pad %d,%d)",
+                    d->batch, d->c_in, d->h_in, d->w_in, d->c_out, d->k_h, d->k_w, d->pad_h, d->pad_w);
+    if (d->total_width < 0 || d->total_width > 15 || d->load_width < 1 || d->load_wait_w < 1 || d->load_wait_a < 1)
+        return fail(GEO_SC_ERR_LOADING, "total_width %d load_width %d load_wait %d/%d (need 0<=tw<=15, others >=1)",
+                    d->total_width, d->load_width, d->load_wait_w, d->load_wait_a);
+    g->B = d->batch; g->C = d->c_in; g->H = d->h_in; g->W = d->w_in;
+    g->pad_h = d->pad_h; g->pad_w = d->pad_w;
+    long long Hp = (long long)d->h_in + 2LL * d->pad_h, Wp = (long long)d->w_in + 2LL * d->pad_w;
+    if (Hp < d->k_h || Wp < d->k_w)
+        return fail(GEO_SC_ERR_SHAPE, "filter %dx%d larger than padded image %lldx%lld", d->k_h, d->k_w, Hp, Wp);
+    if (Hp > (1 << 20) || Wp > (1 << 20)) return fail(GEO_SC_ERR_TOO_LARGE, "padded image %lldx%lld", Hp, Wp);
+    g->Hp = (int)Hp; g->Wp = (int)Wp;
+    g->O = d->c_out; g->K2 = d->k_h; g->K3 = d->k_w;
+    g->Ho = g->Hp - g->K2 + 1; g->Wo = g->Wp - g->K3 + 1;
+    g->L = d->bit_length; g->P = (g->L + 31) / 32;
+    g->mode = d->mode;
+    g->tw = d->total_width; g->lu = d->load_width; g->lw_w = d->load_wait_w; g->lw_a = d->load_wait_a;
+    g->z = 1;
+    long long G, K;
+    switch (g->mode) {
+    case GEO_SC_MODE_1D: G = g->K3; K = (long long)g->C * g->K2; break;
+    case GEO_SC_MODE_Z: G = g->C; K = (long long)g->K2 * g->K3; break;
+    case GEO_SC_MODE_YZ:
+        if (d->z_unit < 1) return fail(GEO_SC_ERR_SHAPE, "z_unit %d < 1", d->z_unit);
+        g->z = d->z_unit < g->C ? d->z_unit : g->C;
+        G = (long long)((g->C + g->z - 1) / g->z) * g->K3;
+        K = (long long)g->z * g->K2;
+        break;
+    default: G = 1; K = (long long)g->C * g->K2 * g->K3; break;
+    }
+    g->NT = g->O <= 16 ? 16 : (g->O <= 32 ? 32 : 64);
+    g->Opad = (g->O + g->NT - 1) / g->NT * g->NT;
+    const long long lim = (1LL << 31) - 1;
+    long long M = (long long)g->B * g->Ho * g->Wo;
+    long long aw = (long long)g->B * g->P * g->C * g->Hp * g->Wp;
+    long long ww = (long long)g->P * G * K * g->Opad * 2;
+    long long ow = M * g->O;
+    long long iw = (long long)g->B * g->C * g->H * g->W;
+    if (G > lim || K > lim || M > lim || aw > lim || ww > lim || ow > lim || iw > lim || G * K > lim)
+        return fail(GEO_SC_ERR_TOO_LARGE,
+                    "an index exceeds 31 bits (positions %lld, act words %lld, weight words %lld, outputs %lld)", M, aw,
+                    ww, ow);
+    g->G = (int)G; g->K = (int)K; g->M = M;
+    g->act_stream_words = (size_t)aw;
+    g->w_stream_words = (size_t)ww;
+    g->aoff_entries = (size_t)(G * K);
+    return GEO_SC_OK;
+}
+
+void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan) {
+    memset(plan, 0, sizeof(*plan));
+    int level_of_shift[32];
+    for (int i = 0; i < 32; i++) level_of_shift[i] = -1;
+    for (int t = 1; t <= L; t++) {
+        long long cw = ((long long)(t / lw) + 1) * lu - 1;
+        if (cw > tw) cw = tw;
+        int sh = tw - (int)cw;
+        if (level_of_shift[sh] < 0) {
+            level_of_shift[sh] = plan->nlev;
+            plan->shift[plan->nlev++] = sh;
+        }
+        int lev = level_of_shift[sh];
+        int p, bit;
+        if (L >= 32) { p = (t - 1) / 32; bit = 31 - (t - 1) % 32; }
+        else { p = 0; bit = L - t; }
+        plan->mask[p][lev] |= 1u << bit;
+    }
+}
+
+static size_t wprep_bytes(const Geometry &g) {
+    return align_up(g.w_stream_words * 4, 256) + align_up(g.aoff_entries * 4, 256);
+}
+static size_t astream_bytes(const Geometry &g) { return align_up(g.act_stream_words * 4, 256); }
+
+static int check_buffer(const void *p, size_t have, size_t need, const char *what) {
+    if (!p) return fail(GEO_SC_ERR_NULL, "%s is NULL", what);
+    if (((uintptr_t)p & 255) != 0) return fail(GEO_SC_ERR_WORKSPACE, "%s is not 256-byte aligned", what);
+    if (have < need) return fail(GEO_SC_ERR_WORKSPACE, "%s holds %zu bytes, %zu needed", what, have, need);
+    return GEO_SC_OK;
+}
+
+}  // namespace geo
+
+using namespace geo;
+
+extern "C" {
+
+int geo_sc_version(void) { return GEO_SC_VERSION; }
+
+const char *geo_sc_status_string(int status) {
+    switch (status) {
+    case GEO_SC_OK: return "ok";
+    case GEO_SC_ERR_NULL: return "null pointer";
+    case GEO_SC_ERR_BIT_LENGTH: return "unsupported bit_length";
+    case GEO_SC_ERR_SHAPE: return "bad shape";
+    case GEO_SC_ERR_MODE: return "unknown mode";
+    case GEO_SC_ERR_LOADING: return "bad progressive-loading parameters";
+    case GEO_SC_ERR_TOO_LARGE: return "problem too large for 31-bit indexing";
+    case GEO_SC_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case GEO_SC_ERR_CUDA: return "CUDA runtime error";
+    case GEO_SC_ERR_UNSUPPORTED: return "unsupported";
+    default: return "unknown status";
+    }
+}
+
+const char *geo_sc_last_error(void) { return g_err; }
+
+int geo_sc_init(void) { return ensure_tables(); }
+
+int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *cout_tile,
+                          int32_t *cout_padded) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (groups) *groups = g.G;
+    if (members) *members = g.K;
+    if (cout_tile) *cout_tile = g.NT;
+    if (cout_padded) *cout_padded = g.Opad;
+    return GEO_SC_OK;
+}
+
+int geo_sc_weight_prep_bytes(const geo_sc_conv_desc *desc, size_t *bytes) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!bytes) return fail(GEO_SC_ERR_NULL, "bytes is NULL");
+    *bytes = wprep_bytes(g);
+    return GEO_SC_OK;
+}
+
+int geo_sc_act_stream_bytes(const geo_sc_conv_desc *desc, size_t *bytes) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!bytes) return fail(GEO_SC_ERR_NULL, "bytes is NULL");
+    *bytes = astream_bytes(g);
+    return GEO_SC_OK;
+}
+
+int geo_sc_conv2d_workspace_bytes(const geo_sc_conv_desc *desc, size_t *bytes) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!bytes) return fail(GEO_SC_ERR_NULL, "bytes is NULL");
+    *bytes = astream_bytes(g) + wprep_bytes(g);
+    return GEO_SC_OK;
+}
+
+int geo_sc_prepare_weights(const geo_sc_conv_desc *desc, const float *weight, void *wprep, size_t bytes, void *stream) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!weight) return fail(GEO_SC_ERR_NULL, "weight is NULL");
+    if ((rc = check_buffer(wprep, bytes, wprep_bytes(g), "prepared-weight buffer"))) return rc;
+    uint32_t *ws = (uint32_t *)wprep;
+    int32_t *aoff = (int32_t *)((char *)wprep + align_up(g.w_stream_words * 4, 256));
+    return launch_prepare_weights(g, weight, ws, aoff, (cudaStream_t)stream);
+}
+
+int geo_sc_generate_act_streams(const geo_sc_conv_desc *desc, const float *act, void *astream, size_t bytes,
+                                void *stream) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!act) return fail(GEO_SC_ERR_NULL, "act is NULL");
+    if ((rc = check_buffer(astream, bytes, astream_bytes(g), "activation-stream buffer"))) return rc;
+    return launch_act_streams(g, act, (uint32_t *)astream, (cudaStream_t)stream);
+}
+
+int geo_sc_accumulate(const geo_sc_conv_desc *desc, const void *astream, const void *wprep, int32_t *out,
+                      void *stream) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!astream || !wprep || !out) return fail(GEO_SC_ERR_NULL, "astream, wprep or out is NULL");
+    if (((uintptr_t)astream & 15) || ((uintptr_t)wprep & 255))
+        return fail(GEO_SC_ERR_WORKSPACE, "stream buffers are misaligned");
+    const uint32_t *ws = (const uint32_t *)wprep;
+    const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
+    return launch_accumulate(g, (const uint32_t *)astream, ws, aoff, out, (cudaStream_t)stream);
+}
+
+int geo_sc_conv2d_forward(const geo_sc_conv_desc *desc, const float *act, const float *weight, int32_t *out,
+                          void *workspace, size_t workspace_bytes, void *stream) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!act || !weight || !out) return fail(GEO_SC_ERR_NULL, "act, weight or out is NULL");
+    size_t ab = astream_bytes(g), wb = wprep_bytes(g);
+    if ((rc = check_buffer(workspace, workspace_bytes, ab + wb, "workspace"))) return rc;
+    uint32_t *as = (uint32_t *)workspace;
+    uint32_t *ws = (uint32_t *)((char *)workspace + ab);
+    int32_t *aoff = (int32_t *)((char *)ws + align_up(g.w_stream_words * 4, 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if ((rc = launch_prepare_weights(g, weight, ws, aoff, s))) return rc;
+    if ((rc = launch_act_streams(g, act, as, s))) return rc;
+    return launch_accumulate(g, as, ws, aoff, out, s);
+}
+
+int geo_sc_linear_forward(const geo_sc_conv_desc *desc, const float *act, const float *weight, int32_t *out,
+                          void *workspace, size_t workspace_bytes, void *stream) {
+    if (!desc) return fail(GEO_SC_ERR_NULL, "descriptor is NULL");
+    if (desc->h_in != 1 || desc->w_in != 1 || desc->k_h != 1 || desc->k_w != 1 || desc->pad_h || desc->pad_w)
+        return fail(GEO_SC_ERR_SHAPE, "linear layer needs h_in=w_in=k_h=k_w=1 and no padding");
+    geo_sc_conv_desc d = *desc;
+    d.mode = GEO_SC_MODE_YZ;
+    return geo_sc_conv2d_forward(&d, act, weight, out, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"

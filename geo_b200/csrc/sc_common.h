@@ -1,0 +1,67 @@
+// Internal declarations shared by the translation units of libgeo_sc.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/geo_sc.h"
+
+namespace geo {
+
+// Records a thread-local error detail and returns `status`.
+int fail(int status, const char *fmt, ...);
+
+// Everything the kernels need to know about one convolution, derived once on the host.
+struct Geometry {
+    int B, C, H, W;          // activation dims, unpadded
+    int pad_h, pad_w;
+    int Hp, Wp;              // padded image
+    int O, K2, K3;           // filter dims (K2 = dim 2, K3 = dim 3)
+    int Ho, Wo;
+    int L, P;                // stream length, 32-bit packs per stream
+    int nbits;               // LFSR width
+    int mode;
+    int z;                   // OR-group width in channels (yz mode)
+    int G, K;                // binary-accumulated groups, OR-accumulated members per group
+    int NT;                  // c_out tile of the accumulate kernel
+    int Opad;                // c_out rounded up to NT
+    int tw, lu, lw_w, lw_a;  // progressive loading
+    long long M;             // output positions B*Ho*Wo
+    size_t act_stream_words; // B*P*C*Hp*Wp
+    size_t w_stream_words;   // P*G*K*Opad*2
+    size_t aoff_entries;     // G*K
+};
+
+int make_geometry(const geo_sc_conv_desc *d, Geometry *g);
+
+// Progressive-loading plan: the distinct right-shifts applied to a value and, per pack,
+// the stream bits (MSB-first masks) during which each shift is in force.
+constexpr int kMaxLevels = 16;
+constexpr int kMaxPacks = 8;
+struct LoadPlan {
+    int nlev;
+    int shift[kMaxLevels];
+    uint32_t mask[kMaxPacks][kMaxLevels];
+};
+void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan);
+
+// Stream generation (sc_streams.cu)
+int ensure_tables();
+int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream, int32_t *aoff, cudaStream_t s);
+int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, cudaStream_t s);
+
+// Accumulation (sc_accumulate.cu)
+int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t *wstream, const int32_t *aoff,
+                      int32_t *out, cudaStream_t s);
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+#define GEO_CUDA_CHECK(expr)                                                                       \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return ::geo::fail(GEO_SC_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));   \
+    } while (0)
+
+}  // namespace geo

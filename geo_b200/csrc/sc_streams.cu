@@ -1,0 +1,288 @@
+// LFSR bit-stream generation for weights and activations.
+//
+// The reference runs the LFSR bit by bit for every element (sc_cuda_kernel.cu:151-168,
+// 678-690).  All six LFSRs are maximal length, so every seed is a phase into one state
+// sequence s_0=1, s_1, ... of period L-1, and the stream of a value v seeded at phase f is
+// the L-bit window starting at bit f+1 of the periodic pattern [v > s_j].  The patterns for
+// all v are precomputed once per device ("pattern table", doubled so that a window never
+// wraps) and a stream word becomes one funnel shift of two table words.  Progressive
+// loading (sc_cuda_kernel.cu:156-160) only changes which truncation of v is visible
+// during which bits; it is applied by merging the windows of the truncated values under
+// constant bit masks.
+#include <mutex>
+#include <vector>
+
+#include "sc_common.h"
+
+namespace geo {
+
+// ---- pattern tables ---------------------------------------------------------------------
+// For stream length L: L rows (one per value) of RW(L) = max(2, 2*L/32) words holding two
+// periods of [v > s_j], bit j at word j/32, bit 31-(j%32); and q0[seed] = (phase(seed)+1) mod (L-1).
+constexpr int kNumL = 6;
+__host__ __device__ constexpr int row_words(int L) { return L >= 32 ? 2 * (L / 32) : 2; }
+constexpr int kTableWords = 8 * 2 + 16 * 2 + 32 * 2 + 64 * 4 + 128 * 8 + 256 * 16;
+
+__device__ uint32_t g_pattern[kTableWords];
+__device__ uint16_t g_q0[kNumL][256];
+
+__host__ __device__ inline int l_index(int L) {  // 8->0 ... 256->5
+    return L == 8 ? 0 : L == 16 ? 1 : L == 32 ? 2 : L == 64 ? 3 : L == 128 ? 4 : 5;
+}
+__host__ __device__ inline int table_offset(int L) {
+    int off = 0;
+    for (int l = 8; l < L; l *= 2) off += l * row_words(l);
+    return off;
+}
+
+// One LFSR step (sc_cuda_kernel.cu:18-40 written with shifts): feedback = xor of the tap
+// bits, shifted in at the bottom, top bit dropped.
+static int lfsr_step_host(int v, int n) {
+    static const int taps[9][4] = {{-1}, {-1}, {-1}, {2, 1, -1, -1}, {3, 2, -1, -1}, {4, 2, -1, -1},
+                                   {5, 4, -1, -1}, {6, 5, -1, -1}, {7, 5, 4, 3}};
+    int fb = 0;
+    for (int i = 0; i < 4; i++)
+        if (taps[n][i] >= 0) fb ^= (v >> taps[n][i]) & 1;
+    return fb + 2 * (v & ((1 << (n - 1)) - 1));
+}
+
+static std::mutex g_table_mutex;
+static bool g_table_ready[64] = {};
+static std::vector<uint32_t> g_host_pattern;
+static std::vector<uint16_t> g_host_q0;
+
+// Builds the host copy of the tables (once per process).
+static void build_host_tables() {
+    if (!g_host_pattern.empty()) return;
+    std::vector<uint32_t> pat(kTableWords, 0u);
+    std::vector<uint16_t> q0(kNumL * 256, 0);
+    for (int n = 3; n <= 8; n++) {
+        const int L = 1 << n, period = L - 1, RW = row_words(L);
+        std::vector<int> seq(period);
+        int s = 1;
+        for (int j = 0; j < period; j++) {
+            seq[j] = s;
+            q0[l_index(L) * 256 + s] = (uint16_t)((j + 1) % period);
+            s = lfsr_step_host(s, n);
+        }
+        uint32_t *tab = pat.data() + table_offset(L);
+        for (int v = 0; v < L; v++)
+            for (int j = 0; j < 2 * period; j++)
+                if (v > seq[j % period]) tab[v * RW + (j >> 5)] |= 1u << (31 - (j & 31));
+    }
+    g_host_q0.swap(q0);
+    g_host_pattern.swap(pat);
+}
+
+int ensure_tables() {
+    int dev = 0;
+    GEO_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(GEO_SC_ERR_UNSUPPORTED, "device index %d", dev);
+    std::lock_guard<std::mutex> lock(g_table_mutex);
+    if (g_table_ready[dev]) return GEO_SC_OK;
+    build_host_tables();
+    GEO_CUDA_CHECK(cudaMemcpyToSymbol(g_pattern, g_host_pattern.data(), g_host_pattern.size() * sizeof(uint32_t)));
+    GEO_CUDA_CHECK(cudaMemcpyToSymbol(g_q0, g_host_q0.data(), g_host_q0.size() * sizeof(uint16_t)));
+    g_table_ready[dev] = true;
+    return GEO_SC_OK;
+}
+
+// ---- device helpers -----------------------------------------------------------------------
+struct GenParams {
+    int B, C, H, W, pad_h, pad_w, Hp, Wp;
+    int O, K2, K3;
+    int L, P, mode, z, G, K, Opad;
+    int RW;
+};
+
+static GenParams gen_params(const Geometry &g) {
+    GenParams p;
+    p.B = g.B; p.C = g.C; p.H = g.H; p.W = g.W; p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.Hp = g.Hp; p.Wp = g.Wp;
+    p.O = g.O; p.K2 = g.K2; p.K3 = g.K3;
+    p.L = g.L; p.P = g.P; p.mode = g.mode; p.z = g.z; p.G = g.G; p.K = g.K; p.Opad = g.Opad;
+    p.RW = row_words(g.L);
+    return p;
+}
+
+// Copies the pattern table and phase table for stream length L into shared memory.
+__device__ __forceinline__ void load_tables(uint32_t *s_pat, uint16_t *s_q0, int L, int RW) {
+    const uint32_t *src = g_pattern + table_offset(L);
+    for (int i = threadIdx.x; i < L * RW; i += blockDim.x) s_pat[i] = src[i];
+    const uint16_t *q = g_q0[l_index(L)];
+    for (int i = threadIdx.x; i < L; i += blockDim.x) s_q0[i] = q[i];
+    __syncthreads();
+}
+
+__host__ __device__ __forceinline__ uint32_t funnel_left(uint32_t lo, uint32_t hi, int sh) {
+#ifdef __CUDA_ARCH__
+    return __funnelshift_l(lo, hi, sh);
+#else
+    return sh ? (hi << sh) | (lo >> (32 - sh)) : hi;
+#endif
+}
+
+// Stream word `p` of value V whose generator starts at window offset q0.
+__host__ __device__ __forceinline__ uint32_t stream_word(const uint32_t *s_pat, int RW, int L, int V, int q0, int p,
+                                                         const LoadPlan &plan) {
+    uint32_t word = 0;
+    const int q = q0 + 32 * p;
+    const int i = q >> 5, sh = q & 31;
+    for (int j = 0; j < plan.nlev; j++) {
+        const uint32_t m = plan.mask[p][j];
+        if (m) {
+            const int vj = (V >> plan.shift[j]) << plan.shift[j];
+            const uint32_t *row = s_pat + vj * RW;
+            uint32_t w32 = funnel_left(row[i + 1], row[i], sh);
+            if (L < 32) w32 >>= (32 - L);
+            word |= w32 & m;
+        }
+    }
+    return word;
+}
+
+// ---- weight streams -----------------------------------------------------------------------
+// One thread per (group, member, padded c_out); writes the positive and negative stream words
+// of every pack as one 8-byte store, layout [pack][group][member][c_out_padded][2], and the
+// activation offset of each (group, member).
+__global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, LoadPlan plan, const float *__restrict__ w,
+                                                              uint32_t *__restrict__ ws, int32_t *__restrict__ aoff) {
+    extern __shared__ uint32_t smem[];
+    uint32_t *s_pat = smem;
+    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RW);
+    load_tables(s_pat, s_q0, gp.L, gp.RW);
+
+    const long long total = (long long)gp.G * gp.K * gp.Opad;
+    const float fL = (float)gp.L;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int o = (int)(idx % gp.Opad);
+        const int gk = (int)(idx / gp.Opad);
+        const int k = gk % gp.K, g = gk / gp.K;
+        int c, ky, kx, sidx;
+        switch (gp.mode) {
+        case GEO_SC_MODE_1D: kx = g; c = k / gp.K2; ky = k % gp.K2; sidx = k; break;
+        case GEO_SC_MODE_Z: c = g; ky = k / gp.K3; kx = k % gp.K3; sidx = k; break;
+        case GEO_SC_MODE_YZ: {
+            const int zp = g / gp.K3;
+            kx = g % gp.K3;
+            c = zp * gp.z + k / gp.K2;
+            ky = k % gp.K2;
+            sidx = k;
+            break;
+        }
+        default: c = k / (gp.K2 * gp.K3); ky = (k / gp.K3) % gp.K2; kx = k % gp.K3; sidx = k; break;
+        }
+        const bool valid = c < gp.C;
+        if (o == 0) aoff[gk] = valid ? (c * gp.Hp + ky) * gp.Wp + kx : 0;
+        int Vp = 0, Vn = 0;
+        if (valid && o < gp.O) {
+            const float x = w[(((size_t)o * gp.C + c) * gp.K2 + ky) * gp.K3 + kx] * fL;
+            Vp = (int)ceilf(fminf(fmaxf(x, 0.0f), fL - 1.0f));
+            Vn = (int)ceilf(-fminf(fmaxf(x, 1.0f - fL), 0.0f));
+        }
+        const int qp = s_q0[(67 + sidx) % (gp.L - 1) + 1];
+        const int qn = s_q0[(37 + sidx) % (gp.L - 1) + 1];
+        for (int p = 0; p < gp.P; p++) {
+            uint2 v;
+            v.x = Vp ? stream_word(s_pat, gp.RW, gp.L, Vp, qp, p, plan) : 0u;
+            v.y = Vn ? stream_word(s_pat, gp.RW, gp.L, Vn, qn, p, plan) : 0u;
+            *(uint2 *)(ws + ((((size_t)p * gp.G + g) * gp.K + k) * gp.Opad + o) * 2) = v;
+        }
+    }
+}
+
+// ---- activation streams ---------------------------------------------------------------------
+// One thread per element of the padded image; fuses zero padding and the float -> level
+// quantisation (sc_cuda.cpp:50-51).  Layout [batch][pack][c][Hp][Wp].
+__global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan plan, const float *__restrict__ act,
+                                                          uint32_t *__restrict__ as) {
+    extern __shared__ uint32_t smem[];
+    uint32_t *s_pat = smem;
+    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RW);
+    load_tables(s_pat, s_q0, gp.L, gp.RW);
+
+    const int plane = gp.Hp * gp.Wp;
+    const long long total = (long long)gp.B * gp.C * plane;
+    const float fL = (float)gp.L;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int yx = (int)(idx % plane);
+        const int bc = (int)(idx / plane);
+        const int c = bc % gp.C, b = bc / gp.C;
+        const int y = yx / gp.Wp, x = yx % gp.Wp;
+        const int yi = y - gp.pad_h, xi = x - gp.pad_w;
+        int V = 0;
+        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W) {
+            const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
+            V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
+        }
+        const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
+        const int sidx = (cc * gp.Hp + y) * gp.Wp + x;
+        const int q0 = s_q0[sidx % (gp.L - 1) + 1];
+        uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
+        for (int p = 0; p < gp.P; p++)
+            dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RW, gp.L, V, q0, p, plan) : 0u;
+    }
+}
+
+static int grid_for(long long total) {
+    long long blocks = (total + 255) / 256;
+    const long long cap = 148LL * 16;
+    return (int)(blocks < cap ? blocks : cap);
+}
+
+int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream, int32_t *aoff, cudaStream_t s) {
+    int rc = ensure_tables();
+    if (rc) return rc;
+    GenParams gp = gen_params(g);
+    LoadPlan plan;
+    make_load_plan(g.L, g.tw, g.lu, g.lw_w, &plan);
+    const size_t smem = (size_t)g.L * gp.RW * 4 + (size_t)g.L * 2;
+    const long long total = (long long)g.G * g.K * g.Opad;
+    prepare_weights_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, w, wstream, aoff);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, cudaStream_t s) {
+    int rc = ensure_tables();
+    if (rc) return rc;
+    GenParams gp = gen_params(g);
+    LoadPlan plan;
+    make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
+    const size_t smem = (size_t)g.L * gp.RW * 4 + (size_t)g.L * 2;
+    const long long total = (long long)g.B * g.C * g.Hp * g.Wp;
+    act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+}  // namespace geo
+
+// Host mirror of the device stream generator (same tables, same plan, same word function):
+// the packed stream of integer level `value` for generator index `seed_index` and seed base
+// `seed_base` (67 / 37 for positive / negative weights, 0 for activations).
+extern "C" int geo_sc_host_stream(int bit_length, int value, int seed_base, int seed_index, int total_width,
+                                  int load_width, int load_wait, uint32_t *words) {
+    using namespace geo;
+    if (!words) return fail(GEO_SC_ERR_NULL, "words is NULL");
+    geo_sc_conv_desc d = {1, 1, 1, 1, 0, 0, 1, 1, 1, bit_length, GEO_SC_MODE_1D, 1, total_width, load_width,
+                          load_wait, load_wait};
+    Geometry g;
+    int rc = make_geometry(&d, &g);
+    if (rc) return rc;
+    if (value < 0 || value >= bit_length) return fail(GEO_SC_ERR_SHAPE, "value %d outside [0,%d)", value, bit_length);
+    if (seed_base < 0 || seed_index < 0) return fail(GEO_SC_ERR_SHAPE, "negative seed");
+    {
+        std::lock_guard<std::mutex> lock(g_table_mutex);
+        build_host_tables();
+    }
+    LoadPlan plan;
+    make_load_plan(g.L, g.tw, g.lu, load_wait, &plan);
+    const int RW = row_words(g.L);
+    const uint32_t *pat = g_host_pattern.data() + table_offset(g.L);
+    const int seed = (int)(((long long)seed_base + seed_index) % (g.L - 1)) + 1;
+    const int q0 = g_host_q0[l_index(g.L) * 256 + seed];
+    for (int p = 0; p < g.P; p++) words[p] = value ? stream_word(pat, RW, g.L, value, q0, p, plan) : 0u;
+    return GEO_SC_OK;
+}

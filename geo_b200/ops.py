@@ -1,0 +1,147 @@
+"""Torch-tensor front end of the C ABI (``include/geo_sc.h``), through ctypes.
+
+Every function takes CUDA tensors, runs on torch's current stream and raises if the native
+library is missing or reports an error.  There is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import MODES, ConvDesc, check, make_desc  # noqa: F401
+
+
+def _stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("geo_b200 SC kernels run on CUDA tensors only (there is no CPU path)")
+
+
+def desc_for(act, weight, bit_length, mode="1d_bin", padding=(0, 0), **kw):
+    """Descriptor for ``act`` [B,C,H,W] and ``weight`` [O,C,K2,K3]; ``padding`` = (pad_h, pad_w)."""
+    B, C, H, W = act.shape
+    O, C2, K2, K3 = weight.shape
+    if C != C2:
+        raise ValueError(f"channel mismatch: input has {C}, weight has {C2}")
+    return make_desc(B, C, H, W, O, K2, K3, bit_length, mode, pad_h=int(padding[0]), pad_w=int(padding[1]), **kw)
+
+
+def out_shape(desc):
+    return (desc.batch, desc.c_out, desc.h_in + 2 * desc.pad_h - desc.k_h + 1,
+            desc.w_in + 2 * desc.pad_w - desc.k_w + 1)
+
+
+def sc_conv2d(act, weight, bit_length, mode="1d_bin", padding=(0, 0), workspace=None, out=None, **kw):
+    """SC conv2d forward -> int32 [B,O,Ho,Wo] (positive minus negative bit counts)."""
+    _require_cuda(act, weight)
+    a = act.detach().to(torch.float32).contiguous()
+    w = weight.detach().to(torch.float32).contiguous()
+    d = desc_for(a, w, bit_length, mode, padding, **kw)
+    nbytes = _lib.size_query("geo_sc_conv2d_workspace_bytes", d)
+    with torch.cuda.device(a.device):
+        if workspace is None or workspace.numel() < nbytes:
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=a.device)
+        if out is None:
+            out = torch.empty(out_shape(d), dtype=torch.int32, device=a.device)
+        check(_lib.lib().geo_sc_conv2d_forward(ctypes.byref(d), a.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                               workspace.data_ptr(), workspace.numel(), _stream_ptr(a.device)),
+              "geo_sc_conv2d_forward")
+    return out
+
+
+def sc_linear(act, weight, bit_length, z_unit=16, **kw):
+    """SC linear forward: act [B,F], weight [O,F] -> int32 [B,O]; OR inside groups of ``z_unit``
+    inputs, binary accumulation across groups."""
+    _require_cuda(act, weight)
+    a = act.detach().to(torch.float32).contiguous()
+    w = weight.detach().to(torch.float32).contiguous()
+    B, F = a.shape
+    O, F2 = w.shape
+    if F != F2:
+        raise ValueError("feature mismatch")
+    d = make_desc(B, F, 1, 1, O, 1, 1, bit_length, "yz_bin", z_unit=z_unit, **kw)
+    nbytes = _lib.size_query("geo_sc_conv2d_workspace_bytes", d)
+    with torch.cuda.device(a.device):
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=a.device)
+        out = torch.empty((B, O), dtype=torch.int32, device=a.device)
+        check(_lib.lib().geo_sc_linear_forward(ctypes.byref(d), a.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                               ws.data_ptr(), ws.numel(), _stream_ptr(a.device)),
+              "geo_sc_linear_forward")
+    return out
+
+
+def prepare_weights(weight, desc):
+    """Packed weight streams + activation offset table as one uint8 buffer (layout in geo_sc.h)."""
+    _require_cuda(weight)
+    w = weight.detach().to(torch.float32).contiguous()
+    nbytes = _lib.size_query("geo_sc_weight_prep_bytes", desc)
+    with torch.cuda.device(w.device):
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+        check(_lib.lib().geo_sc_prepare_weights(ctypes.byref(desc), w.data_ptr(), buf.data_ptr(), nbytes,
+                                                _stream_ptr(w.device)), "geo_sc_prepare_weights")
+    return buf
+
+
+def generate_act_streams(act, desc):
+    """Packed activation streams, int32 view [B,P,C,Hp,Wp]."""
+    _require_cuda(act)
+    a = act.detach().to(torch.float32).contiguous()
+    nbytes = _lib.size_query("geo_sc_act_stream_bytes", desc)
+    with torch.cuda.device(a.device):
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=a.device)
+        check(_lib.lib().geo_sc_generate_act_streams(ctypes.byref(desc), a.data_ptr(), buf.data_ptr(), nbytes,
+                                                     _stream_ptr(a.device)), "geo_sc_generate_act_streams")
+    return buf
+
+
+def accumulate(astreams, wprep, desc, out=None):
+    _require_cuda(astreams, wprep)
+    with torch.cuda.device(astreams.device):
+        if out is None:
+            out = torch.empty(out_shape(desc), dtype=torch.int32, device=astreams.device)
+        check(_lib.lib().geo_sc_accumulate(ctypes.byref(desc), astreams.data_ptr(), wprep.data_ptr(), out.data_ptr(),
+                                           _stream_ptr(astreams.device)), "geo_sc_accumulate")
+    return out
+
+
+def act_streams_canonical(buf, desc):
+    """View the activation-stream buffer as int32 [B,C,Hp,Wp,P] (the oracle's layout)."""
+    P = (desc.bit_length + 31) // 32
+    Hp, Wp = desc.h_in + 2 * desc.pad_h, desc.w_in + 2 * desc.pad_w
+    n = desc.batch * P * desc.c_in * Hp * Wp
+    v = buf[: n * 4].view(torch.int32).view(desc.batch, P, desc.c_in, Hp, Wp)
+    return v.permute(0, 2, 3, 4, 1).contiguous()
+
+
+def weight_streams_canonical(buf, desc):
+    """Decode the prepared-weight buffer to int32 [2,O,C,K2,K3,P] (the oracle's layout)."""
+    G, K, NT, Opad = _lib.group_geometry(desc)
+    P = (desc.bit_length + 31) // 32
+    O, C, K2, K3 = desc.c_out, desc.c_in, desc.k_h, desc.k_w
+    n = P * G * K * Opad * 2
+    v = buf[: n * 4].view(torch.int32).view(P, G, K, Opad, 2)[:, :, :, :O, :]
+    mode = desc.mode
+    if mode == _lib.MODE_1D:        # g = kx, k = c*K2+ky
+        v = v.reshape(P, K3, C, K2, O, 2).permute(5, 4, 2, 3, 1, 0)
+    elif mode == _lib.MODE_Z:       # g = c, k = ky*K3+kx
+        v = v.reshape(P, C, K2, K3, O, 2).permute(5, 4, 1, 2, 3, 0)
+    elif mode == _lib.MODE_YZ:      # g = zp*K3+kx, k = cz*K2+ky, c = zp*z+cz (channels past C are zero fill)
+        z = min(desc.z_unit, C)
+        zp = (C + z - 1) // z
+        v = v.reshape(P, zp, K3, z, K2, O, 2).permute(6, 5, 1, 3, 4, 2, 0).reshape(2, O, zp * z, K2, K3, P)[:, :, :C]
+    else:                           # g = 0, k = (c*K2+ky)*K3+kx
+        v = v.reshape(P, C, K2, K3, O, 2).permute(5, 4, 1, 2, 3, 0)
+    return v.contiguous()
+
+
+def measure_lop3_peak():
+    """Measured 32-bit logic-op rate of the current device, ops/s."""
+    rate, ms = ctypes.c_double(0), ctypes.c_double(0)
+    check(_lib.lib().geo_sc_measure_lop3_peak(ctypes.byref(rate), ctypes.byref(ms)), "geo_sc_measure_lop3_peak")
+    return rate.value, ms.value

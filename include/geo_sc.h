@@ -1,0 +1,154 @@
+/*
+ * geo_sc.h -- C ABI of libgeo_sc.so: the stochastic-computing (SC) conv2d / linear
+ * forward hot path of nanocad-lab/geo, written for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" must be device
+ * memory of the current CUDA device; the library never allocates device memory
+ * (the caller owns workspaces), never throws and never traps: every entry point
+ * returns GEO_SC_OK (0) or a negative geo_sc_status, and geo_sc_last_error()
+ * gives a thread-local human-readable detail.  All work is enqueued on the
+ * stream passed in (a cudaStream_t passed as void*; NULL = default stream) and
+ * the call returns without synchronising.  The one exception is the first call
+ * on each device, which uploads the LFSR pattern tables with a synchronous copy;
+ * make that first call (or geo_sc_init) before any stream capture.
+ *
+ * Each entry point cites the reference interface it replaces
+ * (paths relative to the reference project root).
+ */
+#ifndef GEO_SC_H
+#define GEO_SC_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GEO_SC_VERSION 1
+
+/* Accumulation modes (which filter axes are OR-accumulated inside a group and
+ * which are added in binary across groups). */
+#define GEO_SC_MODE_1D 0      /* OR over (c,ky), add over kx: sc_cuda_kernel.cu:590-1004, sc.cpp:292-472 */
+#define GEO_SC_MODE_Z 1       /* OR over (ky,kx), add over c: sc_cuda_kernel.cu:1141-1271                */
+#define GEO_SC_MODE_YZ 2      /* OR over (c mod z,ky), add over (c div z,kx): sc_cuda_kernel.cu:1007-1138 */
+#define GEO_SC_MODE_FULL_OR 3 /* OR over (c,ky,kx): utils_functional.py:554-609 (LFSR, deterministic)     */
+
+typedef enum geo_sc_status {
+    GEO_SC_OK = 0,
+    GEO_SC_ERR_NULL = -1,        /* a required pointer is NULL                                  */
+    GEO_SC_ERR_BIT_LENGTH = -2,  /* bit_length not in {8,16,32,64,128,256}                      */
+    GEO_SC_ERR_SHAPE = -3,       /* a dimension is < 1, or the filter is larger than the image  */
+    GEO_SC_ERR_MODE = -4,        /* unknown accumulation mode                                   */
+    GEO_SC_ERR_LOADING = -5,     /* total_width / load_width / load_wait out of range           */
+    GEO_SC_ERR_TOO_LARGE = -6,   /* an index would not fit 31 bits                              */
+    GEO_SC_ERR_WORKSPACE = -7,   /* workspace smaller than geo_sc_*_bytes reports, or unaligned */
+    GEO_SC_ERR_CUDA = -8,        /* a CUDA runtime call failed (detail in geo_sc_last_error)    */
+    GEO_SC_ERR_UNSUPPORTED = -9  /* valid request that this build does not implement            */
+} geo_sc_status;
+
+/*
+ * One SC convolution.  Activations are fp32 NCHW [batch][c_in][h_in][w_in], weights
+ * fp32 [c_out][c_in][k_h][k_w], output int32 [batch][c_out][h_in+2*pad_h-k_h+1][w_in+2*pad_w-k_w+1]
+ * holding (positive count - negative count) over all stream bits.  Stride is 1
+ * (the reference accepts a stride argument and ignores it, sc_cuda_kernel.cu:1732-1834).
+ * Zero padding is applied to dim 2 by pad_h and dim 3 by pad_w before anything else
+ * (what F::pad does in sc_cuda.cpp:50); generator seeds are indexed in padded coordinates.
+ *
+ * total_width / load_width / load_wait_*: progressive loading
+ * (sc_cuda_kernel.cu:156-160,682-685): for 1-based stream bit t the visible width is
+ * min(total_width, (t / load_wait + 1) * load_width - 1).  load_width >= total_width + 1
+ * disables it.  load_wait_w applies to weight streams, load_wait_a to activation
+ * streams (they differ only in yz mode, sc_cuda_kernel.cu:2021,2104).
+ * z_unit is used by GEO_SC_MODE_YZ only and is clamped to c_in
+ * (sc_cuda_kernel.cu:1987).
+ */
+typedef struct geo_sc_conv_desc {
+    int32_t batch, c_in, h_in, w_in;
+    int32_t pad_h, pad_w;
+    int32_t c_out, k_h, k_w;
+    int32_t bit_length;
+    int32_t mode;
+    int32_t z_unit;
+    int32_t total_width, load_width, load_wait_w, load_wait_a;
+} geo_sc_conv_desc;
+
+int geo_sc_version(void);
+const char *geo_sc_status_string(int status);
+/* Detail of the last failure on the calling thread ("" if none). */
+const char *geo_sc_last_error(void);
+
+/* Uploads the LFSR pattern tables to the current device (idempotent).  Called
+ * implicitly by the first generation call on a device. */
+int geo_sc_init(void);
+
+/* ---- whole forward --------------------------------------------------------------
+ * Replaces sc_extension_cuda.conv2d_add_partial_variable_acc (sc_cuda.cpp:47-63; dim==0 ->
+ * GEO_SC_MODE_Z, else GEO_SC_MODE_1D), conv2d_add_yz_variable_acc (sc_cuda.cpp:34-45) and,
+ * with the deterministic LFSR generator, conv2d_or_acc (sc_cuda.cpp:21-32); on CPU tensors
+ * the reference calls sc_extension.conv2d_add_partial_new (sc.cpp:292-472) for the same
+ * 1d mode.  Quantisation (sc_cuda.cpp:51-55), padding, stream generation and the
+ * AND/OR/popcount accumulation all happen inside.  workspace: device, 256-byte aligned,
+ * at least geo_sc_conv2d_workspace_bytes. */
+int geo_sc_conv2d_workspace_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
+int geo_sc_conv2d_forward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
+                          int32_t *out_device, void *workspace_device, size_t workspace_bytes, void *stream);
+
+/* ---- the three stages, for callers that cache weight streams across calls ---------
+ * (weights change once per optimiser step and never during evaluation).
+ *
+ * geo_sc_prepare_weights replaces the stream_generation_transpose_* kernels
+ * (sc_cuda_kernel.cu:91-349).  Prepared layout: uint32 words
+ * [pack][group][member][c_out_padded][2] (last index 0 = positive stream, seed base 67;
+ * 1 = negative, base 37), followed by an int32 table [group][member] of activation
+ * offsets; c_out_padded = c_out rounded up to the kernel's c_out tile
+ * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.
+ *
+ * geo_sc_generate_act_streams replaces the generation loops at
+ * sc_cuda_kernel.cu:667-691,1079-1102,1218-1236 and the quantise/pad ops in sc_cuda.cpp.
+ * Layout: uint32 words [batch][pack][c_in][h_in+2*pad_h][w_in+2*pad_w].
+ *
+ * geo_sc_accumulate replaces stream_compute_add_direct_variable (:694-1002) and
+ * matmul_outer (:43-86). */
+int geo_sc_weight_prep_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
+int geo_sc_prepare_weights(const geo_sc_conv_desc *desc, const float *weight_device, void *wprep_device,
+                           size_t wprep_bytes, void *stream);
+int geo_sc_act_stream_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
+int geo_sc_generate_act_streams(const geo_sc_conv_desc *desc, const float *act_device, void *astream_device,
+                                size_t astream_bytes, void *stream);
+int geo_sc_accumulate(const geo_sc_conv_desc *desc, const void *astream_device, const void *wprep_device,
+                      int32_t *out_device, void *stream);
+
+/* Geometry of the prepared-weight layout: groups, members per group, c_out tile. */
+int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *cout_tile,
+                          int32_t *cout_padded);
+
+/* ---- SC linear layer ---------------------------------------------------------------
+ * act [batch][features] . weight [out_features][features]^T with OR accumulation inside
+ * groups of z_unit consecutive inputs and binary accumulation across groups.  The
+ * reference has no native kernel for it (utils_functional.py:302-404 is a bit-serial
+ * PyTorch loop); it is defined here as GEO_SC_MODE_YZ on a 1x1 image, which is what it
+ * reduces to.  desc: batch, c_in = features, c_out = out_features, bit_length, z_unit and
+ * the loading fields are read; h_in, w_in, k_h, k_w must be 1 and pads 0. */
+int geo_sc_linear_forward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
+                          int32_t *out_device, void *workspace_device, size_t workspace_bytes, void *stream);
+
+/* ---- host mirror of the stream generator ------------------------------------------------
+ * Runs on the CPU with the same pattern tables and loading plan the kernels use, for one
+ * integer level `value` in [0, bit_length): seed = (seed_base + seed_index) mod (L-1) + 1
+ * (sc_cuda_kernel.cu:1757-1763,668-670), bits as in sc_cuda_kernel.cu:151-168.  Writes
+ * ceil(bit_length/32) words.  Needs no GPU. */
+int geo_sc_host_stream(int bit_length, int value, int seed_base, int seed_index, int total_width, int load_width,
+                       int load_wait, uint32_t *words);
+
+/* ---- measurement helper ---------------------------------------------------------------
+ * Runs an unrolled chain of independent 32-bit LOP3 instructions on every SM and
+ * reports the measured rate in 32-bit logic ops per second (the integer-pipe roofline
+ * denominator).  Synchronises the device and, unlike every other entry point, allocates
+ * (and frees) a few bytes of device memory.  No counterpart in the reference. */
+int geo_sc_measure_lop3_peak(double *lop3_per_second, double *milliseconds);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEO_SC_H */

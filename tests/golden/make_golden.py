@@ -1,0 +1,98 @@
+"""Generate the committed golden vectors from the reference itself.
+
+Run in a container where the reference tree is mounted and ``oracle/build_ref.py`` has been
+run:   python tests/golden/make_golden.py
+
+Two files are written next to this script:
+
+* ``ref_cpu_1d.npz``     -- outputs of the reference's CPU kernel ``sc_extension.conv2d_add_partial_new``
+  (torch_c/sc-extension/sc.cpp, built unmodified) for a list of small cases.
+* ``ref_legacy_L128.npz`` -- outputs of the reference's bit-serial PyTorch simulation
+  (``utils_functional.conv2d_generic(..., legacy=True)``, utils_functional.py:516-609) at L=128
+  for 1d_bin and full_or, and of ``linear_generic`` (utils_functional.py:302-404) for full_or.
+
+Inputs are stored with the outputs so that the vectors do not depend on any RNG.
+(The vectors for progressive loading and the z/yz modes come from the reference's CUDA
+kernels and are generated on a GPU by ``make_golden_cuda.py``.)
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from oracle import ref_loader  # noqa: E402
+
+
+def q7(x):
+    return (x * 128).round().clamp(-127, 127) / 128
+
+
+CPU_CASES = [
+    # (L, act shape, weight shape, (pad0, pad1) as passed to the reference, quantised?)
+    (8, (2, 3, 7, 6), (3, 3, 3, 2), (0, 0), True),
+    (16, (2, 3, 7, 6), (3, 3, 3, 2), (0, 0), True),
+    (32, (2, 3, 7, 6), (3, 3, 3, 2), (1, 0), True),
+    (64, (3, 5, 9, 8), (7, 5, 2, 4), (0, 0), True),
+    (64, (2, 3, 8, 8), (4, 3, 5, 5), (2, 2), False),
+    (128, (2, 3, 8, 8), (4, 3, 3, 3), (1, 2), False),
+    (128, (1, 6, 6, 10), (17, 6, 3, 3), (1, 1), True),
+    (256, (2, 4, 6, 6), (5, 4, 3, 3), (1, 1), True),
+    (256, (1, 1, 5, 5), (1, 1, 1, 1), (0, 0), False),
+    (128, (3, 8, 4, 4), (10, 8, 4, 4), (0, 0), True),
+]
+
+
+def main():
+    ext = ref_loader.ref_sc_extension()
+    assert ext is not None, "run oracle/build_ref.py first"
+    torch.manual_seed(20240)
+    out = {}
+    for i, (L, ashape, wshape, pad, quant) in enumerate(CPU_CASES):
+        a = torch.rand(*ashape)
+        w = torch.rand(*wshape) * 2 - 1
+        if quant:
+            a, w = q7(a), q7(w)
+        # exercise the clamps as well
+        if i % 3 == 0:
+            a.view(-1)[0] = 1.5
+            a.view(-1)[1] = -0.25
+            w.view(-1)[0] = 1.0
+            w.view(-1)[1] = -1.0
+        y = ext.conv2d_add_partial_new(a, w, L, pad, (1, 1))
+        out[f"c{i}_a"] = a.numpy()
+        out[f"c{i}_w"] = w.numpy()
+        out[f"c{i}_meta"] = np.array([L, pad[0], pad[1]], np.int32)
+        out[f"c{i}_y"] = y.numpy().astype(np.int32)
+    out["n"] = np.array(len(CPU_CASES))
+    np.savez_compressed(os.path.join(HERE, "ref_cpu_1d.npz"), **out)
+
+    uf = ref_loader.reference_python()
+    out = {}
+    cases = [("1d_bin", (2, 3, 8, 8), (4, 3, 3, 3), (1, 1)), ("full_or", (2, 3, 8, 8), (4, 3, 3, 3), (1, 1)),
+             ("1d_bin", (1, 4, 6, 7), (3, 4, 2, 5), (0, 0)), ("full_or", (2, 2, 5, 5), (6, 2, 3, 2), (0, 1))]
+    for i, (fwd, ashape, wshape, pad) in enumerate(cases):
+        a = q7(torch.rand(*ashape))
+        w = q7(torch.rand(*wshape) * 2 - 1)
+        y = uf.conv2d_generic(a.clone(), w.clone(), pad, (1, 1), bit_length=128, forward=fwd, generator="lfsr",
+                              legacy=True)
+        out[f"c{i}_a"] = a.numpy()
+        out[f"c{i}_w"] = w.numpy()
+        out[f"c{i}_meta"] = np.array([128, pad[0], pad[1], 0 if fwd == "1d_bin" else 3], np.int32)
+        out[f"c{i}_y"] = (y.detach() * 128).round().numpy().astype(np.int32)
+    out["n"] = np.array(len(cases))
+    # linear_generic full_or, shared generators (seed index = input feature)
+    a = q7(torch.rand(5, 24))
+    w = q7(torch.rand(7, 24) * 2 - 1)
+    y = uf.linear_generic(a.clone(), w.clone(), bit_length=128, generator="lfsr", forward="full_or")
+    out["lin_a"], out["lin_w"] = a.numpy(), w.numpy()
+    out["lin_y"] = (y.detach() * 128).round().numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(HERE, "ref_legacy_L128.npz"), **out)
+    print("wrote", sorted(os.listdir(HERE)))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,72 @@
+"""The CPU oracle against the golden vectors generated from the reference itself
+(tests/golden/make_golden.py, make_golden_cuda.py)."""
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_lfsr_maximal_length_and_reference_formula(oracle_lib):
+    # Every LFSR visits all non-zero states once per period (period 2^n - 1), 0 is a fixed point.
+    for n in range(3, 9):
+        seen, s = [], 1
+        for _ in range((1 << n) - 1):
+            seen.append(s)
+            s = oracle_lib.lfsr_step(s, n)
+        assert s == 1 and sorted(seen) == list(range(1, 1 << n))
+        assert oracle_lib.lfsr_step(0, n) == 0
+
+
+def test_oracle_matches_reference_cpu_kernel(oracle_lib):
+    g = np.load(os.path.join(GOLDEN, "ref_cpu_1d.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1 = (int(v) for v in g[f"c{i}_meta"])
+        # the reference pads the last dimension by padding[0] and dimension 2 by padding[1]
+        y = oracle_lib.conv2d(g[f"c{i}_a"], g[f"c{i}_w"], L, "1d_bin", pad_h=p1, pad_w=p0)
+        assert np.array_equal(y, g[f"c{i}_y"]), f"case {i} (L={L})"
+
+
+def test_oracle_matches_reference_bit_serial_simulation(oracle_lib):
+    g = np.load(os.path.join(GOLDEN, "ref_legacy_L128.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1, mode = (int(v) for v in g[f"c{i}_meta"])
+        y = oracle_lib.conv2d(g[f"c{i}_a"], g[f"c{i}_w"], L, mode, pad_h=p1, pad_w=p0)
+        assert np.array_equal(y, g[f"c{i}_y"]), f"case {i} mode {mode}"
+    a, w = g["lin_a"], g["lin_w"]
+    y = oracle_lib.linear(a, w, 128, z_unit=a.shape[1])
+    assert np.array_equal(y, g["lin_y"])
+
+
+@pytest.mark.parametrize("name", ["ref_cuda_modes.npz"])
+def test_oracle_matches_reference_cuda_kernels(oracle_lib, name):
+    path = os.path.join(GOLDEN, name)
+    if not os.path.exists(path):
+        pytest.skip("reference-CUDA golden vectors not generated yet")
+    g = np.load(path)
+    for i in range(int(g["n"])):
+        L, mode, z, tw, lu, lww, lwa = (int(v) for v in g[f"c{i}_meta"])
+        y = oracle_lib.conv2d(g[f"c{i}_a"], g[f"c{i}_w"], L, mode, z_unit=z, total_width=tw, load_width=lu,
+                              load_wait_w=lww, load_wait_a=lwa)
+        assert np.array_equal(y, g[f"c{i}_y"]), f"case {i} meta {g[f'c{i}_meta']}"
+
+
+def test_mode_identities(oracle_lib):
+    rng = np.random.default_rng(5)
+    a = rng.random((2, 4, 5, 6), dtype=np.float32)
+    w = (rng.random((3, 4, 2, 3), dtype=np.float32) * 2 - 1)
+    for L in (32, 128):
+        # yz with z_unit >= C and K3 == 1 collapses to full OR when weights have one column
+        w1 = w[:, :, :, :1].copy()
+        assert np.array_equal(oracle_lib.conv2d(a, w1, L, "yz_bin", z_unit=64), oracle_lib.conv2d(a, w1, L, "1d_bin"))
+        # a 1x1 filter makes z_bin and yz_bin(z=1) the same sum over channels (seeds coincide: idx 0)
+        w11 = w[:, :, :1, :1].copy()
+        assert np.array_equal(oracle_lib.conv2d(a, w11, L, "z_bin"), oracle_lib.conv2d(a, w11, L, "yz_bin", z_unit=1)) \
+            or True  # activation seeds differ between the two modes (c vs c mod z); identity only for C == 1
+        a1 = a[:, :1].copy()
+        assert np.array_equal(oracle_lib.conv2d(a1, w11[:, :1], L, "z_bin"),
+                              oracle_lib.conv2d(a1, w11[:, :1], L, "yz_bin", z_unit=1))
+    # zero weights or zero activations give zero counts
+    assert not oracle_lib.conv2d(a * 0, w, 64).any()
+    assert not oracle_lib.conv2d(a, w * 0, 64).any()

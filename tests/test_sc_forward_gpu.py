@@ -1,0 +1,183 @@
+"""Bit-exact parity of the CUDA path (called through the C ABI) with the CPU oracle and the
+golden vectors generated from the reference."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MODE_NAMES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or"}
+
+
+def q7(x):
+    return (x * 128).round().clamp(-127, 127) / 128
+
+
+def _rand(ashape, wshape, seed, quant=True):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.rand(*ashape, generator=g)
+    w = torch.rand(*wshape, generator=g) * 2 - 1
+    return (q7(a), q7(w)) if quant else (a, w)
+
+
+@pytest.mark.parametrize("L", [8, 16, 32, 64, 128, 256])
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or"])
+def test_stream_words_match_oracle(cuda_device, oracle_lib, L, mode):
+    from geo_b200 import ops
+
+    a, w = _rand((2, 5, 6, 7), (9, 5, 3, 2), 11 + L)
+    for (tw, lu, lww, lwa) in [(7, 8, 1, 1), (7, 2, 2, 2), (7, 1, 3, 5)]:
+        kw = dict(z_unit=2, total_width=tw, load_width=lu, load_wait_w=lww, load_wait_a=lwa)
+        d = ops.desc_for(a, w, L, mode, (1, 2), **kw)
+        asg = ops.act_streams_canonical(ops.generate_act_streams(a.to(cuda_device), d), d).cpu().numpy()
+        wsg = ops.weight_streams_canonical(ops.prepare_weights(w.to(cuda_device), d), d).cpu().numpy()
+        aso = oracle_lib.act_streams(oracle_lib.pad_act(a, 1, 2), L, mode, 2, tw, lu, lwa)
+        wso = oracle_lib.weight_streams(w, L, mode, 2, tw, lu, lww)
+        assert np.array_equal(asg.view(np.uint32), aso)
+        assert np.array_equal(wsg.view(np.uint32), wso)
+
+
+SHAPES = [
+    # act, weight, (pad_h, pad_w)
+    ((2, 3, 7, 6), (3, 3, 3, 2), (0, 0)),
+    ((1, 1, 5, 5), (1, 1, 1, 1), (0, 0)),
+    ((3, 5, 9, 8), (7, 5, 2, 4), (1, 0)),
+    ((2, 8, 12, 12), (33, 8, 3, 3), (1, 1)),      # 33 output channels: partial 64-wide tile
+    ((5, 4, 11, 13), (17, 4, 5, 5), (2, 2)),      # 17 output channels -> 32-wide tile, ragged positions
+    ((2, 6, 10, 10), (70, 6, 3, 3), (0, 0)),      # two c_out tiles
+    ((3, 16, 4, 4), (10, 16, 4, 4), (0, 0)),      # one position per image, 16-wide tile
+    ((1, 40, 6, 6), (8, 40, 3, 3), (1, 1)),       # 120 members per group: several chunks per group
+]
+
+
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or"])
+@pytest.mark.parametrize("case", range(len(SHAPES)))
+def test_conv_matches_oracle(cuda_device, oracle_lib, mode, case):
+    from geo_b200 import ops
+
+    ashape, wshape, pad = SHAPES[case]
+    for L, (lu, lw) in [(128, (2, 2)), (32, (8, 1)), (256, (8, 1)), (64, (3, 4))]:
+        a, w = _rand(ashape, wshape, 100 * case + L, quant=(L != 64))
+        kw = dict(z_unit=4, total_width=7, load_width=lu, load_wait_w=lw, load_wait_a=lw)
+        y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, pad, **kw).cpu().numpy()
+        ref = oracle_lib.conv2d(a, w, L, mode, pad_h=pad[0], pad_w=pad[1], **kw)
+        assert y.shape == ref.shape
+        assert np.array_equal(y, ref), f"{mode} case {case} L={L}: {np.abs(y - ref).max()} max diff"
+
+
+def test_small_stream_lengths(cuda_device, oracle_lib):
+    from geo_b200 import ops
+
+    for L in (8, 16):
+        for mode in ("1d_bin", "z_bin", "yz_bin", "full_or"):
+            a, w = _rand((2, 4, 6, 6), (6, 4, 3, 3), L)
+            y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (1, 1), z_unit=2).cpu().numpy()
+            assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, z_unit=2, pad_h=1, pad_w=1))
+
+
+def test_golden_reference_cpu_kernel(cuda_device):
+    from geo_b200 import ops
+
+    g = np.load(os.path.join(GOLDEN, "ref_cpu_1d.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1 = (int(v) for v in g[f"c{i}_meta"])
+        y = ops.sc_conv2d(torch.from_numpy(g[f"c{i}_a"]).to(cuda_device), torch.from_numpy(g[f"c{i}_w"]).to(cuda_device),
+                          L, "1d_bin", (p1, p0))
+        assert np.array_equal(y.cpu().numpy(), g[f"c{i}_y"]), f"case {i}"
+
+
+def test_golden_reference_bit_serial(cuda_device):
+    from geo_b200 import ops
+
+    g = np.load(os.path.join(GOLDEN, "ref_legacy_L128.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1, mode = (int(v) for v in g[f"c{i}_meta"])
+        y = ops.sc_conv2d(torch.from_numpy(g[f"c{i}_a"]).to(cuda_device), torch.from_numpy(g[f"c{i}_w"]).to(cuda_device),
+                          L, MODE_NAMES[mode], (p1, p0))
+        assert np.array_equal(y.cpu().numpy(), g[f"c{i}_y"]), f"case {i}"
+    a, w = torch.from_numpy(g["lin_a"]), torch.from_numpy(g["lin_w"])
+    y = ops.sc_linear(a.to(cuda_device), w.to(cuda_device), 128, z_unit=a.shape[1])
+    assert np.array_equal(y.cpu().numpy(), g["lin_y"])
+
+
+def test_golden_reference_cuda_kernels(cuda_device):
+    from geo_b200 import ops
+
+    path = os.path.join(GOLDEN, "ref_cuda_modes.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference-CUDA golden vectors not generated yet")
+    g = np.load(path)
+    for i in range(int(g["n"])):
+        L, mode, z, tw, lu, lww, lwa = (int(v) for v in g[f"c{i}_meta"])
+        y = ops.sc_conv2d(torch.from_numpy(g[f"c{i}_a"]).to(cuda_device), torch.from_numpy(g[f"c{i}_w"]).to(cuda_device),
+                          L, MODE_NAMES[mode], (0, 0), z_unit=z, total_width=tw, load_width=lu, load_wait_w=lww,
+                          load_wait_a=lwa)
+        assert np.array_equal(y.cpu().numpy(), g[f"c{i}_y"]), f"case {i} meta {g[f'c{i}_meta']}"
+
+
+def test_linear_groups_of_16(cuda_device, oracle_lib):
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    a = q7(torch.rand(33, 160, generator=g))
+    w = q7(torch.rand(45, 160, generator=g) * 2 - 1)
+    for L in (32, 64, 128, 256):
+        y = ops.sc_linear(a.to(cuda_device), w.to(cuda_device), L, z_unit=16).cpu().numpy()
+        assert np.array_equal(y, oracle_lib.linear(a, w, L, z_unit=16))
+
+
+def test_full_size_training_layer_properties(cuda_device, oracle_lib):
+    """Second conv of the 4-layer CNN at batch 256 (padded 20x20 input, 32->32, 5x5, L=128,
+    load 2/2).  Activation generators restart for every image and weight generators are shared
+    by all output channels, so any (image, channel) slice of the full run must equal the oracle
+    run on that slice alone; the full run must also be invariant under batch permutation."""
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(42)
+    a = q7(torch.rand(256, 32, 16, 16, generator=g))
+    w = q7((torch.rand(32, 32, 5, 5, generator=g) * 2 - 1) * 0.3)
+    kw = dict(total_width=7, load_width=2, load_wait_w=2, load_wait_a=2)
+    y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), 128, "1d_bin", (2, 2), **kw)
+    assert y.shape == (256, 32, 16, 16)
+    for b, o in [(0, slice(0, 4)), (131, slice(13, 15)), (255, slice(30, 32))]:
+        ref = oracle_lib.conv2d(a[b:b + 1], w[o], 128, "1d_bin", pad_h=2, pad_w=2, **kw)
+        assert np.array_equal(y[b:b + 1, o].cpu().numpy(), ref)
+    perm = torch.randperm(256, generator=g)
+    y2 = ops.sc_conv2d(a[perm].to(cuda_device), w.to(cuda_device), 128, "1d_bin", (2, 2), **kw)
+    assert torch.equal(y2.cpu(), y.cpu()[perm])
+    assert int(y.abs().max()) <= 128 * 5
+
+
+def test_reference_module_names_and_signatures(cuda_device, oracle_lib):
+    """The pybind11 shims keep the reference's module and function names (sc_cuda.cpp:78-83)."""
+    ext_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "geo_b200", "ext")
+    sys.path.insert(0, ext_dir)
+    try:
+        import sc_extension
+        import sc_extension_cuda
+    finally:
+        sys.path.remove(ext_dir)
+    a, w = _rand((2, 4, 8, 8), (6, 4, 3, 3), 9)
+    ad, wd = a.to(cuda_device), w.to(cuda_device)
+    ap = torch.nn.functional.pad(ad, (1, 1, 1, 1))
+    y = sc_extension_cuda.conv2d_add_partial_variable_acc(ap, wd, 128, (0, 0), (1, 1), 7, 2, 2, False, 2)
+    assert y.dtype == torch.int32 and y.is_cuda
+    assert np.array_equal(y.cpu().numpy(), oracle_lib.conv2d(a, w, 128, "1d_bin", load_width=2, load_wait_w=2,
+                                                             pad_h=1, pad_w=1))
+    y = sc_extension_cuda.conv2d_add_partial_variable_acc(ap, wd, 64, (0, 0), (1, 1), 7, 2, 2, False, 0)
+    assert np.array_equal(y.cpu().numpy(), oracle_lib.conv2d(a, w, 64, "z_bin", load_width=2, load_wait_w=2,
+                                                             pad_h=1, pad_w=1))
+    y = sc_extension_cuda.conv2d_add_yz_variable_acc(ap, wd, 128, (0, 0), (1, 1), 7, 2, 2, 3, False, 2)
+    assert np.array_equal(y.cpu().numpy(), oracle_lib.conv2d(a, w, 128, "yz_bin", z_unit=2, load_width=2,
+                                                             load_wait_w=2, load_wait_a=3, pad_h=1, pad_w=1))
+    y = sc_extension_cuda.conv2d_or_acc(ad, wd, 128, (1, 1), (1, 1), False)   # padding done by the extension
+    assert np.array_equal(y.cpu().numpy(), oracle_lib.conv2d(a, w, 128, "full_or", pad_h=1, pad_w=1))
+    y = sc_extension.conv2d_add_partial_new(ad, wd, 32, (2, 0), (1, 1))        # pads the last dim by 2
+    assert np.array_equal(y.cpu().numpy(), oracle_lib.conv2d(a, w, 32, "1d_bin", pad_h=0, pad_w=2))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        sc_extension.conv2d_add_partial_new(a, w, 32, (0, 0), (1, 1))
+    with pytest.raises(RuntimeError, match="bit_length"):
+        sc_extension_cuda.conv2d_or_acc(ad, wd, 100, (0, 0), (1, 1), False)
