@@ -1,0 +1,126 @@
+"""The models the headline benchmarks are quoted on.
+
+``CONV_tiny_add_partial`` mirrors the reference's 4-layer SC CNN (network.py:126-190; the
+training default of main_conv.py).  ``VGG11_add_partial`` is the VGG-11-style SC CNN used for the
+data-parallel configuration; the reference has no such model file, it is built from the same
+layers in the same conv -> BN -> (pool) -> hardtanh order.
+"""
+from __future__ import annotations
+
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import layers
+
+
+def _per_layer(values, n):
+    values = list(values)
+    if len(values) < n:
+        values = values + [values[-1]] * (n - len(values))
+    return values
+
+
+class CONV_tiny_add_partial(nn.Module):
+    """conv 3->32 5x5, conv 32->32 5x5, conv 32->64 5x5 (each: BN, 2x2 average pool, hardtanh(0,1)),
+    then a 4x4 conv 64->classes and a 1d BN.  Per-layer stream length exponent ``err``, OR width
+    exponent ``z_unit``, ``load_unit`` and ``load_wait`` are lists indexed by layer, assigned after
+    construction exactly as main_conv.py:178-182 does."""
+
+    def __init__(self, num_classes=10, c_ins=3, uniform=False, generator="lfsr", sc_compute="1d_bin", legacy=False,
+                 relu=False):
+        super().__init__()
+        self.bn1 = layers.BatchNorm2d_fixed(32)
+        self.bn2 = layers.BatchNorm2d_fixed(32)
+        self.bn3 = layers.BatchNorm2d_fixed(64)
+        self.bn4 = layers.BatchNorm1d_fixed(num_classes)
+        self.conv1 = layers.Conv2d_Add_Partial(3, 32, kernel_size=5, padding=2, bias=False)
+        self.conv2 = layers.Conv2d_Add_Partial(32, 32, kernel_size=5, padding=2, bias=False)
+        self.conv3 = layers.Conv2d_Add_Partial(32, 64, kernel_size=5, padding=2, bias=False)
+        self.fc1 = layers.Conv2d_Add_Partial(64, num_classes, kernel_size=4, padding=0, bias=False)
+        self.tanh = nn.Hardtanh(0, 1)
+        self.pool = nn.AvgPool2d(2)
+        self.err = [7, 7, 7, 7]
+        self.z_unit = [3, 3, 4, 4]
+        self.load_unit = [2, 2, 2, 2]
+        self.load_wait = [2, 2, 2, 2]
+        self.num_classes = num_classes
+        self.generator = generator
+        self.compute = sc_compute
+        self.legacy = legacy
+        self.relu = relu
+        if uniform:  # larger weights for very short streams (network.py:153-158)
+            for conv in (self.conv1, self.conv2):
+                conv.weight_org *= 2
+                conv.weight.data *= 2
+
+    def _sc(self, conv, x, i):
+        # The last layer takes its weight load_wait from entry 2 and its activation load_wait from
+        # entry 3 (network.py:186); kept so that per-layer settings mean the same thing.
+        wait_w = self.load_wait[2] if i == 3 else self.load_wait[i]
+        return conv(x, err=self.err[i], forward=self.compute, generator=self.generator, z_unit=2 ** self.z_unit[i],
+                    legacy=self.legacy, load_unit=self.load_unit[i], load_wait_w=wait_w,
+                    load_wait_a=self.load_wait[i])
+
+    def forward(self, x_in, target=None):
+        x = x_in
+        for i, (conv, bn) in enumerate(((self.conv1, self.bn1), (self.conv2, self.bn2), (self.conv3, self.bn3))):
+            x = bn(self._sc(conv, x, i))
+            if self.relu:
+                x = F.relu(x)
+            x = self.tanh(self.pool(x))
+        x = self._sc(self.fc1, x, 3).view(-1, self.num_classes)
+        return self.bn4(x)  # BN at the output stabilises training (network.py:188-189)
+
+
+class VGG11_add_partial(nn.Module):
+    """VGG-11-style SC CNN for 32x32 inputs: eight 3x3 SC convs (64,128,256,256,512,512,512,512;
+    2x2 average pool after convs 1,2,4,6,8), then three SC layers 512->512->512->classes written as
+    1x1 convs on the 1x1 feature map."""
+
+    WIDTHS = (64, 128, 256, 256, 512, 512, 512, 512)
+    POOL_AFTER = (0, 1, 3, 5, 7)
+
+    def __init__(self, num_classes=10, generator="lfsr", sc_compute="1d_bin", legacy=False):
+        super().__init__()
+        convs, bns, c = [], [], 3
+        for wd in self.WIDTHS:
+            convs.append(layers.Conv2d_Add_Partial(c, wd, kernel_size=3, padding=1, bias=False))
+            bns.append(layers.BatchNorm2d_fixed(wd))
+            c = wd
+        self.convs = nn.ModuleList(convs)
+        self.bns = nn.ModuleList(bns)
+        self.fc1 = layers.Conv2d_Add_Partial(512, 512, kernel_size=1, padding=0, bias=False)
+        self.fc2 = layers.Conv2d_Add_Partial(512, 512, kernel_size=1, padding=0, bias=False)
+        self.fc3 = layers.Conv2d_Add_Partial(512, num_classes, kernel_size=1, padding=0, bias=False)
+        self.bnf1 = layers.BatchNorm2d_fixed(512)
+        self.bnf2 = layers.BatchNorm2d_fixed(512)
+        self.bn_out = layers.BatchNorm1d_fixed(num_classes)
+        self.tanh = nn.Hardtanh(0, 1)
+        self.pool = nn.AvgPool2d(2)
+        n = len(self.WIDTHS) + 3
+        self.err = [7] * n
+        self.z_unit = [4] * n
+        self.load_unit = [2] * n
+        self.load_wait = [2] * n
+        self.num_classes = num_classes
+        self.generator = generator
+        self.compute = sc_compute
+        self.legacy = legacy
+
+    def _sc(self, conv, x, i):
+        err, zu = _per_layer(self.err, i + 1)[i], _per_layer(self.z_unit, i + 1)[i]
+        lu, lw = _per_layer(self.load_unit, i + 1)[i], _per_layer(self.load_wait, i + 1)[i]
+        return conv(x, err=err, forward=self.compute, generator=self.generator, z_unit=2 ** zu, legacy=self.legacy,
+                    load_unit=lu, load_wait_w=lw, load_wait_a=lw)
+
+    def forward(self, x, target=None):
+        for i, (conv, bn) in enumerate(zip(self.convs, self.bns)):
+            x = bn(self._sc(conv, x, i))
+            if i in self.POOL_AFTER:
+                x = self.pool(x)
+            x = self.tanh(x)
+        n = len(self.convs)
+        x = self.tanh(self.bnf1(self._sc(self.fc1, x, n)))
+        x = self.tanh(self.bnf2(self._sc(self.fc2, x, n + 1)))
+        x = self._sc(self.fc3, x, n + 2).view(-1, self.num_classes)
+        return self.bn_out(x)

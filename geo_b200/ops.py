@@ -13,6 +13,35 @@ from . import _lib
 from ._lib import MODES, ConvDesc, check, make_desc  # noqa: F401
 
 
+class _Stats:
+    """Launch accounting for the benchmark: ``launches`` counts kernels of this library enqueued
+    since the last reset; with ``profile`` on, every accumulate launch is bracketed by CUDA events
+    on the launching stream and recorded as (algorithmic LOP3 count, algorithmic bytes, start, end)."""
+
+    def __init__(self):
+        self.launches = 0
+        self.profile = False
+        self.records = []
+
+    def reset(self):
+        self.launches = 0
+        self.records = []
+
+
+STATS = _Stats()
+
+
+def algorithmic_work(desc):
+    """(LOP3 count, HBM bytes) of one SC forward by definition: 2*MAC*packs 32-bit logic ops, and
+    fp32 activations + fp32 weights in, int32 counts out."""
+    B, O, Ho, Wo = out_shape(desc)
+    mac = B * O * Ho * Wo * desc.c_in * desc.k_h * desc.k_w
+    packs = (desc.bit_length + 31) // 32
+    nbytes = 4 * (desc.batch * desc.c_in * desc.h_in * desc.w_in + O * desc.c_in * desc.k_h * desc.k_w
+                  + B * O * Ho * Wo)
+    return 2 * mac * packs, nbytes
+
+
 def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -52,7 +81,26 @@ def sc_conv2d(act, weight, bit_length, mode="1d_bin", padding=(0, 0), workspace=
         check(_lib.lib().geo_sc_conv2d_forward(ctypes.byref(d), a.data_ptr(), w.data_ptr(), out.data_ptr(),
                                                workspace.data_ptr(), workspace.numel(), _stream_ptr(a.device)),
               "geo_sc_conv2d_forward")
+    STATS.launches += 3
     return out
+
+
+def sc_conv2d_staged(act, weight, bit_length, mode="1d_bin", padding=(0, 0), wprep=None, **kw):
+    """Same result as :func:`sc_conv2d` through the three stage entry points; ``wprep`` may hold
+    weight streams prepared earlier for the same weights and descriptor geometry."""
+    _require_cuda(act, weight)
+    d = desc_for(act, weight, bit_length, mode, padding, **kw)
+    if wprep is None:
+        wprep = prepare_weights(weight, d)
+    astreams = generate_act_streams(act, d)
+    if STATS.profile:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(torch.cuda.current_stream(act.device))
+        out = accumulate(astreams, wprep, d)
+        e1.record(torch.cuda.current_stream(act.device))
+        STATS.records.append(algorithmic_work(d) + (e0, e1))
+        return out
+    return accumulate(astreams, wprep, d)
 
 
 def sc_linear(act, weight, bit_length, z_unit=16, **kw):
@@ -73,6 +121,7 @@ def sc_linear(act, weight, bit_length, z_unit=16, **kw):
         check(_lib.lib().geo_sc_linear_forward(ctypes.byref(d), a.data_ptr(), w.data_ptr(), out.data_ptr(),
                                                ws.data_ptr(), ws.numel(), _stream_ptr(a.device)),
               "geo_sc_linear_forward")
+    STATS.launches += 3
     return out
 
 
@@ -85,6 +134,7 @@ def prepare_weights(weight, desc):
         buf = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
         check(_lib.lib().geo_sc_prepare_weights(ctypes.byref(desc), w.data_ptr(), buf.data_ptr(), nbytes,
                                                 _stream_ptr(w.device)), "geo_sc_prepare_weights")
+    STATS.launches += 1
     return buf
 
 
@@ -97,6 +147,7 @@ def generate_act_streams(act, desc):
         buf = torch.empty(nbytes, dtype=torch.uint8, device=a.device)
         check(_lib.lib().geo_sc_generate_act_streams(ctypes.byref(desc), a.data_ptr(), buf.data_ptr(), nbytes,
                                                      _stream_ptr(a.device)), "geo_sc_generate_act_streams")
+    STATS.launches += 1
     return buf
 
 
@@ -107,6 +158,7 @@ def accumulate(astreams, wprep, desc, out=None):
             out = torch.empty(out_shape(desc), dtype=torch.int32, device=astreams.device)
         check(_lib.lib().geo_sc_accumulate(ctypes.byref(desc), astreams.data_ptr(), wprep.data_ptr(), out.data_ptr(),
                                            _stream_ptr(astreams.device)), "geo_sc_accumulate")
+    STATS.launches += 1
     return out
 
 

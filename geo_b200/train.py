@@ -1,0 +1,56 @@
+"""One optimiser step of SC-CNN training, mirroring the loop body of the reference's
+``utils_own.forward`` (utils_own.py:57-114): scaled cross-entropy loss, backward through the
+guide, gradients copied to an fp32 master copy of the parameters, optimiser step on the master
+copy, parameters copied back and ``weight_org`` refreshed (clamped to [-1, 0.999])."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+SCALE_FACTOR = 128.0  # loss scale (utils_own.py:15,81)
+
+
+class TrainStep:
+    """Holds the model, the master parameter copy and the optimiser; ``__call__`` runs one step
+    on a device batch and returns the (scaled) loss tensor.
+
+    ``grad_hook`` is called with the list of parameters after backward and before the gradients
+    are copied to the master copy: the data-parallel wrapper all-reduces them there."""
+
+    def __init__(self, model, lr=2e-3, optim="SGD", grad_hook=None):
+        self.model = model
+        self.criterion = nn.CrossEntropyLoss()
+        self.param_copy = [p.clone().float().detach().requires_grad_(True) for p in model.parameters()]
+        if optim == "SGD":      # main_conv.py:216-217
+            self.optimizer = torch.optim.SGD(self.param_copy, lr=lr, weight_decay=0, momentum=0.01)
+        elif optim == "Adam":   # main_conv.py:212-213
+            self.optimizer = torch.optim.Adam(self.param_copy, lr=lr, weight_decay=0)
+        else:
+            raise ValueError(optim)
+        self.grad_hook = grad_hook
+        self.params = list(model.parameters())
+        self.sc_modules = [m for m in model.modules() if hasattr(m, "weight_org")]
+
+    def __call__(self, inputs, targets):
+        model = self.model
+        model.train()
+        output = model(inputs)
+        loss = self.criterion(output, targets) * SCALE_FACTOR
+        for p in self.params:
+            p.grad = None
+        loss.backward()
+        if self.grad_hook is not None:
+            self.grad_hook(self.params)
+        with torch.no_grad():
+            for m in self.sc_modules:
+                m.weight.data.copy_(m.weight_org)
+            for master, p in zip(self.param_copy, self.params):
+                if p.grad is not None:
+                    master.grad = p.grad.detach().to(torch.float32) / SCALE_FACTOR
+            self.optimizer.step()
+            for master, p in zip(self.param_copy, self.params):
+                p.data.copy_(master.data)
+            for m in self.sc_modules:
+                m.weight_org.copy_(m.weight.data.clamp(-1, 0.999))
+            self.optimizer.zero_grad(set_to_none=True)
+        return loss.detach(), output.detach()
