@@ -58,10 +58,13 @@ def lib():
     i32p = ctypes.POINTER(ctypes.c_int32)
     L.geo_sc_group_geometry.argtypes = [dp, i32p, i32p, i32p, i32p]
     L.geo_sc_host_stream.argtypes = [i32] * 7 + [vp]
+    L.geo_sc_guide_bytes.argtypes = [dp, szp, szp, szp]
+    L.geo_sc_guide_forward.argtypes = [dp, vp, vp, vp, sz, vp, sz, vp]
+    L.geo_sc_guide_backward.argtypes = [dp, vp, vp, sz, vp, vp, vp, vp, sz, vp]
     L.geo_sc_measure_lop3_peak.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
     for n in ("geo_sc_conv2d_forward", "geo_sc_linear_forward", "geo_sc_prepare_weights",
               "geo_sc_generate_act_streams", "geo_sc_accumulate", "geo_sc_group_geometry", "geo_sc_host_stream",
-              "geo_sc_measure_lop3_peak"):
+              "geo_sc_measure_lop3_peak", "geo_sc_guide_bytes", "geo_sc_guide_forward", "geo_sc_guide_backward"):
         getattr(L, n).restype = i32
     _lib = L
     return L

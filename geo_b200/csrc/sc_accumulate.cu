@@ -31,6 +31,7 @@ struct AccParams {
     int P, G, K;
     int img_words;        // P*C*Hp*Wp
     int pack_words;       // C*Hp*Wp
+    int splits;           // CTAs along grid.z sharing one output tile; > 1 => atomic accumulation
 };
 
 __device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr) {
@@ -58,7 +59,7 @@ struct Tile {
 };
 
 template <int NT, int NTHREADS>
-__global__ void __launch_bounds__(NTHREADS) accumulate_kernel(AccParams pr) {
+__global__ void __launch_bounds__(NTHREADS, 384 / NTHREADS) accumulate_kernel(AccParams pr) {
     using T = Tile<NT, NTHREADS>;
     constexpr int MT = T::MT, TX = T::TX;
     extern __shared__ __align__(16) uint32_t smem[];
@@ -90,10 +91,15 @@ __global__ void __launch_bounds__(NTHREADS) accumulate_kernel(AccParams pr) {
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
     const int chunks = (pr.K + KC - 1) / KC;
-    const int nstages = pr.P * pr.G * chunks;
+    // This CTA owns the (pack, group) pairs [pair0, pair1) of the P*G pairs; the sum over pairs is
+    // an integer sum, so splitting it over CTAs and adding atomically is exact and order-free.
+    const int pairs = pr.P * pr.G;
+    const int pair0 = (int)((long long)pairs * blockIdx.z / pr.splits);
+    const int pair1 = (int)((long long)pairs * (blockIdx.z + 1) / pr.splits);
+    const int nstages = (pair1 - pair0) * chunks;
 
     // stage cursor for the producer side
-    int ld_p = 0, ld_g = 0, ld_c = 0, ld_s = 0;
+    int ld_p = pair0 / pr.G, ld_g = pair0 % pr.G, ld_c = 0, ld_s = 0;
     auto issue_stage = [&]() {
         if (ld_s < nstages) {
             const int buf = ld_s % NSTAGE;
@@ -187,14 +193,18 @@ __global__ void __launch_bounds__(NTHREADS) accumulate_kernel(AccParams pr) {
 #pragma unroll
             for (int j = 0; j < TN; j++) {
                 const int o = o0 + ty * TN + j;
-                if (o < pr.O) pr.out[((size_t)b * pr.O + o) * pr.HoWo + rem] = osum[i][j];
+                if (o < pr.O) {
+                    int32_t *dst = pr.out + ((size_t)b * pr.O + o) * pr.HoWo + rem;
+                    if (pr.splits > 1) atomicAdd(dst, osum[i][j]);
+                    else *dst = osum[i][j];
+                }
             }
         }
     }
 }
 
 template <int NT, int NTHREADS>
-static int launch_tile(const Geometry &g, const AccParams &pr, cudaStream_t s) {
+static int launch_tile(const Geometry &g, AccParams pr, cudaStream_t s) {
     using T = Tile<NT, NTHREADS>;
     static bool configured[64] = {};
     int dev = 0;
@@ -204,7 +214,16 @@ static int launch_tile(const Geometry &g, const AccParams &pr, cudaStream_t s) {
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
         configured[dev] = true;
     }
-    dim3 grid((unsigned)((g.M + T::MT - 1) / T::MT), (unsigned)(g.Opad / NT));
+    dim3 grid((unsigned)((g.M + T::MT - 1) / T::MT), (unsigned)(g.Opad / NT), 1);
+    // Aim for several CTAs per SM so that the tail of the last wave is short.
+    const long long tiles = (long long)grid.x * grid.y, want = 148LL * 8;
+    long long splits = (want + tiles - 1) / tiles;
+    const long long pairs = (long long)g.P * g.G;
+    if (splits > pairs) splits = pairs;
+    if (splits < 1) splits = 1;
+    pr.splits = (int)splits;
+    grid.z = (unsigned)splits;
+    if (splits > 1) GEO_CUDA_CHECK(cudaMemsetAsync(pr.out, 0, (size_t)g.M * g.O * sizeof(int32_t), s));
     accumulate_kernel<NT, NTHREADS><<<grid, NTHREADS, T::SMEM, s>>>(pr);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
@@ -218,10 +237,11 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
     pr.P = g.P; pr.G = g.G; pr.K = g.K;
     pr.pack_words = g.C * g.Hp * g.Wp;
     pr.img_words = g.P * pr.pack_words;
+    pr.splits = 1;
     switch (g.NT) {
-    case 16: return launch_tile<16, 128>(g, pr, s);
-    case 32: return launch_tile<32, 256>(g, pr, s);
-    default: return launch_tile<64, 256>(g, pr, s);
+    case 16: return g.M <= 2048 ? launch_tile<16, 64>(g, pr, s) : launch_tile<16, 128>(g, pr, s);
+    case 32: return launch_tile<32, 128>(g, pr, s);
+    default: return launch_tile<64, 128>(g, pr, s);
     }
 }
 

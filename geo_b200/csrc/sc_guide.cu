@@ -1,0 +1,685 @@
+// Float "guide" of the SC convolution and its gradient (the straight-through backward used for
+// training).  Replaces, as native fp32 kernels, what the reference obtains from PyTorch autograd
+// over many small cuDNN convolutions (utils_functional.py:189-296 and :611-634):
+//
+//   w+ = clamp(w, 0, 100), w- = -clamp(w, -100, 0)
+//   y±_g[m][o] = sum_k a[m, k_g] * w±[g][k][o]                 (one plain conv per group g)
+//   out        = sum_g (1 - exp(-y+_g)) - sum_g (1 - exp(-y-_g))   (value replaced by the SC result)
+//   d out / d y+_g = exp(-y+_g) =: E+_g,   d out / d y-_g = -exp(-y-_g) =: -E-_g
+//   grad_w[o,c,ky,kx] = [w >= 0] * sum_m a * gout * E+_g  +  [w <= 0] * sum_m a * gout * E-_g
+//   grad_a[b,c,y,x]   = sum_{ky,kx,o} gout * (E+_g * w+ - E-_g * w-)   at output (y+ph-ky, x+pw-kx)
+//
+// (clamp passes the gradient on both branches at w == 0, hence the two inclusive masks.)
+//
+// Three register-tiled FFMA implicit-GEMM kernels, all fed through cp.async rings:
+//   guide_forward_kernel : E±_g = exp(-conv)            M = positions, N = 2*c_out, K = members
+//   guide_wgrad_kernel   : sum_m a * D                  M = members,   N = 2*c_out, K = positions (split)
+//   guide_dgrad_kernel   : conv of D with flipped w     M = input pixels, N = c_in block, K = ky*kx*2*c_out
+// with D = gout * E written in place over E by an element-wise kernel in between.
+// E / D layout: [group][polarity][c_out_padded][position], position = (b*Ho + oy)*Wo + ox.
+#include "sc_common.h"
+
+namespace geo {
+
+namespace {
+
+__device__ __forceinline__ void cp4(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 4 : 0;  // src-size 0: the 4 destination bytes are zero-filled
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// Decodes (group, member) into filter coordinates; returns false for zero-filled members
+// (channels past c_in in the last yz group).
+__host__ __device__ inline bool decode_member(int mode, int z, int C, int K2, int K3, int g, int k, int *c, int *ky,
+                                              int *kx) {
+    switch (mode) {
+    case GEO_SC_MODE_1D: *kx = g; *c = k / K2; *ky = k % K2; break;
+    case GEO_SC_MODE_Z: *c = g; *ky = k / K3; *kx = k % K3; break;
+    case GEO_SC_MODE_YZ: *kx = g % K3; *c = (g / K3) * z + k / K2; *ky = k % K2; break;
+    default: *c = k / (K2 * K3); *ky = (k / K3) % K2; *kx = k % K3; break;
+    }
+    return *c < C;
+}
+
+struct GuideDims {
+    int B, C, H, W, ph, pw, Hp, Wp, O, K2, K3, Ho, Wo, HoWo;
+    int mode, z, G, K, Opad, N2, M;
+    int cb, J, cbpad;   // dgrad: channels per block sharing one set of D planes, blocks, padded width
+    int Min;            // input pixels B*H*W
+};
+
+GuideDims guide_dims(const Geometry &g) {
+    GuideDims d;
+    d.B = g.B; d.C = g.C; d.H = g.H; d.W = g.W; d.ph = g.pad_h; d.pw = g.pad_w; d.Hp = g.Hp; d.Wp = g.Wp;
+    d.O = g.O; d.K2 = g.K2; d.K3 = g.K3; d.Ho = g.Ho; d.Wo = g.Wo; d.HoWo = g.Ho * g.Wo;
+    d.mode = g.mode; d.z = g.z; d.G = g.G; d.K = g.K; d.Opad = g.Opad; d.N2 = 2 * g.Opad; d.M = (int)g.M;
+    switch (g.mode) {
+    case GEO_SC_MODE_Z: d.cb = 1; d.J = g.C; break;
+    case GEO_SC_MODE_YZ: d.cb = g.z; d.J = (g.C + g.z - 1) / g.z; break;
+    default: d.cb = g.C; d.J = 1; break;
+    }
+    d.cbpad = d.cb <= 8 ? 8 : (d.cb <= 16 ? 16 : (d.cb <= 32 ? 32 : (d.cb + 63) / 64 * 64));
+    d.Min = g.B * g.H * g.W;
+    return d;
+}
+
+// ---- preparation: padded activations, split weights, tables --------------------------------
+__global__ void __launch_bounds__(256) pad_act_kernel(GuideDims d, const float *__restrict__ act,
+                                                      float *__restrict__ apad) {
+    const long long total = (long long)d.B * d.C * d.Hp * d.Wp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int x = (int)(i % d.Wp), y = (int)((i / d.Wp) % d.Hp);
+        const long long bc = i / ((long long)d.Wp * d.Hp);
+        const int yi = y - d.ph, xi = x - d.pw;
+        apad[i] = (yi >= 0 && yi < d.H && xi >= 0 && xi < d.W) ? act[(bc * d.H + yi) * d.W + xi] : 0.0f;
+    }
+}
+
+// Wf[g][k][Opad][2] = (w+, w-) and aoff[g][k] = offset of the member inside a padded image.
+__global__ void __launch_bounds__(256) guide_prep_fwd_kernel(GuideDims d, const float *__restrict__ w,
+                                                             float *__restrict__ wf, int *__restrict__ aoff) {
+    const long long total = (long long)d.G * d.K * d.Opad;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int o = (int)(i % d.Opad);
+        const int gk = (int)(i / d.Opad), k = gk % d.K, g = gk / d.K;
+        int c, ky, kx;
+        const bool valid = decode_member(d.mode, d.z, d.C, d.K2, d.K3, g, k, &c, &ky, &kx);
+        if (o == 0) aoff[gk] = valid ? (c * d.Hp + ky) * d.Wp + kx : 0;
+        float v = 0.0f;
+        if (valid && o < d.O) v = w[(((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx];
+        float2 r;
+        r.x = fminf(fmaxf(v, 0.0f), 100.0f);
+        r.y = -fminf(fmaxf(v, -100.0f), 0.0f);
+        *(float2 *)(wf + (size_t)i * 2) = r;
+    }
+}
+
+// Wd[j][(ky*K3+kx)*N2 + pol*Opad + o][cbpad] = w+ (pol 0) or -(w-) (pol 1) of channel j*cb+cc.
+__global__ void __launch_bounds__(256) guide_prep_dgrad_kernel(GuideDims d, const float *__restrict__ w,
+                                                               float *__restrict__ wd) {
+    const int R = d.K2 * d.K3 * d.N2;
+    const long long total = (long long)d.J * R * d.cbpad;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int cc = (int)(i % d.cbpad);
+        const int r = (int)((i / d.cbpad) % R), j = (int)(i / ((long long)d.cbpad * R));
+        const int n2 = r % d.N2, kk = r / d.N2, ky = kk / d.K3, kx = kk % d.K3;
+        const int pol = n2 / d.Opad, o = n2 % d.Opad, c = j * d.cb + cc;
+        float v = 0.0f;
+        if (cc < d.cb && c < d.C && o < d.O) {
+            const float x = w[(((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx];
+            v = pol == 0 ? fminf(fmaxf(x, 0.0f), 100.0f) : fminf(fmaxf(x, -100.0f), 0.0f);
+        }
+        wd[i] = v;
+    }
+}
+
+// ---- forward: E±_g = exp(-conv_g) -------------------------------------------------------------
+constexpr int FKC = 16, FSTAGE = 3;
+
+struct FwdParams {
+    const float *apad;  // [B][C][Hp][Wp]
+    const float *wf;    // [G][K][Opad][2]
+    const int *aoff;    // [G][K]
+    float *E;           // [G][2][Opad][M]
+    int M, Opad, HoWo, Wo, Wp, K, img;
+};
+
+template <int NT, int NTHREADS>
+__global__ void __launch_bounds__(NTHREADS) guide_forward_kernel(FwdParams pr) {
+    constexpr int TY = NT / 4, TX = NTHREADS / TY, MT = TX * 8;
+    constexpr int A_F = FKC * MT, W_F = FKC * NT * 2, ST_F = A_F + W_F;
+    extern __shared__ __align__(16) float fsm[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    constexpr int WX = TX / 8;
+    const int tx = (warp % WX) * 8 + (lane & 7), ty = (warp / WX) * 4 + (lane >> 3);
+    const int m0 = blockIdx.x * MT, o0 = blockIdx.y * NT, g = blockIdx.z;
+
+    constexpr int MPT = MT > NTHREADS ? MT / NTHREADS : 1;
+    constexpr int RSTEP = NTHREADS > MT ? NTHREADS / MT : 1;
+    const int r0 = NTHREADS > MT ? t / MT : 0;
+    int abase[MPT];
+#pragma unroll
+    for (int j = 0; j < MPT; j++) {
+        int m = m0 + (t % MT) + j * NTHREADS;
+        if (m >= pr.M) m = pr.M - 1;
+        const int b = m / pr.HoWo, rem = m % pr.HoWo;
+        abase[j] = b * pr.img + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+    }
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(fsm);
+    const int chunks = (pr.K + FKC - 1) / FKC;
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < chunks) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % FSTAGE) * ST_F * 4, w_s = a_s + A_F * 4;
+            const int k0 = ld * FKC, rows = min(FKC, pr.K - k0);
+            const int *ao = pr.aoff + g * pr.K + k0;
+#pragma unroll
+            for (int j = 0; j < MPT; j++) {
+                const int mcol = (t % MT) + j * NTHREADS;
+                for (int r = r0; r < rows; r += RSTEP)
+                    cp4(a_s + (uint32_t)(r * MT + mcol) * 4, pr.apad + abase[j] + __ldg(ao + r), true);
+            }
+            constexpr int CPR = NT / 2;
+            const float *wsrc = pr.wf + ((size_t)(g * pr.K + k0) * pr.Opad + o0) * 2;
+            for (int i = t; i < rows * CPR; i += NTHREADS) {
+                const int r = i / CPR, ch = i % CPR;
+                cp16(w_s + (uint32_t)(r * NT * 2 + ch * 4) * 4, wsrc + (size_t)r * pr.Opad * 2 + ch * 4, true);
+            }
+            ld++;
+        }
+        cp_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < FSTAGE - 1; s++) issue();
+
+    float accp[8][4], accn[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) { accp[i][j] = 0.f; accn[i][j] = 0.f; }
+
+    for (int s = 0; s < chunks; s++) {
+        cp_wait<FSTAGE - 2>();
+        __syncthreads();
+        issue();
+        const float *a_s = fsm + (size_t)(s % FSTAGE) * ST_F, *w_s = a_s + A_F;
+        const int rows = min(FKC, pr.K - s * FKC);
+        const float4 *a4 = (const float4 *)a_s + tx, *w4 = (const float4 *)w_s + ty * 2;
+#pragma unroll 4
+        for (int r = 0; r < rows; r++) {
+            const float4 al = a4[r * (MT / 4)], ah = a4[r * (MT / 4) + MT / 8];
+            const float4 wa = w4[r * (NT / 2)], wb = w4[r * (NT / 2) + 1];
+            const float a[8] = {al.x, al.y, al.z, al.w, ah.x, ah.y, ah.z, ah.w};
+            const float wp[4] = {wa.x, wa.z, wb.x, wb.z}, wn[4] = {wa.y, wa.w, wb.y, wb.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    accp[i][j] = fmaf(a[i], wp[j], accp[i][j]);
+                    accn[i][j] = fmaf(a[i], wn[j], accn[i][j]);
+                }
+        }
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int o = o0 + ty * 4 + j;
+        float *ep = pr.E + ((size_t)(g * 2 + 0) * pr.Opad + o) * pr.M;
+        float *en = pr.E + ((size_t)(g * 2 + 1) * pr.Opad + o) * pr.M;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int m = m0 + (i < 4 ? tx * 4 + i : MT / 2 + tx * 4 + (i - 4));
+            if (m < pr.M) {
+                ep[m] = expf(-accp[i][j]);
+                en[m] = expf(-accn[i][j]);
+            }
+        }
+    }
+}
+
+// ---- D = gout * E in place ------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) guide_make_d_kernel(GuideDims d, const float *__restrict__ gout,
+                                                           float *__restrict__ E) {
+    const long long total = (long long)d.G * d.N2 * d.M;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i % d.M);
+        const int o = (int)((i / d.M) % d.Opad);
+        float v = 0.0f;
+        if (o < d.O) {
+            const int b = m / d.HoWo, rem = m % d.HoWo;
+            v = E[i] * gout[((size_t)b * d.O + o) * d.HoWo + rem];
+        }
+        E[i] = v;
+    }
+}
+
+// ---- wgrad: partial[slice][g][k][n2] = sum_{m in slice} a[m, k_g] * D[g][n2][m] -----------------------
+constexpr int WMC = 32, WRS = WMC + 4, WSTAGE = 3, WNT = 64;
+
+struct WgradParams {
+    const float *apad;
+    const float *D;     // [G][N2][M]
+    const int *aoff;    // [G][K]
+    float *partial;     // [S][G][K][N2]
+    int M, N2, HoWo, Wo, Wp, K, G, img;
+    int slice_len;      // positions per slice, multiple of WMC
+};
+
+template <int KT>
+__global__ void __launch_bounds__(KT) guide_wgrad_kernel(WgradParams pr) {
+    constexpr int NTHREADS = KT;           // (KT/8) member-threads x 8 channel-threads
+    constexpr int KTH = KT / 8;
+    constexpr int A_F = KT * WRS, D_F = WNT * WRS, ST_F = A_F + D_F;
+    extern __shared__ __align__(16) float wsm[];
+    const int t = threadIdx.x;
+    const int kth = t % KTH, nth = t / KTH;
+    const int g = blockIdx.z / ((pr.N2 + WNT - 1) / WNT), nt = blockIdx.z % ((pr.N2 + WNT - 1) / WNT);
+    const int k0 = blockIdx.y * KT, n0 = nt * WNT;
+    const int mbeg = blockIdx.x * pr.slice_len, mend = min(pr.M, mbeg + pr.slice_len);
+    const int chunks = (mend - mbeg + WMC - 1) / WMC;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(wsm);
+    const bool vec = (pr.M & 3) == 0;
+
+    // gather assignment for A: column m = t % WMC, rows t / WMC + i * (NTHREADS / WMC)
+    const int am = t % WMC, ar0 = t / WMC;
+    constexpr int ARS = NTHREADS / WMC > 0 ? NTHREADS / WMC : 1;
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < chunks) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % WSTAGE) * ST_F * 4, d_s = a_s + A_F * 4;
+            const int mc = mbeg + ld * WMC;
+            {
+                const int m = mc + am;
+                const bool mv = m < mend;
+                const int mm = mv ? m : mbeg;
+                const int b = mm / pr.HoWo, rem = mm % pr.HoWo;
+                const float *src = pr.apad + b * pr.img + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+                const int *ao = pr.aoff + g * pr.K;
+                for (int r = ar0; r < KT; r += ARS) {
+                    const int k = k0 + r;
+                    const bool v = mv && k < pr.K;
+                    cp4(a_s + (uint32_t)(r * WRS + am) * 4, src + (v ? __ldg(ao + k) : 0), v);
+                }
+            }
+            if (vec) {
+                for (int i = t; i < WNT * (WMC / 4); i += NTHREADS) {
+                    const int r = i / (WMC / 4), c4 = i % (WMC / 4);
+                    const int n = n0 + r, m = mc + c4 * 4;
+                    const bool v = n < pr.N2 && m < mend;  // M % 4 == 0 and slices are multiples of 4
+                    const float *src = pr.D + ((size_t)(g * pr.N2 + (v ? n : 0))) * pr.M + (v ? m : 0);
+                    cp16(d_s + (uint32_t)(r * WRS + c4 * 4) * 4, src, v);
+                }
+            } else {
+                for (int i = t; i < WNT * WMC; i += NTHREADS) {
+                    const int r = i / WMC, c = i % WMC;
+                    const int n = n0 + r, m = mc + c;
+                    const bool v = n < pr.N2 && m < mend;
+                    const float *src = pr.D + ((size_t)(g * pr.N2 + (v ? n : 0))) * pr.M + (v ? m : 0);
+                    cp4(d_s + (uint32_t)(r * WRS + c) * 4, src, v);
+                }
+            }
+            ld++;
+        }
+        cp_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < WSTAGE - 1; s++) issue();
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+
+    for (int s = 0; s < chunks; s++) {
+        cp_wait<WSTAGE - 2>();
+        __syncthreads();
+        issue();
+        const float *a_s = wsm + (size_t)(s % WSTAGE) * ST_F, *d_s = a_s + A_F;
+#pragma unroll 2
+        for (int m4 = 0; m4 < WMC; m4 += 4) {
+            float4 av[8], dv[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) av[i] = *(const float4 *)(a_s + (kth + KTH * i) * WRS + m4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) dv[j] = *(const float4 *)(d_s + (nth + 8 * j) * WRS + m4);
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    acc[i][j] = fmaf(av[i].x, dv[j].x, acc[i][j]);
+                    acc[i][j] = fmaf(av[i].y, dv[j].y, acc[i][j]);
+                    acc[i][j] = fmaf(av[i].z, dv[j].z, acc[i][j]);
+                    acc[i][j] = fmaf(av[i].w, dv[j].w, acc[i][j]);
+                }
+        }
+    }
+    cp_wait<0>();
+    float *dst = pr.partial + ((size_t)blockIdx.x * pr.G + g) * pr.K * pr.N2;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int k = k0 + kth + KTH * i;
+        if (k < pr.K) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int n = n0 + nth + 8 * j;
+                if (n < pr.N2) dst[(size_t)k * pr.N2 + n] = acc[i][j];
+            }
+        }
+    }
+}
+
+// grad_w[o][c][ky][kx] = [w>=0] * sum_s partial[s][g][k][o] + [w<=0] * sum_s partial[s][g][k][Opad+o]
+__global__ void __launch_bounds__(256) guide_wgrad_reduce_kernel(GuideDims d, int S, const float *__restrict__ partial,
+                                                                 const float *__restrict__ w, float *__restrict__ gw) {
+    const long long total = (long long)d.G * d.K * d.O;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int o = (int)(i % d.O);
+        const int gk = (int)(i / d.O), k = gk % d.K, g = gk / d.K;
+        int c, ky, kx;
+        if (!decode_member(d.mode, d.z, d.C, d.K2, d.K3, g, k, &c, &ky, &kx)) continue;
+        float sp = 0.f, sn = 0.f;
+        const size_t stride = (size_t)d.G * d.K * d.N2;
+        const float *p = partial + ((size_t)g * d.K + k) * d.N2;
+        for (int s = 0; s < S; s++) {
+            sp += p[s * stride + o];
+            sn += p[s * stride + d.Opad + o];
+        }
+        const size_t wi = (((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx;
+        const float wv = w[wi];
+        gw[wi] = (wv >= 0.f && wv <= 100.f ? sp : 0.f) + (wv <= 0.f && wv >= -100.f ? sn : 0.f);
+    }
+}
+
+// ---- dgrad: grad_a[b][c][y][x] = sum_{ky,kx,n2} D[g][n2][b, y+ph-ky, x+pw-kx] * Wd[j][(ky,kx,n2)][c] -----
+constexpr int DKC = 16, DSTAGE = 3;
+
+struct DgradParams {
+    const float *D;    // [G][N2][M]
+    const float *wd;   // [J][R][cbpad]
+    float *ga;         // [B][C][H][W]
+    int M, N2, Ho, Wo, H, W, C, ph, pw, K2, K3, mode, cb, cbpad, Min, R;
+};
+
+template <int NT, int NTHREADS>
+__global__ void __launch_bounds__(NTHREADS) guide_dgrad_kernel(DgradParams pr) {
+    constexpr int TY = NT / 8, TX = NTHREADS / TY, MT = TX * 8;   // thread tile: 8 pixels x 8 channels
+    constexpr int A_F = DKC * MT, W_F = DKC * NT, ST_F = A_F + W_F;
+    static_assert(MT % NTHREADS == 0, "each thread gathers MT/NTHREADS pixel columns");
+    constexpr int MPT = MT / NTHREADS;
+    extern __shared__ __align__(16) float dsm[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    int tx, ty;
+    if constexpr (TY >= 4) {  // warps of 8 pixel columns x 4 channel rows
+        constexpr int WX = TX / 8;
+        tx = (warp % WX) * 8 + (lane & 7);
+        ty = (warp / WX) * 4 + (lane >> 3);
+    } else {
+        tx = t % TX;
+        ty = t / TX;
+    }
+    const int m0 = blockIdx.x * MT, c0 = blockIdx.y * NT, j = blockIdx.z;
+    const int HoWo = pr.Ho * pr.Wo, HW = pr.H * pr.W;
+
+    int pb[MPT], py[MPT], px[MPT];
+#pragma unroll
+    for (int q = 0; q < MPT; q++) {
+        int m = m0 + t + q * NTHREADS;
+        const bool v = m < pr.Min;
+        if (!v) m = 0;
+        const int b = m / HW, rem = m % HW;
+        pb[q] = v ? b * HoWo : -1;
+        py[q] = rem / pr.W + pr.ph;
+        px[q] = rem % pr.W + pr.pw;
+    }
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dsm);
+    const int chunks = pr.R / DKC;   // R = K2*K3*N2 and N2 is a multiple of 32
+    const int cpk = pr.N2 / DKC;     // chunks per (ky,kx)
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < chunks) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % DSTAGE) * ST_F * 4, w_s = a_s + A_F * 4;
+            const int kk = ld / cpk, n2 = (ld % cpk) * DKC;
+            const int ky = kk / pr.K3, kx = kk % pr.K3;
+            int g;
+            switch (pr.mode) {
+            case GEO_SC_MODE_1D: g = kx; break;
+            case GEO_SC_MODE_Z: g = j; break;
+            case GEO_SC_MODE_YZ: g = j * pr.K3 + kx; break;
+            default: g = 0; break;
+            }
+            const float *plane = pr.D + (size_t)(g * pr.N2 + n2) * pr.M;
+#pragma unroll
+            for (int q = 0; q < MPT; q++) {
+                const int oy = py[q] - ky, ox = px[q] - kx;
+                const bool v = pb[q] >= 0 && oy >= 0 && oy < pr.Ho && ox >= 0 && ox < pr.Wo;
+                const float *src = plane + (v ? pb[q] + oy * pr.Wo + ox : 0);
+                const uint32_t dst = a_s + (uint32_t)(t + q * NTHREADS) * 4;
+#pragma unroll
+                for (int r = 0; r < DKC; r++) cp4(dst + (uint32_t)(r * MT) * 4, src + (size_t)r * pr.M, v);
+            }
+            const float *wsrc = pr.wd + ((size_t)j * pr.R + (size_t)ld * DKC) * pr.cbpad + c0;
+            constexpr int CPR = NT / 4;
+            for (int i = t; i < DKC * CPR; i += NTHREADS) {
+                const int r = i / CPR, ch = i % CPR;
+                cp16(w_s + (uint32_t)(r * NT + ch * 4) * 4, wsrc + (size_t)r * pr.cbpad + ch * 4, true);
+            }
+            ld++;
+        }
+        cp_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < DSTAGE - 1; s++) issue();
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) acc[i][q] = 0.f;
+
+    for (int s = 0; s < chunks; s++) {
+        cp_wait<DSTAGE - 2>();
+        __syncthreads();
+        issue();
+        const float *a_s = dsm + (size_t)(s % DSTAGE) * ST_F, *w_s = a_s + A_F;
+        const float4 *a4 = (const float4 *)a_s + tx, *w4 = (const float4 *)w_s + ty * 2;
+#pragma unroll 4
+        for (int r = 0; r < DKC; r++) {
+            const float4 al = a4[r * (MT / 4)], ah = a4[r * (MT / 4) + MT / 8];
+            const float4 wa = w4[r * (NT / 4)], wb = w4[r * (NT / 4) + 1];
+            const float a[8] = {al.x, al.y, al.z, al.w, ah.x, ah.y, ah.z, ah.w};
+            const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int q = 0; q < 8; q++) acc[i][q] = fmaf(a[i], wv[q], acc[i][q]);
+        }
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? tx * 4 + i : MT / 2 + tx * 4 + (i - 4));
+        if (m < pr.Min) {
+            const int b = m / HW, rem = m % HW;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int cc = c0 + ty * 8 + q;
+                const int c = j * pr.cb + cc;
+                if (cc < pr.cb && c < pr.C) pr.ga[((size_t)b * pr.C + c) * HW + rem] = acc[i][q];
+            }
+        }
+    }
+}
+
+int grid1d(long long total) {
+    long long blocks = (total + 255) / 256;
+    return (int)(blocks < 148 * 16 ? (blocks > 0 ? blocks : 1) : 148 * 16);
+}
+
+// ---- buffer plans -----------------------------------------------------------------------------------
+struct GuidePlan {
+    size_t e_bytes, apad_bytes, aoff_bytes;  // saved: E | apad | aoff
+    size_t wf_bytes;                         // forward scratch
+    size_t wd_bytes, partial_bytes;          // backward scratch
+    int S, slice_len, KT;
+};
+
+GuidePlan guide_plan(const GuideDims &d) {
+    GuidePlan p;
+    p.e_bytes = align_up((size_t)d.G * d.N2 * d.M * 4, 256);
+    p.apad_bytes = align_up((size_t)d.B * d.C * d.Hp * d.Wp * 4, 256);
+    p.aoff_bytes = align_up((size_t)d.G * d.K * 4, 256);
+    p.wf_bytes = align_up((size_t)d.G * d.K * d.Opad * 2 * 4, 256);
+    p.wd_bytes = align_up((size_t)d.J * d.K2 * d.K3 * d.N2 * d.cbpad * 4, 256);
+    p.KT = d.K >= 96 ? 128 : (d.K > 32 ? 64 : 32);
+    const long long tiles = (long long)d.G * ((d.K + p.KT - 1) / p.KT) * ((d.N2 + WNT - 1) / WNT);
+    long long S = (148LL * 6 + tiles - 1) / tiles;
+    const long long maxS = (d.M + WMC - 1) / WMC;
+    if (S > maxS) S = maxS;
+    if (S < 1) S = 1;
+    long long len = (d.M + S - 1) / S;
+    len = (len + WMC - 1) / WMC * WMC;
+    p.slice_len = (int)len;
+    p.S = (int)((d.M + len - 1) / len);
+    p.partial_bytes = align_up((size_t)p.S * d.G * d.K * d.N2 * 4, 256);
+    return p;
+}
+
+template <typename Kern>
+int set_smem(Kern kern, size_t bytes) {
+    GEO_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return GEO_SC_OK;
+}
+
+template <int NT, int NTHREADS>
+int launch_guide_fwd(const GuideDims &d, const FwdParams &pr, cudaStream_t s) {
+    constexpr int TY = NT / 4, TX = NTHREADS / TY, MT = TX * 8;
+    constexpr size_t smem = (size_t)FSTAGE * (FKC * MT + FKC * NT * 2) * 4;
+    int rc = set_smem(guide_forward_kernel<NT, NTHREADS>, smem);
+    if (rc) return rc;
+    dim3 grid((d.M + MT - 1) / MT, d.Opad / NT, d.G);
+    guide_forward_kernel<NT, NTHREADS><<<grid, NTHREADS, smem, s>>>(pr);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+template <int KT>
+int launch_guide_wgrad(const GuideDims &d, const GuidePlan &p, const WgradParams &pr, cudaStream_t s) {
+    constexpr size_t smem = (size_t)WSTAGE * (KT * WRS + WNT * WRS) * 4;
+    int rc = set_smem(guide_wgrad_kernel<KT>, smem);
+    if (rc) return rc;
+    dim3 grid(p.S, (d.K + KT - 1) / KT, d.G * ((d.N2 + WNT - 1) / WNT));
+    guide_wgrad_kernel<KT><<<grid, KT, smem, s>>>(pr);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+template <int NT, int NTHREADS>
+int launch_guide_dgrad(const GuideDims &d, const DgradParams &pr, cudaStream_t s) {
+    constexpr int TY = NT / 8, TX = NTHREADS / TY, MT = TX * 8;
+    constexpr size_t smem = (size_t)DSTAGE * (DKC * MT + DKC * NT) * 4;
+    int rc = set_smem(guide_dgrad_kernel<NT, NTHREADS>, smem);
+    if (rc) return rc;
+    dim3 grid((d.Min + MT - 1) / MT, d.cbpad / NT, d.J);
+    guide_dgrad_kernel<NT, NTHREADS><<<grid, NTHREADS, smem, s>>>(pr);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+}  // namespace
+
+}  // namespace geo
+
+using namespace geo;
+
+extern "C" {
+
+int geo_sc_guide_bytes(const geo_sc_conv_desc *desc, size_t *saved_bytes, size_t *forward_scratch_bytes,
+                       size_t *backward_scratch_bytes) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    const GuideDims d = guide_dims(g);
+    if ((long long)d.G * d.N2 * d.M > (1LL << 31) - 1 || (long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad > (1LL << 31) - 1)
+        return fail(GEO_SC_ERR_TOO_LARGE, "guide tensors exceed 31-bit indexing (groups %d x channels %d x positions %d)",
+                    d.G, d.N2, d.M);
+    const GuidePlan p = guide_plan(d);
+    if (saved_bytes) *saved_bytes = p.e_bytes + p.apad_bytes + p.aoff_bytes;
+    if (forward_scratch_bytes) *forward_scratch_bytes = p.wf_bytes;
+    if (backward_scratch_bytes) *backward_scratch_bytes = p.wd_bytes + p.partial_bytes;
+    return GEO_SC_OK;
+}
+
+int geo_sc_guide_forward(const geo_sc_conv_desc *desc, const float *act, const float *weight, void *saved,
+                         size_t saved_bytes, void *scratch, size_t scratch_bytes, void *stream) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!act || !weight || !saved || !scratch) return fail(GEO_SC_ERR_NULL, "act, weight, saved or scratch is NULL");
+    const GuideDims d = guide_dims(g);
+    const GuidePlan p = guide_plan(d);
+    if (saved_bytes < p.e_bytes + p.apad_bytes + p.aoff_bytes || scratch_bytes < p.wf_bytes ||
+        ((uintptr_t)saved & 255) || ((uintptr_t)scratch & 255))
+        return fail(GEO_SC_ERR_WORKSPACE, "guide buffers too small or not 256-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    float *E = (float *)saved;
+    float *apad = (float *)((char *)saved + p.e_bytes);
+    int *aoff = (int *)((char *)saved + p.e_bytes + p.apad_bytes);
+    float *wf = (float *)scratch;
+    pad_act_kernel<<<grid1d((long long)d.B * d.C * d.Hp * d.Wp), 256, 0, s>>>(d, act, apad);
+    guide_prep_fwd_kernel<<<grid1d((long long)d.G * d.K * d.Opad), 256, 0, s>>>(d, weight, wf, aoff);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    FwdParams pr;
+    pr.apad = apad; pr.wf = wf; pr.aoff = aoff; pr.E = E;
+    pr.M = d.M; pr.Opad = d.Opad; pr.HoWo = d.HoWo; pr.Wo = d.Wo; pr.Wp = d.Wp; pr.K = d.K;
+    pr.img = d.C * d.Hp * d.Wp;
+    switch (g.NT) {
+    case 16: return launch_guide_fwd<16, 128>(d, pr, s);
+    case 32: return launch_guide_fwd<32, 256>(d, pr, s);
+    default: return launch_guide_fwd<64, 256>(d, pr, s);
+    }
+}
+
+int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *weight, void *saved, size_t saved_bytes,
+                          const float *grad_out, float *grad_act, float *grad_weight, void *scratch,
+                          size_t scratch_bytes, void *stream) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!weight || !saved || !grad_out || !scratch) return fail(GEO_SC_ERR_NULL, "weight, saved, grad_out or scratch is NULL");
+    const GuideDims d = guide_dims(g);
+    const GuidePlan p = guide_plan(d);
+    if (saved_bytes < p.e_bytes + p.apad_bytes + p.aoff_bytes || scratch_bytes < p.wd_bytes + p.partial_bytes ||
+        ((uintptr_t)saved & 255) || ((uintptr_t)scratch & 255))
+        return fail(GEO_SC_ERR_WORKSPACE, "guide buffers too small or not 256-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    float *E = (float *)saved;
+    const float *apad = (const float *)((char *)saved + p.e_bytes);
+    const int *aoff = (const int *)((char *)saved + p.e_bytes + p.apad_bytes);
+    float *wd = (float *)scratch;
+    float *partial = (float *)((char *)scratch + p.wd_bytes);
+
+    guide_make_d_kernel<<<grid1d((long long)d.G * d.N2 * d.M), 256, 0, s>>>(d, grad_out, E);
+    GEO_CUDA_CHECK(cudaGetLastError());
+
+    if (grad_weight) {
+        WgradParams pr;
+        pr.apad = apad; pr.D = E; pr.aoff = aoff; pr.partial = partial;
+        pr.M = d.M; pr.N2 = d.N2; pr.HoWo = d.HoWo; pr.Wo = d.Wo; pr.Wp = d.Wp; pr.K = d.K; pr.G = d.G;
+        pr.img = d.C * d.Hp * d.Wp; pr.slice_len = p.slice_len;
+        switch (p.KT) {
+        case 32: rc = launch_guide_wgrad<32>(d, p, pr, s); break;
+        case 64: rc = launch_guide_wgrad<64>(d, p, pr, s); break;
+        default: rc = launch_guide_wgrad<128>(d, p, pr, s); break;
+        }
+        if (rc) return rc;
+        guide_wgrad_reduce_kernel<<<grid1d((long long)d.G * d.K * d.O), 256, 0, s>>>(d, p.S, partial, weight, grad_weight);
+        GEO_CUDA_CHECK(cudaGetLastError());
+    }
+    if (grad_act) {
+        guide_prep_dgrad_kernel<<<grid1d((long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad), 256, 0, s>>>(d, weight, wd);
+        GEO_CUDA_CHECK(cudaGetLastError());
+        DgradParams pr;
+        pr.D = E; pr.wd = wd; pr.ga = grad_act;
+        pr.M = d.M; pr.N2 = d.N2; pr.Ho = d.Ho; pr.Wo = d.Wo; pr.H = d.H; pr.W = d.W; pr.C = d.C; pr.ph = d.ph; pr.pw = d.pw;
+        pr.K2 = d.K2; pr.K3 = d.K3; pr.mode = d.mode; pr.cb = d.cb; pr.cbpad = d.cbpad; pr.Min = d.Min;
+        pr.R = d.K2 * d.K3 * d.N2;
+        if (d.cbpad == 8) rc = launch_guide_dgrad<8, 64>(d, pr, s);
+        else if (d.cbpad == 16) rc = launch_guide_dgrad<16, 128>(d, pr, s);
+        else if (d.cbpad == 32) rc = launch_guide_dgrad<32, 128>(d, pr, s);
+        else rc = launch_guide_dgrad<64, 256>(d, pr, s);
+        if (rc) return rc;
+    }
+    return GEO_SC_OK;
+}
+
+}  // extern "C"

@@ -162,6 +162,53 @@ def accumulate(astreams, wprep, desc, out=None):
     return out
 
 
+def guide_bytes(desc):
+    """(saved, forward scratch, backward scratch) buffer sizes of the guide kernels."""
+    a, b, c = ctypes.c_size_t(0), ctypes.c_size_t(0), ctypes.c_size_t(0)
+    check(_lib.lib().geo_sc_guide_bytes(ctypes.byref(desc), ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)),
+          "geo_sc_guide_bytes")
+    return a.value, b.value, c.value
+
+
+def guide_forward(act, weight, desc):
+    """exp(-y) of every group of the float guide, as the opaque `saved` buffer for guide_backward."""
+    _require_cuda(act, weight)
+    a = act.detach().to(torch.float32).contiguous()
+    w = weight.detach().to(torch.float32).contiguous()
+    nsaved, nfwd, _ = guide_bytes(desc)
+    with torch.cuda.device(a.device):
+        saved = torch.empty(nsaved, dtype=torch.uint8, device=a.device)
+        scratch = torch.empty(max(nfwd, 256), dtype=torch.uint8, device=a.device)
+        check(_lib.lib().geo_sc_guide_forward(ctypes.byref(desc), a.data_ptr(), w.data_ptr(), saved.data_ptr(),
+                                              saved.numel(), scratch.data_ptr(), scratch.numel(),
+                                              _stream_ptr(a.device)), "geo_sc_guide_forward")
+    STATS.launches += 3
+    return saved
+
+
+def guide_backward(weight, saved, grad_out, desc, need_act=True, need_weight=True):
+    """(grad_act or None, grad_weight or None); consumes ``saved``."""
+    _require_cuda(weight, saved, grad_out)
+    w = weight.detach().to(torch.float32).contiguous()
+    go = grad_out.detach().to(torch.float32).contiguous()
+    if tuple(go.shape) != out_shape(desc):
+        raise ValueError(f"grad_out has shape {tuple(go.shape)}, expected {out_shape(desc)}")
+    _, _, nbwd = guide_bytes(desc)
+    dev = w.device
+    with torch.cuda.device(dev):
+        scratch = torch.empty(max(nbwd, 256), dtype=torch.uint8, device=dev)
+        ga = torch.empty((desc.batch, desc.c_in, desc.h_in, desc.w_in), dtype=torch.float32, device=dev) \
+            if need_act else None
+        gw = torch.empty((desc.c_out, desc.c_in, desc.k_h, desc.k_w), dtype=torch.float32, device=dev) \
+            if need_weight else None
+        check(_lib.lib().geo_sc_guide_backward(ctypes.byref(desc), w.data_ptr(), saved.data_ptr(), saved.numel(),
+                                               go.data_ptr(), ga.data_ptr() if need_act else None,
+                                               gw.data_ptr() if need_weight else None, scratch.data_ptr(),
+                                               scratch.numel(), _stream_ptr(dev)), "geo_sc_guide_backward")
+    STATS.launches += 1 + (2 if need_weight else 0) + (2 if need_act else 0)
+    return ga, gw
+
+
 def act_streams_canonical(buf, desc):
     """View the activation-stream buffer as int32 [B,C,Hp,Wp,P] (the oracle's layout)."""
     P = (desc.bit_length + 31) // 32

@@ -133,6 +133,27 @@ int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t
 int geo_sc_linear_forward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
                           int32_t *out_device, void *workspace_device, size_t workspace_bytes, void *stream);
 
+/* ---- float guide: the straight-through backward used for training ------------------------
+ * Replaces what the reference gets from PyTorch autograd over its guide functions
+ * (utils_functional.py:189-296 and :611-634): with w+ = clamp(w,0,100), w- = -clamp(w,-100,0)
+ * and y(+/-)_g the plain fp32 convolution restricted to binary-accumulated group g,
+ *     out = sum_g (1 - exp(-y+_g)) - sum_g (1 - exp(-y-_g)),
+ * whose value the caller replaces by the SC result and whose gradient is the layer's gradient.
+ *
+ * geo_sc_guide_forward computes exp(-y(+/-)_g) for every group into `saved` (device, 256-byte
+ * aligned, geo_sc_guide_bytes gives the three sizes).  geo_sc_guide_backward turns `saved` and
+ * grad_out [batch][c_out][Ho][Wo] into grad_act [batch][c_in][h_in][w_in] and/or grad_weight
+ * [c_out][c_in][k_h][k_w] (either may be NULL = not wanted); it overwrites `saved`, so one
+ * forward supports one backward.  All fp32, no atomics: results are run-to-run deterministic. */
+int geo_sc_guide_bytes(const geo_sc_conv_desc *desc, size_t *saved_bytes, size_t *forward_scratch_bytes,
+                       size_t *backward_scratch_bytes);
+int geo_sc_guide_forward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
+                         void *saved_device, size_t saved_bytes, void *scratch_device, size_t scratch_bytes,
+                         void *stream);
+int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *weight_device, void *saved_device,
+                          size_t saved_bytes, const float *grad_out_device, float *grad_act_device,
+                          float *grad_weight_device, void *scratch_device, size_t scratch_bytes, void *stream);
+
 /* ---- host mirror of the stream generator ------------------------------------------------
  * Runs on the CPU with the same pattern tables and loading plan the kernels use, for one
  * integer level `value` in [0, bit_length): seed = (seed_base + seed_index) mod (L-1) + 1

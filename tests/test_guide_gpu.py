@@ -1,0 +1,103 @@
+"""fp32 parity of the native guide kernels (forward exp(-y), weight and activation gradients) with
+the PyTorch restatement of the reference's guide functions, run on the CPU in fp32.
+Tolerance: 1e-5 relative to the largest magnitude of each gradient tensor."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-5
+
+
+def q7(x):
+    return (x * 128).round().clamp(-127, 127) / 128
+
+
+CASES = [
+    # act, weight, (pad_h, pad_w), z_unit
+    ((2, 3, 7, 6), (3, 3, 3, 2), (0, 0), 2),
+    ((3, 5, 9, 8), (7, 5, 2, 4), (1, 0), 2),
+    ((2, 8, 12, 12), (33, 8, 3, 3), (1, 1), 4),
+    ((5, 4, 11, 13), (17, 4, 5, 5), (2, 2), 3),
+    ((4, 32, 8, 8), (20, 32, 5, 5), (2, 2), 8),
+    ((3, 16, 4, 4), (10, 16, 4, 4), (0, 0), 16),
+    ((2, 40, 6, 6), (70, 40, 3, 3), (1, 1), 16),
+    ((9, 24, 1, 1), (12, 24, 1, 1), (0, 0), 8),
+]
+
+
+def _close(a, b, what):
+    scale = b.abs().max().item() + 1e-30
+    err = (a - b).abs().max().item()
+    assert err <= RTOL * scale, f"{what}: max err {err:.3e} vs scale {scale:.3e} (rel {err / scale:.2e})"
+
+
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or"])
+@pytest.mark.parametrize("case", range(len(CASES)))
+def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
+    from geo_b200 import ops
+    from oracle import guide as oracle_guide
+
+    ashape, wshape, pad, z = CASES[case]
+    g = torch.Generator().manual_seed(17 * case + len(mode))
+    a = q7(torch.rand(*ashape, generator=g))
+    w = q7((torch.rand(*wshape, generator=g) * 2 - 1) * 0.5)
+    w.view(-1)[::7] = 0.0          # exact zeros: clamp passes the gradient on both branches there
+    desc = ops.desc_for(a, w, 128, mode, pad, z_unit=z)
+    go = torch.randn(*ops.out_shape(desc), generator=g)
+    ga_ref, gw_ref = oracle_guide.guide_grads(a, w, go, mode, pad[0], pad[1], z_unit=z)
+
+    ad, wd = a.to(cuda_device), w.to(cuda_device)
+    saved = ops.guide_forward(ad, wd, desc)
+    ga, gw = ops.guide_backward(wd, saved, go.to(cuda_device), desc)
+    _close(gw.cpu(), gw_ref, f"{mode} grad_weight")
+    _close(ga.cpu(), ga_ref, f"{mode} grad_act")
+
+
+def test_layer_autograd_matches_reference_semantics(cuda_device, oracle_lib):
+    """conv2d_generic: value = SC counts / L (bit-exact), gradient = guide gradient."""
+    from geo_b200 import functional as sc_f
+    from oracle import guide as oracle_guide
+
+    g = torch.Generator().manual_seed(5)
+    a = q7(torch.rand(4, 6, 10, 10, generator=g))
+    w = q7((torch.rand(12, 6, 5, 5, generator=g) * 2 - 1) * 0.4)
+    for mode, kw in (("1d_bin", {}), ("yz_bin", {"z_unit": 2}), ("z_bin", {}), ("full_or", {})):
+        ad = a.to(cuda_device).requires_grad_(True)
+        wd = w.to(cuda_device).requires_grad_(True)
+        out = sc_f.conv2d_generic(ad, wd, (2, 2), (1, 1), bit_length=128, forward=mode, generator="lfsr", load_unit=2,
+                                  load_wait_w=2, load_wait_a=2, **kw)
+        lu = 8 if mode == "full_or" else 2
+        lw = 1 if mode == "full_or" else 2
+        ref = oracle_lib.conv2d(a, w, 128, mode, pad_h=2, pad_w=2, load_width=lu, load_wait_w=lw, load_wait_a=lw,
+                                z_unit=kw.get("z_unit", 1024))
+        assert torch.equal(out.detach().cpu(), torch.from_numpy(ref).float() / 128)
+        go = torch.randn(out.shape, generator=g)
+        out.backward(go.to(cuda_device))
+        ga_ref, gw_ref = oracle_guide.guide_grads(a, w, go, mode, 2, 2, z_unit=kw.get("z_unit", 1024))
+        _close(wd.grad.cpu(), gw_ref, f"{mode} layer grad_weight")
+        _close(ad.grad.cpu(), ga_ref, f"{mode} layer grad_act")
+
+
+def test_training_layer_shapes_full_batch(cuda_device):
+    """Second conv of the 4-layer CNN at batch 256: gradients against the same guide evaluated by
+    PyTorch on the GPU with TF32 convolutions disabled."""
+    from geo_b200 import ops
+    from oracle import guide as oracle_guide
+
+    g = torch.Generator().manual_seed(8)
+    a = q7(torch.rand(256, 32, 16, 16, generator=g)).to(cuda_device)
+    w = q7((torch.rand(32, 32, 5, 5, generator=g) * 2 - 1) * 0.1).to(cuda_device)
+    go = torch.randn(256, 32, 16, 16, generator=g).to(cuda_device)
+    desc = ops.desc_for(a, w, 128, "1d_bin", (2, 2))
+    saved = ops.guide_forward(a, w, desc)
+    ga, gw = ops.guide_backward(w, saved, go, desc)
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        ga_ref, gw_ref = oracle_guide.guide_grads(a, w, go, "1d_bin", 2, 2)
+    finally:
+        torch.backends.cudnn.allow_tf32 = old
+    # 65536 positions are summed per weight: allow the summation-order error of fp32 itself
+    scale = gw_ref.abs().max().item()
+    assert (gw - gw_ref).abs().max().item() <= 5e-5 * scale
+    assert (ga - ga_ref).abs().max().item() <= 1e-5 * ga_ref.abs().max().item()
