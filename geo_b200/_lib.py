@@ -58,6 +58,9 @@ def lib():
     i32p = ctypes.POINTER(ctypes.c_int32)
     L.geo_sc_group_geometry.argtypes = [dp, i32p, i32p, i32p, i32p]
     L.geo_sc_host_stream.argtypes = [i32] * 7 + [vp]
+    L.geo_sc_static_scratch_bytes.restype = ctypes.c_size_t
+    L.geo_sc_conv2d_forward_static.argtypes = [dp, vp, vp, vp, vp]
+    L.geo_sc_conv2d_forward_static.restype = i32
     L.geo_sc_guide_bytes.argtypes = [dp, szp, szp, szp]
     L.geo_sc_guide_forward.argtypes = [dp, vp, vp, vp, sz, vp, sz, vp]
     L.geo_sc_guide_backward.argtypes = [dp, vp, vp, sz, vp, vp, vp, vp, sz, vp]

@@ -94,6 +94,25 @@ int geo_sc_conv2d_workspace_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
 int geo_sc_conv2d_forward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
                           int32_t *out_device, void *workspace_device, size_t workspace_bytes, void *stream);
 
+/* ---- whole forward without a workspace argument -----------------------------------------
+ * No counterpart in the reference (whose launchers allocate managed memory on every call).
+ * For hosts that cannot give the library device memory at call time -- a runtime whose memory
+ * plan is frozen, a loop that must not touch the allocator once it is running, a plugin
+ * interface that carries tensor pointers only -- the stream scratch of this variant is a fixed
+ * array of geo_sc_static_scratch_bytes() = 64 MiB inside the library, resident on every GPU
+ * that loads it until the process exits.  It performs no device allocation of any kind; the
+ * caller still passes act, weight and out.  Same results as geo_sc_conv2d_forward.
+ *   - A convolution whose streams need more than the array is refused with
+ *     GEO_SC_ERR_WORKSPACE (the message gives both sizes).
+ *   - All calls share the array and it keeps whatever the previous call left; each call
+ *     rewrites every word it later reads, so that is harmless for calls that run one after
+ *     another, but two calls that may overlap on the GPU (other streams, other threads) race.
+ *   - The first call on each device looks up the array's device address (and, like every entry
+ *     point, may upload the LFSR tables): make it before starting any stream capture. */
+size_t geo_sc_static_scratch_bytes(void);
+int geo_sc_conv2d_forward_static(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
+                                 int32_t *out_device, void *stream);
+
 /* ---- the three stages, for callers that cache weight streams across calls ---------
  * (weights change once per optimiser step and never during evaluation).
  *
