@@ -60,8 +60,9 @@ def guide_output(activation, weight, mode, pad_h=0, pad_w=0, z_unit=1024, sc_val
 
 def guide_grads(activation, weight, grad_out, mode, pad_h=0, pad_w=0, z_unit=1024):
     """(grad_activation, grad_weight) of the guide for upstream gradient ``grad_out``."""
-    a = activation.detach().clone().requires_grad_(True)
-    w = weight.detach().clone().requires_grad_(True)
-    out = guide_output(a, w, mode, pad_h, pad_w, z_unit)
-    ga, gw = torch.autograd.grad(out, (a, w), grad_out)
+    with torch.enable_grad():
+        a = activation.detach().clone().requires_grad_(True)
+        w = weight.detach().clone().requires_grad_(True)
+        out = guide_output(a, w, mode, pad_h, pad_w, z_unit)
+        ga, gw = torch.autograd.grad(out, (a, w), grad_out)
     return ga, gw

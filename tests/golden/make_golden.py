@@ -96,3 +96,70 @@ def main():
 
 if __name__ == "__main__":
     main()
+
+
+def make_training_step_golden():
+    """One forward/backward/SGD step of the reference's own 4-layer CNN on the CPU
+    (network.CONV_tiny_add_partial + utils_class + utils_own.forward, reference files unmodified),
+    batch 4.  Weights are stored as the int8 levels the layers quantise to, inputs as uint8 levels."""
+    import sys
+    import types
+
+    uf = ref_loader.reference_python()
+    ref_root = "/root/reference"
+    for name in ("bokeh", "bokeh.io", "bokeh.plotting", "bokeh.layouts"):   # utils.py imports them, unused here
+        m = types.ModuleType(name)
+        m.output_file = m.save = m.show = m.figure = m.column = None
+        sys.modules.setdefault(name, m)
+    sys.modules["utils_functional"] = uf
+    sys.modules["sc_extension"] = ref_loader.ref_sc_extension()
+    sys.path.insert(0, ref_root)
+    try:
+        import network
+        import utils_own
+    finally:
+        sys.path.remove(ref_root)
+    torch.manual_seed(3)
+    net = network.CONV_tiny_add_partial()
+    net.err, net.z_unit, net.load_unit, net.load_wait = [7] * 4, [3, 3, 4, 4], [8] * 4, [2] * 4
+    convs = [net.conv1, net.conv2, net.conv3, net.fc1]
+    for c in convs:       # put the master weights on the 7-bit grid so that they can be stored as int8
+        c.weight_org.copy_(q7(c.weight_org * 3))
+        c.weight.data.copy_(c.weight_org)
+    x_lv = torch.randint(0, 128, (4, 3, 32, 32), dtype=torch.uint8)
+    y = torch.tensor([3, 1, 4, 1])
+    out = {"x_levels": x_lv.numpy(), "y": y.numpy()}
+    for i, c in enumerate(convs):
+        out[f"w{i}_levels"] = (c.weight_org * 128).round().to(torch.int8).numpy()
+    param_copy = [p.clone().float().detach().requires_grad_(True) for p in net.parameters()]
+    opt = torch.optim.SGD(param_copy, lr=2e-3, weight_decay=0, momentum=0.01)
+    net.train()
+    # forward/backward once by hand to record logits and gradients ...
+    logits = net(x_lv.float() / 128)
+    loss = torch.nn.functional.cross_entropy(logits, y) * 128.0
+    for p in net.parameters():
+        p.grad = None
+    loss.backward()
+    out["logits"] = logits.detach().numpy()
+    out["loss"] = np.array(loss.item(), np.float32)
+    for i, c in enumerate(convs):
+        g = c.weight.grad.detach().numpy()
+        out[f"gw{i}"] = g if g.size <= 8000 else g.reshape(-1)[::16].copy()
+    out["g_bn1_w"] = net.bn1.weight.grad.numpy()
+    out["g_bn4_b"] = net.bn4.bias.grad.numpy()
+    # ... then the reference's own loop body (utils_own.forward) for the optimiser step; it only
+    # steps once 128 samples have been seen, so feed the same 4 images 32 times.
+    loader = [(x_lv.float() / 128, y)] * 32
+    # the reference's accuracy() helper (utils.py:142-155) fails on this torch version (.view of a
+    # non-contiguous tensor); it only feeds the printed metrics, so it is stubbed out here
+    utils_own.accuracy = lambda output, target, topk=(1,): [torch.zeros(1) for _ in topk]
+    utils_own.forward(loader, net, torch.nn.CrossEntropyLoss(), 0, training=True, optimizer=opt,
+                      param_copy=param_copy, modules=net)
+    out["fc1_weight_org_after"] = net.fc1.weight_org.numpy()
+    out["conv1_weight_org_after"] = net.conv1.weight_org.numpy()
+    np.savez_compressed(os.path.join(HERE, "ref_tiny_cnn_step.npz"), **out)
+    print("wrote ref_tiny_cnn_step.npz")
+
+
+if __name__ == "__main__":
+    make_training_step_golden()
