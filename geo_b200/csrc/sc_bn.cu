@@ -1,0 +1,277 @@
+// Quantised batch normalisation ("BatchNorm*_fixed", utils_class.py:37-93) as native kernels.
+//
+// The reference computes it with F.batch_norm (for the autograd graph), separate mean / var
+// reductions, a dozen small element-wise ops for the 7-bit folded scale and shift
+// (quantize_shift, utils_functional.py:41-57) and a final x * w_q + b_q that replaces the value.
+// Here: two deterministic reduction passes (mean, then squared deviations), one single-CTA
+// kernel that folds, quantises and updates the running statistics, and one apply pass.  The
+// backward pass is the ordinary batch-norm gradient with respect to the *unquantised*
+// normalisation, which is what the reference's graph differentiates:
+//     dgamma = sum g * xhat,  dbeta = sum g,  dx = gamma * invstd * (g - dbeta/N - xhat * dgamma/N)
+// (in evaluation mode dx = gamma * invstd * g).  Layout: x [B][C][HW] (HW = 1 for the 1d variant).
+#include "sc_common.h"
+
+namespace geo {
+
+namespace {
+
+constexpr int BN_THREADS = 256;
+
+struct BnDims {
+    int B, C, HW, S;  // S = batch slices per channel in the reduction passes
+};
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    if (threadIdx.x < 32) {
+        r = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    }
+    return r;  // valid in thread 0
+}
+
+// mode 0: sum(x)   mode 1: sum((x - mean)^2)   -> partial[c][s]
+template <int MODE>
+__global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnDims d, const float *__restrict__ x,
+                                                               const float *__restrict__ mean,
+                                                               float *__restrict__ partial) {
+    __shared__ float red[32];
+    const int c = blockIdx.x, s = blockIdx.y;
+    const int b0 = (int)((long long)d.B * s / d.S), b1 = (int)((long long)d.B * (s + 1) / d.S);
+    const float mu = MODE == 1 ? mean[c] : 0.f;
+    float acc = 0.f;
+    const long long n = (long long)(b1 - b0) * d.HW;
+    for (long long i = threadIdx.x; i < n; i += BN_THREADS) {
+        const int b = b0 + (int)(i / d.HW), p = (int)(i % d.HW);
+        const float v = x[((size_t)b * d.C + c) * d.HW + p];
+        if (MODE == 0) acc += v;
+        else acc = fmaf(v - mu, v - mu, acc);
+    }
+    const float tot = block_sum(acc, red);
+    if (threadIdx.x == 0) partial[c * d.S + s] = tot;
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_mean_kernel(BnDims d, const float *__restrict__ partial,
+                                                             float *__restrict__ mean) {
+    const float inv_n = 1.0f / ((float)d.B * (float)d.HW);
+    for (int c = blockIdx.x * BN_THREADS + threadIdx.x; c < d.C; c += gridDim.x * BN_THREADS) {
+        float s = 0.f;
+        for (int i = 0; i < d.S; i++) s += partial[c * d.S + i];
+        mean[c] = s * inv_n;
+    }
+}
+
+// Single CTA: variance, invstd, running statistics, folded scale/shift and their 7-bit
+// quantisation under one power-of-two range (quantize_shift).
+__global__ void __launch_bounds__(BN_THREADS) bn_fold_kernel(BnDims d, int training, float eps, float momentum,
+                                                             const float *__restrict__ partial2, float *mean,
+                                                             float *invstd, const float *__restrict__ weight,
+                                                             const float *__restrict__ bias, float *running_mean,
+                                                             float *running_var, float *wq, float *bq, float *scale_out) {
+    __shared__ float red[32];
+    __shared__ float s_scale;
+    const float n = (float)d.B * (float)d.HW;
+    // pass A: per-channel statistics and the unquantised folded scale; sum of scales for the range
+    float local = 0.f;
+    for (int c = threadIdx.x; c < d.C; c += BN_THREADS) {
+        float mu, var;
+        if (training) {
+            float s = 0.f;
+            for (int i = 0; i < d.S; i++) s += partial2[c * d.S + i];
+            var = s / n;
+            mu = mean[c];
+            if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mu;
+            if (running_var) running_var[c] = (1.f - momentum) * running_var[c] + momentum * (n > 1.f ? s / (n - 1.f) : var);
+        } else {
+            mu = running_mean[c];
+            var = running_var[c];
+            mean[c] = mu;
+        }
+        const float sd = sqrtf(var + eps);
+        invstd[c] = 1.0f / sd;
+        const float w = weight ? weight[c] : 1.0f;
+        const float wn = w / sd;
+        wq[c] = wn;  // unquantised for now
+        local += wn;
+    }
+    const float tot = block_sum(local, red);
+    if (threadIdx.x == 0) {
+        // scale = 2 ** ceil(log2(mean(w_n) * 3))
+        const float m3 = tot / (float)d.C * 3.0f;
+        s_scale = exp2f(ceilf(log2f(m3)));
+        scale_out[0] = s_scale;
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    for (int c = threadIdx.x; c < d.C; c += BN_THREADS) {
+        const float w = weight ? weight[c] : 1.0f;
+        const float b = bias ? bias[c] : 0.0f;
+        const float sd = 1.0f / invstd[c];
+        const float wn = wq[c];
+        const float bn = b - mean[c] * w / sd;
+        const float qw = fminf(fmaxf(rintf(wn / scale * 128.0f), -127.0f), 127.0f) / 128.0f * scale;
+        const float qb = fminf(fmaxf(rintf(bn / scale * 128.0f), -127.0f), 127.0f) / 128.0f * scale;
+        wq[c] = qw;
+        bq[c] = qb;
+    }
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(BnDims d, const float *__restrict__ x,
+                                                              const float *__restrict__ wq, const float *__restrict__ bq,
+                                                              float *__restrict__ out) {
+    const long long total = (long long)d.B * d.C * d.HW;
+    for (long long i = (long long)blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * BN_THREADS) {
+        const int c = (int)((i / d.HW) % d.C);
+        out[i] = x[i] * wq[c] + bq[c];
+    }
+}
+
+// backward pass 1: partial sums of g and g * xhat
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(BnDims d, const float *__restrict__ x,
+                                                                   const float *__restrict__ g,
+                                                                   const float *__restrict__ mean,
+                                                                   const float *__restrict__ invstd,
+                                                                   float *__restrict__ partial) {
+    __shared__ float red[32];
+    const int c = blockIdx.x, s = blockIdx.y;
+    const int b0 = (int)((long long)d.B * s / d.S), b1 = (int)((long long)d.B * (s + 1) / d.S);
+    const float mu = mean[c], is = invstd[c];
+    float sg = 0.f, sgx = 0.f;
+    const long long n = (long long)(b1 - b0) * d.HW;
+    for (long long i = threadIdx.x; i < n; i += BN_THREADS) {
+        const int b = b0 + (int)(i / d.HW), p = (int)(i % d.HW);
+        const size_t idx = ((size_t)b * d.C + c) * d.HW + p;
+        const float gv = g[idx];
+        sg += gv;
+        sgx = fmaf(gv, (x[idx] - mu) * is, sgx);
+    }
+    const float t0 = block_sum(sg, red);
+    const float t1 = block_sum(sgx, red);
+    if (threadIdx.x == 0) {
+        partial[(c * d.S + s) * 2 + 0] = t0;
+        partial[(c * d.S + s) * 2 + 1] = t1;
+    }
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_final_kernel(BnDims d, const float *__restrict__ partial,
+                                                                  float *__restrict__ sums, float *grad_weight,
+                                                                  float *grad_bias) {
+    for (int c = blockIdx.x * BN_THREADS + threadIdx.x; c < d.C; c += gridDim.x * BN_THREADS) {
+        float a = 0.f, b = 0.f;
+        for (int i = 0; i < d.S; i++) {
+            a += partial[(c * d.S + i) * 2 + 0];
+            b += partial[(c * d.S + i) * 2 + 1];
+        }
+        sums[c * 2 + 0] = a;
+        sums[c * 2 + 1] = b;
+        if (grad_bias) grad_bias[c] = a;
+        if (grad_weight) grad_weight[c] = b;
+    }
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnDims d, int training, const float *__restrict__ x,
+                                                                  const float *__restrict__ g,
+                                                                  const float *__restrict__ mean,
+                                                                  const float *__restrict__ invstd,
+                                                                  const float *__restrict__ weight,
+                                                                  const float *__restrict__ sums,
+                                                                  float *__restrict__ gx) {
+    const long long total = (long long)d.B * d.C * d.HW;
+    const float inv_n = 1.0f / ((float)d.B * (float)d.HW);
+    for (long long i = (long long)blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * BN_THREADS) {
+        const int c = (int)((i / d.HW) % d.C);
+        const float w = weight ? weight[c] : 1.0f;
+        const float is = invstd[c];
+        if (training) {
+            const float xhat = (x[i] - mean[c]) * is;
+            gx[i] = w * is * (g[i] - sums[c * 2] * inv_n - xhat * sums[c * 2 + 1] * inv_n);
+        } else {
+            gx[i] = w * is * g[i];
+        }
+    }
+}
+
+int bn_slices(int B, int C) {
+    int S = (148 * 4 + C - 1) / C;
+    if (S > B) S = B;
+    if (S < 1) S = 1;
+    if (S > 64) S = 64;
+    return S;
+}
+
+int bn_grid(long long total) {
+    long long b = (total + BN_THREADS - 1) / BN_THREADS;
+    return (int)(b < 148 * 8 ? (b > 0 ? b : 1) : 148 * 8);
+}
+
+}  // namespace
+
+}  // namespace geo
+
+using namespace geo;
+
+extern "C" {
+
+int geo_sc_bn_fixed_scratch_bytes(int batch, int channels, size_t *bytes) {
+    if (batch < 1 || channels < 1) return fail(GEO_SC_ERR_SHAPE, "batch %d channels %d", batch, channels);
+    if (!bytes) return fail(GEO_SC_ERR_NULL, "bytes is NULL");
+    *bytes = align_up((size_t)channels * 64 * 2 * sizeof(float), 256) + align_up((size_t)channels * 4 * sizeof(float), 256);
+    return GEO_SC_OK;
+}
+
+int geo_sc_bn_fixed_forward(int batch, int channels, int spatial, int training, float eps, float momentum,
+                            const float *x, const float *weight, const float *bias, float *running_mean,
+                            float *running_var, float *out, float *save_mean, float *save_invstd, float *scale_out,
+                            void *scratch, size_t scratch_bytes, void *stream) {
+    if (batch < 1 || channels < 1 || spatial < 1) return fail(GEO_SC_ERR_SHAPE, "batch %d channels %d spatial %d", batch, channels, spatial);
+    if (!x || !out || !save_mean || !save_invstd || !scale_out || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
+    if (!training && (!running_mean || !running_var)) return fail(GEO_SC_ERR_NULL, "evaluation mode needs running statistics");
+    if ((long long)batch * channels * spatial > (1LL << 31) - 1) return fail(GEO_SC_ERR_TOO_LARGE, "tensor too large");
+    size_t need = 0;
+    geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
+    if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+    cudaStream_t s = (cudaStream_t)stream;
+    BnDims d = {batch, channels, spatial, bn_slices(batch, channels)};
+    float *partial = (float *)scratch;
+    float *wq = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
+    float *bq = wq + channels;
+    if (training) {
+        bn_reduce_kernel<0><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
+        bn_mean_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, save_mean);
+        bn_reduce_kernel<1><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
+    }
+    bn_fold_kernel<<<1, BN_THREADS, 0, s>>>(d, training, eps, momentum, partial, save_mean, save_invstd, weight, bias,
+                                            running_mean, running_var, wq, bq, scale_out);
+    bn_apply_kernel<<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(d, x, wq, bq, out);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training, const float *x, const float *grad_out,
+                             const float *weight, const float *save_mean, const float *save_invstd, float *grad_x,
+                             float *grad_weight, float *grad_bias, void *scratch, size_t scratch_bytes, void *stream) {
+    if (batch < 1 || channels < 1 || spatial < 1) return fail(GEO_SC_ERR_SHAPE, "batch %d channels %d spatial %d", batch, channels, spatial);
+    if (!x || !grad_out || !save_mean || !save_invstd || !grad_x || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
+    size_t need = 0;
+    geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
+    if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+    cudaStream_t s = (cudaStream_t)stream;
+    BnDims d = {batch, channels, spatial, bn_slices(batch, channels)};
+    float *partial = (float *)scratch;
+    float *sums = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
+    bn_bwd_reduce_kernel<<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, grad_out, save_mean, save_invstd, partial);
+    bn_bwd_final_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, sums, grad_weight, grad_bias);
+    bn_bwd_apply_kernel<<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(d, training, x, grad_out, save_mean,
+                                                                                      save_invstd, weight, sums, grad_x);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+}  // extern "C"

@@ -11,12 +11,13 @@
 //
 // (clamp passes the gradient on both branches at w == 0, hence the two inclusive masks.)
 //
-// Three register-tiled FFMA implicit-GEMM kernels, all fed through cp.async rings:
-//   guide_forward_kernel : E±_g = exp(-conv)            M = positions, N = 2*c_out, K = members
+// The guide's own value is never used (the reference overwrites it with the SC result), so nothing
+// is computed in the forward pass: the whole guide runs in the backward pass, as three
+// register-tiled FFMA implicit-GEMM kernels fed through cp.async rings:
+//   guide_forward_kernel : D = gout * exp(-conv)        M = positions, N = 2*c_out, K = members
 //   guide_wgrad_kernel   : sum_m a * D                  M = members,   N = 2*c_out, K = positions (split)
 //   guide_dgrad_kernel   : conv of D with flipped w     M = input pixels, N = c_in block, K = ky*kx*2*c_out
-// with D = gout * E written in place over E by an element-wise kernel in between.
-// E / D layout: [group][polarity][c_out_padded][position], position = (b*Ho + oy)*Wo + ox.
+// D layout: [group][polarity][c_out_padded][position], position = (b*Ho + oy)*Wo + ox.
 #include "sc_common.h"
 
 namespace geo {
@@ -122,15 +123,16 @@ __global__ void __launch_bounds__(256) guide_prep_dgrad_kernel(GuideDims d, cons
     }
 }
 
-// ---- forward: E±_g = exp(-conv_g) -------------------------------------------------------------
+// ---- D±_g = gout * exp(-conv_g) -------------------------------------------------------------
 constexpr int FKC = 16, FSTAGE = 3;
 
 struct FwdParams {
     const float *apad;  // [B][C][Hp][Wp]
     const float *wf;    // [G][K][Opad][2]
     const int *aoff;    // [G][K]
-    float *E;           // [G][2][Opad][M]
-    int M, Opad, HoWo, Wo, Wp, K, img;
+    const float *gout;  // [B][O][Ho][Wo]
+    float *D;           // [G][2][Opad][M] = gout * exp(-y)
+    int M, O, Opad, HoWo, Wo, Wp, K, img;
 };
 
 template <int NT, int NTHREADS>
@@ -211,34 +213,19 @@ __global__ void __launch_bounds__(NTHREADS) guide_forward_kernel(FwdParams pr) {
     }
     cp_wait<0>();
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const int o = o0 + ty * 4 + j;
-        float *ep = pr.E + ((size_t)(g * 2 + 0) * pr.Opad + o) * pr.M;
-        float *en = pr.E + ((size_t)(g * 2 + 1) * pr.Opad + o) * pr.M;
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? tx * 4 + i : MT / 2 + tx * 4 + (i - 4));
+        if (m < pr.M) {
+            const int b = m / pr.HoWo, rem = m % pr.HoWo;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int m = m0 + (i < 4 ? tx * 4 + i : MT / 2 + tx * 4 + (i - 4));
-            if (m < pr.M) {
-                ep[m] = expf(-accp[i][j]);
-                en[m] = expf(-accn[i][j]);
+            for (int j = 0; j < 4; j++) {
+                const int o = o0 + ty * 4 + j;
+                // padded channels have no upstream gradient: their D rows are zero
+                const float go = o < pr.O ? __ldg(pr.gout + ((size_t)b * pr.O + o) * pr.HoWo + rem) : 0.0f;
+                pr.D[((size_t)(g * 2 + 0) * pr.Opad + o) * pr.M + m] = go * expf(-accp[i][j]);
+                pr.D[((size_t)(g * 2 + 1) * pr.Opad + o) * pr.M + m] = go * expf(-accn[i][j]);
             }
         }
-    }
-}
-
-// ---- D = gout * E in place ------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) guide_make_d_kernel(GuideDims d, const float *__restrict__ gout,
-                                                           float *__restrict__ E) {
-    const long long total = (long long)d.G * d.N2 * d.M;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int m = (int)(i % d.M);
-        const int o = (int)((i / d.M) % d.Opad);
-        float v = 0.0f;
-        if (o < d.O) {
-            const int b = m / d.HoWo, rem = m % d.HoWo;
-            v = E[i] * gout[((size_t)b * d.O + o) * d.HoWo + rem];
-        }
-        E[i] = v;
     }
 }
 
@@ -354,6 +341,94 @@ __global__ void __launch_bounds__(KT) guide_wgrad_kernel(WgradParams pr) {
                 const int n = n0 + nth + 8 * j;
                 if (n < pr.N2) dst[(size_t)k * pr.N2 + n] = acc[i][j];
             }
+        }
+    }
+}
+
+// Variant for groups of at most 16 members (first layer of the CNN: 15; 3x3 z_bin: 9; linear with
+// z_unit 16): one member x 8 channels per thread, 16 member slots x 8 channel threads per CTA.
+__global__ void __launch_bounds__(128) guide_wgrad_smallk_kernel(WgradParams pr) {
+    constexpr int NTHREADS = 128, KS = 16;
+    constexpr int A_F = KS * WRS, D_F = WNT * WRS, ST_F = A_F + D_F;
+    extern __shared__ __align__(16) float wsm[];
+    const int t = threadIdx.x;
+    const int ks = t % KS, nth = t / KS;
+    const int ntiles = (pr.N2 + WNT - 1) / WNT;
+    const int g = blockIdx.y, n0 = blockIdx.z * WNT;
+    (void)ntiles;
+    const int mbeg = blockIdx.x * pr.slice_len, mend = min(pr.M, mbeg + pr.slice_len);
+    const int chunks = (mend - mbeg + WMC - 1) / WMC;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(wsm);
+    const bool vec = (pr.M & 3) == 0;
+    const int am = t % WMC, ar0 = t / WMC;   // 4 rows per pass
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < chunks) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % WSTAGE) * ST_F * 4, d_s = a_s + A_F * 4;
+            const int mc = mbeg + ld * WMC;
+            {
+                const int m = mc + am;
+                const bool mv = m < mend;
+                const int mm = mv ? m : mbeg;
+                const int b = mm / pr.HoWo, rem = mm % pr.HoWo;
+                const float *src = pr.apad + b * pr.img + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+                const int *ao = pr.aoff + g * pr.K;
+                for (int r = ar0; r < KS; r += NTHREADS / WMC) {
+                    const bool v = mv && r < pr.K;
+                    cp4(a_s + (uint32_t)(r * WRS + am) * 4, src + (v ? __ldg(ao + r) : 0), v);
+                }
+            }
+            if (vec) {
+                for (int i = t; i < WNT * (WMC / 4); i += NTHREADS) {
+                    const int r = i / (WMC / 4), c4 = i % (WMC / 4);
+                    const int n = n0 + r, m = mc + c4 * 4;
+                    const bool v = n < pr.N2 && m < mend;
+                    const float *src = pr.D + ((size_t)(g * pr.N2 + (v ? n : 0))) * pr.M + (v ? m : 0);
+                    cp16(d_s + (uint32_t)(r * WRS + c4 * 4) * 4, src, v);
+                }
+            } else {
+                for (int i = t; i < WNT * WMC; i += NTHREADS) {
+                    const int r = i / WMC, c = i % WMC;
+                    const int n = n0 + r, m = mc + c;
+                    const bool v = n < pr.N2 && m < mend;
+                    const float *src = pr.D + ((size_t)(g * pr.N2 + (v ? n : 0))) * pr.M + (v ? m : 0);
+                    cp4(d_s + (uint32_t)(r * WRS + c) * 4, src, v);
+                }
+            }
+            ld++;
+        }
+        cp_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < WSTAGE - 1; s++) issue();
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    for (int s = 0; s < chunks; s++) {
+        cp_wait<WSTAGE - 2>();
+        __syncthreads();
+        issue();
+        const float *a_s = wsm + (size_t)(s % WSTAGE) * ST_F, *d_s = a_s + A_F;
+#pragma unroll
+        for (int m4 = 0; m4 < WMC; m4 += 4) {
+            const float4 av = *(const float4 *)(a_s + ks * WRS + m4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float4 dv = *(const float4 *)(d_s + (nth + 8 * j) * WRS + m4);
+                acc[j] = fmaf(av.x, dv.x, acc[j]);
+                acc[j] = fmaf(av.y, dv.y, acc[j]);
+                acc[j] = fmaf(av.z, dv.z, acc[j]);
+                acc[j] = fmaf(av.w, dv.w, acc[j]);
+            }
+        }
+    }
+    cp_wait<0>();
+    if (ks < pr.K) {
+        float *dst = pr.partial + (((size_t)blockIdx.x * pr.G + g) * pr.K + ks) * pr.N2;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int n = n0 + nth + 8 * j;
+            if (n < pr.N2) dst[n] = acc[j];
         }
     }
 }
@@ -505,22 +580,31 @@ int grid1d(long long total) {
     return (int)(blocks < 148 * 16 ? (blocks > 0 ? blocks : 1) : 148 * 16);
 }
 
-// ---- buffer plans -----------------------------------------------------------------------------------
+// ---- buffer plan -------------------------------------------------------------------------------------
 struct GuidePlan {
-    size_t e_bytes, apad_bytes, aoff_bytes;  // saved: E | apad | aoff
-    size_t wf_bytes;                         // forward scratch
-    size_t wd_bytes, partial_bytes;          // backward scratch
+    size_t d_bytes, apad_bytes, aoff_bytes, wf_bytes, wd_bytes, partial_bytes;
     int S, slice_len, KT;
+    size_t total() const { return d_bytes + apad_bytes + aoff_bytes + wf_bytes + wd_bytes + partial_bytes; }
 };
 
 GuidePlan guide_plan(const GuideDims &d) {
     GuidePlan p;
-    p.e_bytes = align_up((size_t)d.G * d.N2 * d.M * 4, 256);
+    p.d_bytes = align_up((size_t)d.G * d.N2 * d.M * 4, 256);
     p.apad_bytes = align_up((size_t)d.B * d.C * d.Hp * d.Wp * 4, 256);
     p.aoff_bytes = align_up((size_t)d.G * d.K * 4, 256);
     p.wf_bytes = align_up((size_t)d.G * d.K * d.Opad * 2 * 4, 256);
     p.wd_bytes = align_up((size_t)d.J * d.K2 * d.K3 * d.N2 * d.cbpad * 4, 256);
-    p.KT = d.K >= 96 ? 128 : (d.K > 32 ? 64 : 32);
+    // member tile: 16 (dedicated small-group kernel) or the multiple of 32 up to 192 that wastes
+    // the fewest rows (ties to the larger tile)
+    if (d.K <= 16) {
+        p.KT = 16;
+    } else {
+        long long best = -1;
+        for (int kt = 32; kt <= 192; kt += 32) {
+            const long long rows = (long long)((d.K + kt - 1) / kt) * kt;
+            if (best < 0 || rows <= best) { best = rows; p.KT = kt; }
+        }
+    }
     const long long tiles = (long long)d.G * ((d.K + p.KT - 1) / p.KT) * ((d.N2 + WNT - 1) / WNT);
     long long S = (148LL * 6 + tiles - 1) / tiles;
     const long long maxS = (d.M + WMC - 1) / WMC;
@@ -583,8 +667,7 @@ using namespace geo;
 
 extern "C" {
 
-int geo_sc_guide_bytes(const geo_sc_conv_desc *desc, size_t *saved_bytes, size_t *forward_scratch_bytes,
-                       size_t *backward_scratch_bytes) {
+int geo_sc_guide_backward_bytes(const geo_sc_conv_desc *desc, size_t *scratch_bytes) {
     Geometry g;
     int rc = make_geometry(desc, &g);
     if (rc) return rc;
@@ -592,84 +675,80 @@ int geo_sc_guide_bytes(const geo_sc_conv_desc *desc, size_t *saved_bytes, size_t
     if ((long long)d.G * d.N2 * d.M > (1LL << 31) - 1 || (long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad > (1LL << 31) - 1)
         return fail(GEO_SC_ERR_TOO_LARGE, "guide tensors exceed 31-bit indexing (groups %d x channels %d x positions %d)",
                     d.G, d.N2, d.M);
-    const GuidePlan p = guide_plan(d);
-    if (saved_bytes) *saved_bytes = p.e_bytes + p.apad_bytes + p.aoff_bytes;
-    if (forward_scratch_bytes) *forward_scratch_bytes = p.wf_bytes;
-    if (backward_scratch_bytes) *backward_scratch_bytes = p.wd_bytes + p.partial_bytes;
+    if (!scratch_bytes) return fail(GEO_SC_ERR_NULL, "scratch_bytes is NULL");
+    *scratch_bytes = guide_plan(d).total();
     return GEO_SC_OK;
 }
 
-int geo_sc_guide_forward(const geo_sc_conv_desc *desc, const float *act, const float *weight, void *saved,
-                         size_t saved_bytes, void *scratch, size_t scratch_bytes, void *stream) {
+int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const float *weight, const float *grad_out,
+                          float *grad_act, float *grad_weight, void *scratch, size_t scratch_bytes, void *stream) {
     Geometry g;
     int rc = make_geometry(desc, &g);
     if (rc) return rc;
-    if (!act || !weight || !saved || !scratch) return fail(GEO_SC_ERR_NULL, "act, weight, saved or scratch is NULL");
+    if (!act || !weight || !grad_out || !scratch) return fail(GEO_SC_ERR_NULL, "act, weight, grad_out or scratch is NULL");
     const GuideDims d = guide_dims(g);
+    if ((long long)d.G * d.N2 * d.M > (1LL << 31) - 1 || (long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad > (1LL << 31) - 1)
+        return fail(GEO_SC_ERR_TOO_LARGE, "guide tensors exceed 31-bit indexing");
     const GuidePlan p = guide_plan(d);
-    if (saved_bytes < p.e_bytes + p.apad_bytes + p.aoff_bytes || scratch_bytes < p.wf_bytes ||
-        ((uintptr_t)saved & 255) || ((uintptr_t)scratch & 255))
-        return fail(GEO_SC_ERR_WORKSPACE, "guide buffers too small or not 256-byte aligned");
+    if (scratch_bytes < p.total() || ((uintptr_t)scratch & 255))
+        return fail(GEO_SC_ERR_WORKSPACE, "guide scratch holds %zu bytes, %zu needed (256-byte aligned)", scratch_bytes,
+                    p.total());
+    if (!grad_act && !grad_weight) return GEO_SC_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    float *E = (float *)saved;
-    float *apad = (float *)((char *)saved + p.e_bytes);
-    int *aoff = (int *)((char *)saved + p.e_bytes + p.apad_bytes);
-    float *wf = (float *)scratch;
+    char *base = (char *)scratch;
+    float *D = (float *)base;
+    float *apad = (float *)(base + p.d_bytes);
+    int *aoff = (int *)(base + p.d_bytes + p.apad_bytes);
+    float *wf = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes);
+    float *wd = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes);
+    float *partial = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes + p.wd_bytes);
+
+    // 1. D = gout * exp(-y) for every group and polarity
     pad_act_kernel<<<grid1d((long long)d.B * d.C * d.Hp * d.Wp), 256, 0, s>>>(d, act, apad);
     guide_prep_fwd_kernel<<<grid1d((long long)d.G * d.K * d.Opad), 256, 0, s>>>(d, weight, wf, aoff);
     GEO_CUDA_CHECK(cudaGetLastError());
-    FwdParams pr;
-    pr.apad = apad; pr.wf = wf; pr.aoff = aoff; pr.E = E;
-    pr.M = d.M; pr.Opad = d.Opad; pr.HoWo = d.HoWo; pr.Wo = d.Wo; pr.Wp = d.Wp; pr.K = d.K;
-    pr.img = d.C * d.Hp * d.Wp;
+    FwdParams fp;
+    fp.apad = apad; fp.wf = wf; fp.aoff = aoff; fp.gout = grad_out; fp.D = D;
+    fp.M = d.M; fp.O = d.O; fp.Opad = d.Opad; fp.HoWo = d.HoWo; fp.Wo = d.Wo; fp.Wp = d.Wp; fp.K = d.K;
+    fp.img = d.C * d.Hp * d.Wp;
     switch (g.NT) {
-    case 16: return launch_guide_fwd<16, 128>(d, pr, s);
-    case 32: return launch_guide_fwd<32, 256>(d, pr, s);
-    default: return launch_guide_fwd<64, 256>(d, pr, s);
+    case 16: rc = launch_guide_fwd<16, 128>(d, fp, s); break;
+    case 32: rc = launch_guide_fwd<32, 256>(d, fp, s); break;
+    default: rc = launch_guide_fwd<64, 256>(d, fp, s); break;
     }
-}
-
-int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *weight, void *saved, size_t saved_bytes,
-                          const float *grad_out, float *grad_act, float *grad_weight, void *scratch,
-                          size_t scratch_bytes, void *stream) {
-    Geometry g;
-    int rc = make_geometry(desc, &g);
     if (rc) return rc;
-    if (!weight || !saved || !grad_out || !scratch) return fail(GEO_SC_ERR_NULL, "weight, saved, grad_out or scratch is NULL");
-    const GuideDims d = guide_dims(g);
-    const GuidePlan p = guide_plan(d);
-    if (saved_bytes < p.e_bytes + p.apad_bytes + p.aoff_bytes || scratch_bytes < p.wd_bytes + p.partial_bytes ||
-        ((uintptr_t)saved & 255) || ((uintptr_t)scratch & 255))
-        return fail(GEO_SC_ERR_WORKSPACE, "guide buffers too small or not 256-byte aligned");
-    cudaStream_t s = (cudaStream_t)stream;
-    float *E = (float *)saved;
-    const float *apad = (const float *)((char *)saved + p.e_bytes);
-    const int *aoff = (const int *)((char *)saved + p.e_bytes + p.apad_bytes);
-    float *wd = (float *)scratch;
-    float *partial = (float *)((char *)scratch + p.wd_bytes);
 
-    guide_make_d_kernel<<<grid1d((long long)d.G * d.N2 * d.M), 256, 0, s>>>(d, grad_out, E);
-    GEO_CUDA_CHECK(cudaGetLastError());
-
+    // 2. weight gradient
     if (grad_weight) {
         WgradParams pr;
-        pr.apad = apad; pr.D = E; pr.aoff = aoff; pr.partial = partial;
+        pr.apad = apad; pr.D = D; pr.aoff = aoff; pr.partial = partial;
         pr.M = d.M; pr.N2 = d.N2; pr.HoWo = d.HoWo; pr.Wo = d.Wo; pr.Wp = d.Wp; pr.K = d.K; pr.G = d.G;
         pr.img = d.C * d.Hp * d.Wp; pr.slice_len = p.slice_len;
         switch (p.KT) {
+        case 16: {
+            constexpr size_t smem = (size_t)WSTAGE * (16 * WRS + WNT * WRS) * 4;
+            dim3 grid(p.S, d.G, (d.N2 + WNT - 1) / WNT);
+            guide_wgrad_smallk_kernel<<<grid, 128, smem, s>>>(pr);
+            GEO_CUDA_CHECK(cudaGetLastError());
+            break;
+        }
         case 32: rc = launch_guide_wgrad<32>(d, p, pr, s); break;
         case 64: rc = launch_guide_wgrad<64>(d, p, pr, s); break;
-        default: rc = launch_guide_wgrad<128>(d, p, pr, s); break;
+        case 96: rc = launch_guide_wgrad<96>(d, p, pr, s); break;
+        case 128: rc = launch_guide_wgrad<128>(d, p, pr, s); break;
+        case 160: rc = launch_guide_wgrad<160>(d, p, pr, s); break;
+        default: rc = launch_guide_wgrad<192>(d, p, pr, s); break;
         }
         if (rc) return rc;
         guide_wgrad_reduce_kernel<<<grid1d((long long)d.G * d.K * d.O), 256, 0, s>>>(d, p.S, partial, weight, grad_weight);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
+    // 3. activation gradient
     if (grad_act) {
         guide_prep_dgrad_kernel<<<grid1d((long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad), 256, 0, s>>>(d, weight, wd);
         GEO_CUDA_CHECK(cudaGetLastError());
         DgradParams pr;
-        pr.D = E; pr.wd = wd; pr.ga = grad_act;
+        pr.D = D; pr.wd = wd; pr.ga = grad_act;
         pr.M = d.M; pr.N2 = d.N2; pr.Ho = d.Ho; pr.Wo = d.Wo; pr.H = d.H; pr.W = d.W; pr.C = d.C; pr.ph = d.ph; pr.pw = d.pw;
         pr.K2 = d.K2; pr.K3 = d.K3; pr.mode = d.mode; pr.cb = d.cb; pr.cbpad = d.cbpad; pr.Min = d.Min;
         pr.R = d.K2 * d.K3 * d.N2;

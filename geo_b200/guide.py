@@ -7,7 +7,8 @@ plain convolution restricted to binary-accumulated group g,
     out = sum_g (1 - exp(-y+_g)) - sum_g (1 - exp(-y-_g))
 
 The guide's own value is never used (the reference overwrites it with the SC result), so the
-forward pass only computes exp(-y±_g), which is all the backward pass needs besides grad_out.
+forward pass computes nothing for it: activations and weights are saved and the backward pass
+evaluates exp(-y±_g) and both gradients in one native call.
 """
 from __future__ import annotations
 
@@ -25,25 +26,19 @@ class _SCConv2dGuide(torch.autograd.Function):
         counts = ops.sc_conv2d_staged(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
         need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if need_a or need_w:
-            desc = ops.desc_for(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
-            ctx.desc = desc
-            ctx.saved_guide = ops.guide_forward(activation, weight, desc)
-            ctx.save_for_backward(weight)
-            ctx.dtypes = (activation.dtype, weight.dtype)
+            ctx.desc = ops.desc_for(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
+            ctx.save_for_backward(activation, weight)
         return counts.to(torch.float32) / bit_length
 
     @staticmethod
     def backward(ctx, grad_out):
-        (weight,) = ctx.saved_tensors
-        if ctx.saved_guide is None:
-            raise RuntimeError("the guide buffer of this SC layer was already consumed by a backward pass")
-        ga, gw = ops.guide_backward(weight, ctx.saved_guide, grad_out, ctx.desc, ctx.needs_input_grad[0],
+        activation, weight = ctx.saved_tensors
+        ga, gw = ops.guide_backward(activation, weight, grad_out, ctx.desc, ctx.needs_input_grad[0],
                                     ctx.needs_input_grad[1])
-        ctx.saved_guide = None
         if ga is not None:
-            ga = ga.to(ctx.dtypes[0])
+            ga = ga.to(activation.dtype)
         if gw is not None:
-            gw = gw.to(ctx.dtypes[1])
+            gw = gw.to(weight.dtype)
         return (ga, gw) + (None,) * 9
 
 

@@ -4,9 +4,9 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from . import functional as sc_f
+from . import ops
 
 
 class Conv2d_Add_Partial(nn.Conv2d):
@@ -28,27 +28,31 @@ class Conv2d_Add_Partial(nn.Conv2d):
                                    load_unit=load_unit, load_wait_w=load_wait_w, load_wait_a=load_wait_a)
 
 
-def _fixed_affine(module, x, reduce_dims):
-    """Quantised normalisation shared by the two BatchNorm variants (utils_class.py:43-65,74-93):
-    the autograd graph is that of ``F.batch_norm``; the value is ``x * w_q + b_q`` with the folded
-    scale and shift quantised to 7 bits under one power-of-two range."""
-    out = F.batch_norm(x, module.running_mean, module.running_var, module.weight, module.bias,
-                       training=module.training)
-    if module.training:
-        mean = x.mean(dim=reduce_dims)
-        var = x.var(dim=reduce_dims, unbiased=False)
-    else:
-        mean, var = module.running_mean, module.running_var
-    if module.affine:
-        weight, bias = module.weight.data, module.bias.data
-    else:
-        weight, bias = 1, 0
-    inv = torch.sqrt(var + module.eps)
-    w_n = (weight / inv).detach()
-    b_n = (bias - mean * weight / inv).detach()
-    w_n, module.scale = sc_f.quantize_shift(w_n)
-    b_n, _ = sc_f.quantize_shift(b_n, module.scale)
-    return out, w_n, b_n
+class _BatchNormFixed(torch.autograd.Function):
+    """Value: x * w_q + b_q (folded, 7-bit quantised scale and shift).  Gradient: that of the plain
+    batch normalisation, as in the reference, where F.batch_norm provides the graph and the
+    quantised value is written over its output (utils_class.py:44-65)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, module):
+        momentum = module.momentum
+        if momentum is None:
+            raise NotImplementedError("cumulative moving average (momentum=None) is not provided")
+        out, mean, invstd, scale = ops.bn_fixed_forward(
+            x, weight.detach() if weight is not None else None, bias.detach() if bias is not None else None,
+            module.running_mean, module.running_var, module.training, momentum, module.eps)
+        module.scale = scale.reshape(())
+        ctx.training = module.training
+        ctx.has_affine = weight is not None
+        ctx.save_for_backward(x, weight, mean, invstd)
+        return out.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, mean, invstd = ctx.saved_tensors
+        gx, gw, gb = ops.bn_fixed_backward(x, grad_out, weight.detach() if weight is not None else None, mean, invstd,
+                                           ctx.training, ctx.has_affine)
+        return gx.to(x.dtype).view_as(x), gw, gb, None
 
 
 class BatchNorm2d_fixed(nn.BatchNorm2d):
@@ -59,9 +63,7 @@ class BatchNorm2d_fixed(nn.BatchNorm2d):
         self.register_buffer("scale", None)
 
     def forward(self, x):
-        out, w_n, b_n = _fixed_affine(self, x, (0, 2, 3))
-        out.data = (x.data * w_n.reshape(-1, 1, 1) + b_n.reshape(-1, 1, 1)).to(out.dtype)
-        return out
+        return _BatchNormFixed.apply(x, self.weight if self.affine else None, self.bias if self.affine else None, self)
 
 
 class BatchNorm1d_fixed(nn.BatchNorm1d):
@@ -72,6 +74,4 @@ class BatchNorm1d_fixed(nn.BatchNorm1d):
         self.register_buffer("scale", None)
 
     def forward(self, x):
-        out, w_n, b_n = _fixed_affine(self, x, (0,))
-        out.data = (x.data * w_n + b_n).to(out.dtype)
-        return out
+        return _BatchNormFixed.apply(x, self.weight if self.affine else None, self.bias if self.affine else None, self)

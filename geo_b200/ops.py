@@ -162,51 +162,82 @@ def accumulate(astreams, wprep, desc, out=None):
     return out
 
 
-def guide_bytes(desc):
-    """(saved, forward scratch, backward scratch) buffer sizes of the guide kernels."""
-    a, b, c = ctypes.c_size_t(0), ctypes.c_size_t(0), ctypes.c_size_t(0)
-    check(_lib.lib().geo_sc_guide_bytes(ctypes.byref(desc), ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)),
-          "geo_sc_guide_bytes")
-    return a.value, b.value, c.value
-
-
-def guide_forward(act, weight, desc):
-    """exp(-y) of every group of the float guide, as the opaque `saved` buffer for guide_backward."""
-    _require_cuda(act, weight)
+def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True):
+    """Gradient of the float guide: (grad_act or None, grad_weight or None)."""
+    _require_cuda(act, weight, grad_out)
     a = act.detach().to(torch.float32).contiguous()
-    w = weight.detach().to(torch.float32).contiguous()
-    nsaved, nfwd, _ = guide_bytes(desc)
-    with torch.cuda.device(a.device):
-        saved = torch.empty(nsaved, dtype=torch.uint8, device=a.device)
-        scratch = torch.empty(max(nfwd, 256), dtype=torch.uint8, device=a.device)
-        check(_lib.lib().geo_sc_guide_forward(ctypes.byref(desc), a.data_ptr(), w.data_ptr(), saved.data_ptr(),
-                                              saved.numel(), scratch.data_ptr(), scratch.numel(),
-                                              _stream_ptr(a.device)), "geo_sc_guide_forward")
-    STATS.launches += 3
-    return saved
-
-
-def guide_backward(weight, saved, grad_out, desc, need_act=True, need_weight=True):
-    """(grad_act or None, grad_weight or None); consumes ``saved``."""
-    _require_cuda(weight, saved, grad_out)
     w = weight.detach().to(torch.float32).contiguous()
     go = grad_out.detach().to(torch.float32).contiguous()
     if tuple(go.shape) != out_shape(desc):
         raise ValueError(f"grad_out has shape {tuple(go.shape)}, expected {out_shape(desc)}")
-    _, _, nbwd = guide_bytes(desc)
+    nbytes = _lib.size_query("geo_sc_guide_backward_bytes", desc)
     dev = w.device
     with torch.cuda.device(dev):
-        scratch = torch.empty(max(nbwd, 256), dtype=torch.uint8, device=dev)
+        scratch = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
         ga = torch.empty((desc.batch, desc.c_in, desc.h_in, desc.w_in), dtype=torch.float32, device=dev) \
             if need_act else None
         gw = torch.empty((desc.c_out, desc.c_in, desc.k_h, desc.k_w), dtype=torch.float32, device=dev) \
             if need_weight else None
-        check(_lib.lib().geo_sc_guide_backward(ctypes.byref(desc), w.data_ptr(), saved.data_ptr(), saved.numel(),
-                                               go.data_ptr(), ga.data_ptr() if need_act else None,
+        check(_lib.lib().geo_sc_guide_backward(ctypes.byref(desc), a.data_ptr(), w.data_ptr(), go.data_ptr(),
+                                               ga.data_ptr() if need_act else None,
                                                gw.data_ptr() if need_weight else None, scratch.data_ptr(),
                                                scratch.numel(), _stream_ptr(dev)), "geo_sc_guide_backward")
-    STATS.launches += 1 + (2 if need_weight else 0) + (2 if need_act else 0)
+    STATS.launches += 3 + (2 if need_weight else 0) + (2 if need_act else 0)
     return ga, gw
+
+
+def _bn_scratch(batch, channels, device):
+    n = ctypes.c_size_t(0)
+    check(_lib.lib().geo_sc_bn_fixed_scratch_bytes(batch, channels, ctypes.byref(n)), "geo_sc_bn_fixed_scratch_bytes")
+    return torch.empty(n.value, dtype=torch.uint8, device=device)
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def bn_fixed_forward(x, weight, bias, running_mean, running_var, training, momentum, eps):
+    """Quantised batch norm forward -> (out, save_mean, save_invstd, scale); updates the running
+    statistics in place in training mode.  x is [B,C,H,W] or [B,C], fp32, contiguous."""
+    _require_cuda(x)
+    xc = x.detach().to(torch.float32).contiguous()
+    B, C = xc.shape[0], xc.shape[1]
+    spatial = xc.numel() // (B * C)
+    dev = xc.device
+    with torch.cuda.device(dev):
+        out = torch.empty_like(xc)
+        mean = torch.empty(C, dtype=torch.float32, device=dev)
+        invstd = torch.empty(C, dtype=torch.float32, device=dev)
+        scale = torch.empty(1, dtype=torch.float32, device=dev)
+        scratch = _bn_scratch(B, C, dev)
+        check(_lib.lib().geo_sc_bn_fixed_forward(B, C, spatial, int(bool(training)), float(eps), float(momentum),
+                                                 xc.data_ptr(), _ptr(weight), _ptr(bias), _ptr(running_mean),
+                                                 _ptr(running_var), out.data_ptr(), mean.data_ptr(), invstd.data_ptr(),
+                                                 scale.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                                 _stream_ptr(dev)), "geo_sc_bn_fixed_forward")
+    STATS.launches += 5 if training else 2
+    return out, mean, invstd, scale
+
+
+def bn_fixed_backward(x, grad_out, weight, mean, invstd, training, need_affine=True):
+    """Gradient of the (unquantised) batch normalisation -> (grad_x, grad_weight, grad_bias)."""
+    _require_cuda(x, grad_out)
+    xc = x.detach().to(torch.float32).contiguous()
+    go = grad_out.detach().to(torch.float32).contiguous()
+    B, C = xc.shape[0], xc.shape[1]
+    spatial = xc.numel() // (B * C)
+    dev = xc.device
+    with torch.cuda.device(dev):
+        gx = torch.empty_like(xc)
+        gw = torch.empty(C, dtype=torch.float32, device=dev) if need_affine else None
+        gb = torch.empty(C, dtype=torch.float32, device=dev) if need_affine else None
+        scratch = _bn_scratch(B, C, dev)
+        check(_lib.lib().geo_sc_bn_fixed_backward(B, C, spatial, int(bool(training)), xc.data_ptr(), go.data_ptr(),
+                                                  _ptr(weight), mean.data_ptr(), invstd.data_ptr(), gx.data_ptr(),
+                                                  _ptr(gw), _ptr(gb), scratch.data_ptr(), scratch.numel(),
+                                                  _stream_ptr(dev)), "geo_sc_bn_fixed_backward")
+    STATS.launches += 3
+    return gx, gw, gb
 
 
 def act_streams_canonical(buf, desc):

@@ -159,19 +159,39 @@ int geo_sc_linear_forward(const geo_sc_conv_desc *desc, const float *act_device,
  *     out = sum_g (1 - exp(-y+_g)) - sum_g (1 - exp(-y-_g)),
  * whose value the caller replaces by the SC result and whose gradient is the layer's gradient.
  *
- * geo_sc_guide_forward computes exp(-y(+/-)_g) for every group into `saved` (device, 256-byte
- * aligned, geo_sc_guide_bytes gives the three sizes).  geo_sc_guide_backward turns `saved` and
- * grad_out [batch][c_out][Ho][Wo] into grad_act [batch][c_in][h_in][w_in] and/or grad_weight
- * [c_out][c_in][k_h][k_w] (either may be NULL = not wanted); it overwrites `saved`, so one
- * forward supports one backward.  All fp32, no atomics: results are run-to-run deterministic. */
-int geo_sc_guide_bytes(const geo_sc_conv_desc *desc, size_t *saved_bytes, size_t *forward_scratch_bytes,
-                       size_t *backward_scratch_bytes);
-int geo_sc_guide_forward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
-                         void *saved_device, size_t saved_bytes, void *scratch_device, size_t scratch_bytes,
-                         void *stream);
-int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *weight_device, void *saved_device,
-                          size_t saved_bytes, const float *grad_out_device, float *grad_act_device,
-                          float *grad_weight_device, void *scratch_device, size_t scratch_bytes, void *stream);
+ * The guide's value is never needed, only its gradient, so there is a single entry point for the
+ * backward pass: from act [batch][c_in][h_in][w_in], weight and grad_out [batch][c_out][Ho][Wo]
+ * it produces grad_act (same shape as act) and/or grad_weight [c_out][c_in][k_h][k_w]; either may
+ * be NULL = not wanted.  scratch: device, 256-byte aligned, geo_sc_guide_backward_bytes.
+ * All fp32, no atomics: results are run-to-run deterministic. */
+int geo_sc_guide_backward_bytes(const geo_sc_conv_desc *desc, size_t *scratch_bytes);
+int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
+                          const float *grad_out_device, float *grad_act_device, float *grad_weight_device,
+                          void *scratch_device, size_t scratch_bytes, void *stream);
+
+/* ---- quantised batch normalisation between SC layers -------------------------------------------
+ * Replaces BatchNorm2d_fixed / BatchNorm1d_fixed (utils_class.py:37-93), which the reference
+ * evaluates as F.batch_norm plus separate mean/var reductions and a chain of small element-wise
+ * ops (quantize_shift, utils_functional.py:41-57).  x and out are [batch][channels][spatial]
+ * (spatial = H*W, or 1 for the 1d layer).  Forward value: x * w_q + b_q with the folded scale
+ * w_n = weight / sqrt(var + eps) and shift b_n = bias - mean * weight / sqrt(var + eps) rounded to
+ * 7 bits under the common range scale = 2^ceil(log2(3 * mean_c(w_n))) (written to scale_out[0]);
+ * in training mode mean/var are the biased batch statistics and running_mean / running_var are
+ * updated with `momentum` (unbiased variance), in evaluation mode the running statistics are used.
+ * save_mean / save_invstd [channels] feed the backward pass, which is the gradient of the
+ * unquantised normalisation (what the reference's graph differentiates).  weight / bias may be
+ * NULL (no affine); grad_weight / grad_bias may be NULL.  Reductions are two-level and
+ * order-fixed: results are run-to-run deterministic. */
+int geo_sc_bn_fixed_scratch_bytes(int batch, int channels, size_t *bytes);
+int geo_sc_bn_fixed_forward(int batch, int channels, int spatial, int training, float eps, float momentum,
+                            const float *x_device, const float *weight_device, const float *bias_device,
+                            float *running_mean_device, float *running_var_device, float *out_device,
+                            float *save_mean_device, float *save_invstd_device, float *scale_out_device,
+                            void *scratch_device, size_t scratch_bytes, void *stream);
+int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training, const float *x_device,
+                             const float *grad_out_device, const float *weight_device, const float *save_mean_device,
+                             const float *save_invstd_device, float *grad_x_device, float *grad_weight_device,
+                             float *grad_bias_device, void *scratch_device, size_t scratch_bytes, void *stream);
 
 /* ---- host mirror of the stream generator ------------------------------------------------
  * Runs on the CPU with the same pattern tables and loading plan the kernels use, for one

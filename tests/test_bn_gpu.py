@@ -1,0 +1,70 @@
+"""Native quantised batch norm against a PyTorch restatement of utils_class.py:37-93 (CPU, fp32)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def reference_bn_fixed(x, weight, bias, running_mean, running_var, training, eps=1e-5, momentum=0.1):
+    """utils_class.py:43-65: graph of F.batch_norm, value x * w_q + b_q."""
+    out = F.batch_norm(x, running_mean, running_var, weight, bias, training=training, momentum=momentum, eps=eps)
+    dims = (0, 2, 3) if x.dim() == 4 else (0,)
+    shape = (-1, 1, 1) if x.dim() == 4 else (-1,)
+    if training:
+        mean, var = x.mean(dim=dims), x.var(dim=dims, unbiased=False)
+    else:
+        mean, var = running_mean, running_var
+    w = weight.data if weight is not None else 1
+    b = bias.data if bias is not None else 0
+    w_n = (w / torch.sqrt(var + eps)).detach()
+    b_n = (b - mean * w / torch.sqrt(var + eps)).detach()
+    scale = 2 ** torch.ceil(torch.log2(torch.mean(w_n) * 3))
+    q = lambda t: ((t / scale) * 128).round().clamp(-127, 127) / 128 * scale  # noqa: E731
+    out.data = (x.data * q(w_n).reshape(shape) + q(b_n).reshape(shape)).to(out.dtype)
+    return out, scale
+
+
+@pytest.mark.parametrize("shape", [(16, 32, 8, 8), (5, 7, 3, 5), (64, 10), (256, 64, 4, 4)])
+@pytest.mark.parametrize("training", [True, False])
+@pytest.mark.parametrize("affine", [True, False])
+def test_bn_fixed_matches_reference_formulation(cuda_device, shape, training, affine):
+    from geo_b200 import layers
+
+    g = torch.Generator().manual_seed(sum(shape) + training)
+    C = shape[1]
+    x = torch.rand(*shape, generator=g) * 2 - 0.3
+    cls = layers.BatchNorm2d_fixed if len(shape) == 4 else layers.BatchNorm1d_fixed
+    m = cls(C, affine=affine)
+    with torch.no_grad():
+        if affine:
+            m.weight.copy_(torch.rand(C, generator=g) + 0.5)
+            m.bias.copy_(torch.rand(C, generator=g) - 0.5)
+        m.running_mean.copy_(torch.rand(C, generator=g) * 0.2 + 0.5)
+        m.running_var.copy_(torch.rand(C, generator=g) * 0.2 + 0.2)
+    rm, rv = m.running_mean.clone(), m.running_var.clone()
+    w_ref = m.weight.detach().clone().requires_grad_(True) if affine else None
+    b_ref = m.bias.detach().clone().requires_grad_(True) if affine else None
+    x_ref = x.clone().requires_grad_(True)
+    out_ref, scale_ref = reference_bn_fixed(x_ref, w_ref, b_ref, rm, rv, training)
+    go = torch.randn(*shape, generator=g)
+    out_ref.backward(go)
+
+    m = m.to(cuda_device)
+    m.train(training)
+    xd = x.to(cuda_device).requires_grad_(True)
+    out = m(xd)
+    out.backward(go.to(cuda_device))
+
+    assert float(m.scale) == float(scale_ref)
+    # a folded coefficient that lands within rounding error of a quantisation boundary may fall on
+    # the other side; everything else must agree to fp32 accuracy
+    diff = (out.detach().cpu() - out_ref.detach()).abs()
+    tol = 1e-5 * out_ref.detach().abs().max().item()
+    assert (diff <= tol).float().mean().item() > 0.97
+    assert torch.allclose(xd.grad.cpu(), x_ref.grad, rtol=1e-4, atol=1e-5 * x_ref.grad.abs().max().item())
+    if affine:
+        assert torch.allclose(m.weight.grad.cpu(), w_ref.grad, rtol=1e-4, atol=1e-5 * w_ref.grad.abs().max().item())
+        assert torch.allclose(m.bias.grad.cpu(), b_ref.grad, rtol=1e-4, atol=1e-5 * b_ref.grad.abs().max().item())
+    assert torch.allclose(m.running_mean.cpu(), rm, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(m.running_var.cpu(), rv, rtol=1e-5, atol=1e-6)

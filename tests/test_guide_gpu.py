@@ -47,8 +47,7 @@ def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
     ga_ref, gw_ref = oracle_guide.guide_grads(a, w, go, mode, pad[0], pad[1], z_unit=z)
 
     ad, wd = a.to(cuda_device), w.to(cuda_device)
-    saved = ops.guide_forward(ad, wd, desc)
-    ga, gw = ops.guide_backward(wd, saved, go.to(cuda_device), desc)
+    ga, gw = ops.guide_backward(ad, wd, go.to(cuda_device), desc)
     _close(gw.cpu(), gw_ref, f"{mode} grad_weight")
     _close(ga.cpu(), ga_ref, f"{mode} grad_act")
 
@@ -89,8 +88,7 @@ def test_training_layer_shapes_full_batch(cuda_device):
     w = q7((torch.rand(32, 32, 5, 5, generator=g) * 2 - 1) * 0.1).to(cuda_device)
     go = torch.randn(256, 32, 16, 16, generator=g).to(cuda_device)
     desc = ops.desc_for(a, w, 128, "1d_bin", (2, 2))
-    saved = ops.guide_forward(a, w, desc)
-    ga, gw = ops.guide_backward(w, saved, go, desc)
+    ga, gw = ops.guide_backward(a, w, go, desc)
     old = torch.backends.cudnn.allow_tf32
     torch.backends.cudnn.allow_tf32 = False
     try:
