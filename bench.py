@@ -119,7 +119,7 @@ def run_native(args):
 
     net = build_model(args.workload, device)
     hook = GradientAllReduce(world) if world > 1 else None
-    step = TrainStep(net, lr=2e-3, optim="SGD", grad_hook=hook)
+    step = TrainStep(net, lr=2e-3, optim="SGD", grad_hook=hook, graph=not args.no_graph)
 
     B = PER_GPU_BATCH
     g = torch.Generator().manual_seed(1234 + rank)
@@ -148,13 +148,17 @@ def run_native(args):
         return float(ms.item())
 
     def resident_step(i):
-        step(dev_x[i % nbatch].clone(), dev_y[i % nbatch])
+        x = dev_x[i % nbatch]
+        step(x.clone() if args.no_graph else x, dev_y[i % nbatch])
 
     losses = []
 
     def e2e_step(i):
-        x = host_x[i % nbatch].to(device, non_blocking=True)
-        y = host_y[i % nbatch].to(device, non_blocking=True)
+        if args.no_graph:
+            x = host_x[i % nbatch].to(device, non_blocking=True)
+            y = host_y[i % nbatch].to(device, non_blocking=True)
+        else:  # the pinned host batch is copied straight into the graph's input buffers
+            x, y = host_x[i % nbatch], host_y[i % nbatch]
         loss, _ = step(x, y)
         losses.append(loss.item())  # device -> host read of the step's result
 
@@ -162,19 +166,24 @@ def run_native(args):
         resident_step(i)
     sampler = ClockSampler(local)
     sampler.start()
-    ops.STATS.reset()
     total_ms = timed(resident_step, args.steps)
-    launches = ops.STATS.launches
     clocks = sampler.stop()
     e2e_ms = timed(e2e_step, args.steps)
 
-    # roofline of the dominant kernel: the SC accumulate launches of the same steps, bracketed by events
+    # roofline of the dominant kernel: the same step run eagerly (a graph replay cannot be bracketed
+    # kernel by kernel) with CUDA events around every SC accumulate launch; the same pass counts the
+    # launches of this library's kernels per step
+    eager = TrainStep(net, lr=2e-3, optim="SGD", grad_hook=hook, graph=False)
+    for i in range(2):
+        eager(dev_x[i % nbatch].clone(), dev_y[i % nbatch])
     ops.STATS.reset()
     ops.STATS.profile = True
-    for i in range(min(args.steps, 5)):
-        resident_step(i)
+    nprof = min(args.steps, 5)
+    for i in range(nprof):
+        eager(dev_x[i % nbatch].clone(), dev_y[i % nbatch])
     torch.cuda.synchronize()
     ops.STATS.profile = False
+    launches = ops.STATS.launches // nprof * args.steps
     lop3 = sum(r[0] for r in ops.STATS.records)
     nbytes = sum(r[1] for r in ops.STATS.records)
     acc_ms = sum(r[2].elapsed_time(r[3]) for r in ops.STATS.records)
@@ -196,6 +205,7 @@ def run_native(args):
                        if args.workload == "tiny_cnn" else
                        f"vgg11: VGG-11-style SC CNN training step, batch {B}/GPU, L={BIT_LENGTH}, 1d_bin, lfsr, SGD",
                        "per_gpu_batch": B, "global_batch": B * world, "parallelism": f"dp{world}",
+                       "launch": "eager" if args.no_graph else "whole step replayed as one CUDA graph",
                        "l2": "per-step working set (activation streams, guide tensors) exceeds the 126 MB L2; "
                              "4 input batches rotated; no explicit flush"},
             "e2e": {"value": images / (e2e_ms * 1e-3), "unit": "images/s",
@@ -282,6 +292,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="tiny_cnn", choices=["tiny_cnn", "vgg11"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of one CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     out = run_reference(args) if args.impl == "reference" else run_native(args)

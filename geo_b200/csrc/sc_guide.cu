@@ -618,9 +618,17 @@ GuidePlan guide_plan(const GuideDims &d) {
     return p;
 }
 
+// Raises the dynamic shared-memory limit of a kernel once per device (not on every launch, so
+// that steady-state calls contain nothing but launches and can be captured into a CUDA graph).
 template <typename Kern>
 int set_smem(Kern kern, size_t bytes) {
-    GEO_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    static bool done[64] = {};   // one instance per kernel type
+    int dev = 0;
+    GEO_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+    }
     return GEO_SC_OK;
 }
 

@@ -17,7 +17,7 @@ class TrainStep:
     ``grad_hook`` is called with the list of parameters after backward and before the gradients
     are copied to the master copy: the data-parallel wrapper all-reduces them there."""
 
-    def __init__(self, model, lr=2e-3, optim="SGD", grad_hook=None):
+    def __init__(self, model, lr=2e-3, optim="SGD", grad_hook=None, graph=False):
         self.model = model
         self.criterion = nn.CrossEntropyLoss()
         self.param_copy = [p.clone().float().detach().requires_grad_(True) for p in model.parameters()]
@@ -30,8 +30,39 @@ class TrainStep:
         self.grad_hook = grad_hook
         self.params = list(model.parameters())
         self.sc_modules = [m for m in model.modules() if hasattr(m, "weight_org")]
+        # graph=True: the whole step (forward, backward, gradient exchange, optimiser) is captured
+        # into one CUDA graph on first use and replayed afterwards; shapes must then stay fixed.
+        self.use_graph = graph
+        self._graph = None
+        self._static = None
 
     def __call__(self, inputs, targets):
+        if not self.use_graph:
+            return self._step(inputs, targets)
+        if self._graph is None:
+            self._capture(inputs, targets)
+        sx, sy, sloss, sout = self._static
+        sx.copy_(inputs, non_blocking=True)
+        sy.copy_(targets, non_blocking=True)
+        self._graph.replay()
+        return sloss, sout
+
+    def _capture(self, inputs, targets):
+        sx, sy = inputs.detach().clone(), targets.detach().clone()
+        side = torch.cuda.Stream(device=sx.device)
+        side.wait_stream(torch.cuda.current_stream(sx.device))
+        with torch.cuda.stream(side):
+            for _ in range(3):  # warm-up: lazy initialisation, optimiser state, allocator pools
+                self._step(sx.clone(), sy)
+        torch.cuda.current_stream(sx.device).wait_stream(side)
+        torch.cuda.synchronize(sx.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sloss, sout = self._step(sx.clone(), sy)
+        self._graph = graph
+        self._static = (sx, sy, sloss, sout)
+
+    def _step(self, inputs, targets):
         model = self.model
         model.train()
         output = model(inputs)
