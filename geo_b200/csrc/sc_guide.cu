@@ -621,8 +621,7 @@ GuidePlan guide_plan(const GuideDims &d) {
 // Raises the dynamic shared-memory limit of a kernel once per device (not on every launch, so
 // that steady-state calls contain nothing but launches and can be captured into a CUDA graph).
 template <typename Kern>
-int set_smem(Kern kern, size_t bytes) {
-    static bool done[64] = {};   // one instance per kernel type
+int set_smem(Kern kern, size_t bytes, bool *done) {   // `done`: one 64-entry array per kernel
     int dev = 0;
     GEO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !done[dev]) {
@@ -636,7 +635,8 @@ template <int NT, int NTHREADS>
 int launch_guide_fwd(const GuideDims &d, const FwdParams &pr, cudaStream_t s) {
     constexpr int TY = NT / 4, TX = NTHREADS / TY, MT = TX * 8;
     constexpr size_t smem = (size_t)FSTAGE * (FKC * MT + FKC * NT * 2) * 4;
-    int rc = set_smem(guide_forward_kernel<NT, NTHREADS>, smem);
+    static bool done[64] = {};
+    int rc = set_smem(guide_forward_kernel<NT, NTHREADS>, smem, done);
     if (rc) return rc;
     dim3 grid((d.M + MT - 1) / MT, d.Opad / NT, d.G);
     guide_forward_kernel<NT, NTHREADS><<<grid, NTHREADS, smem, s>>>(pr);
@@ -647,7 +647,8 @@ int launch_guide_fwd(const GuideDims &d, const FwdParams &pr, cudaStream_t s) {
 template <int KT>
 int launch_guide_wgrad(const GuideDims &d, const GuidePlan &p, const WgradParams &pr, cudaStream_t s) {
     constexpr size_t smem = (size_t)WSTAGE * (KT * WRS + WNT * WRS) * 4;
-    int rc = set_smem(guide_wgrad_kernel<KT>, smem);
+    static bool done[64] = {};
+    int rc = set_smem(guide_wgrad_kernel<KT>, smem, done);
     if (rc) return rc;
     dim3 grid(p.S, (d.K + KT - 1) / KT, d.G * ((d.N2 + WNT - 1) / WNT));
     guide_wgrad_kernel<KT><<<grid, KT, smem, s>>>(pr);
@@ -659,7 +660,8 @@ template <int NT, int NTHREADS>
 int launch_guide_dgrad(const GuideDims &d, const DgradParams &pr, cudaStream_t s) {
     constexpr int TY = NT / 8, TX = NTHREADS / TY, MT = TX * 8;
     constexpr size_t smem = (size_t)DSTAGE * (DKC * MT + DKC * NT) * 4;
-    int rc = set_smem(guide_dgrad_kernel<NT, NTHREADS>, smem);
+    static bool done[64] = {};
+    int rc = set_smem(guide_dgrad_kernel<NT, NTHREADS>, smem, done);
     if (rc) return rc;
     dim3 grid((d.Min + MT - 1) / MT, d.cbpad / NT, d.J);
     guide_dgrad_kernel<NT, NTHREADS><<<grid, NTHREADS, smem, s>>>(pr);
