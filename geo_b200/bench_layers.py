@@ -59,7 +59,7 @@ def _time(fn, reps):
     return ts[len(ts) // 2]
 
 
-def run_config(name, batch=None, reps=10, peak=None, device="cuda:0"):
+def run_config(name, batch=None, reps=10, peak=None, device="cuda:0", guide=False):
     ash, wsh, pad, L, mode, lu, lw, z = CONFIGS[name]
     if batch:
         ash = (batch,) + tuple(ash[1:])
@@ -78,10 +78,15 @@ def run_config(name, batch=None, reps=10, peak=None, device="cuda:0"):
     t_a = _time(lambda: ops.generate_act_streams(a, d), reps)
     t_c = _time(lambda: ops.accumulate(astr, wprep, d, out), reps)
     t_all = _time(lambda: ops.sc_conv2d(a, w, L, mode, pad, workspace=ws, out=out, **kw), reps)
+    t_g = None
+    if guide:
+        go = torch.randn(ops.out_shape(d), generator=g).to(dev)
+        t_g = _time(lambda: ops.guide_backward(a, w, go, d), reps)
     rate = lop3 / (t_c * 1e-3)
     G, K, NT, Opad = _lib.group_geometry(d)
     return {"config": name, "act": list(ash), "weight": list(wsh), "L": L, "mode": mode, "groups": G, "members": K,
             "ms_weight_streams": t_w, "ms_act_streams": t_a, "ms_accumulate": t_c, "ms_forward": t_all,
+            "ms_guide_backward": t_g, "guide_tflops": (6 * lop3 / (2 * ((L + 31) // 32)) * 2 / (t_g * 1e-3) / 1e12) if t_g else None,
             "lop3": lop3, "tlop3_per_s": rate / 1e12, "frac_of_lop3_peak": rate / peak if peak else None,
             "sc_bitops_per_s": lop3 * 32 * (L / (32 * ((L + 31) // 32))) / (t_all * 1e-3),
             "hbm_gb_per_s": nbytes / (t_all * 1e-3) / 1e9}
@@ -93,6 +98,7 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--no-peak", action="store_true")
+    ap.add_argument("--guide", action="store_true", help="also time the fp32 guide backward (dgrad + wgrad)")
     a = ap.parse_args(argv)
     names = a.config or ["c1", "c2conv1", "c2conv2", "c2conv3", "c2fc1", "c4_1d", "c4_full_or"]
     peak = None
@@ -100,7 +106,7 @@ def main(argv=None):
         peak, _ = ops.measure_lop3_peak()
         print(json.dumps({"lop3_peak_per_s": peak, "lanes_per_clk_per_sm_at_1965MHz": peak / 148 / 1.965e9}))
     for n in names:
-        print(json.dumps(run_config(n, a.batch, a.reps, peak)), flush=True)
+        print(json.dumps(run_config(n, a.batch, a.reps, peak, guide=a.guide)), flush=True)
 
 
 if __name__ == "__main__":

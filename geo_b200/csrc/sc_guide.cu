@@ -133,6 +133,7 @@ struct FwdParams {
     const float *gout;  // [B][O][Ho][Wo]
     float *D;           // [G][2][Opad][M] = gout * exp(-y)
     int M, O, Opad, HoWo, Wo, Wp, K, img;
+    int vec_ok;         // M and Ho*Wo multiples of 4 and gout 16-byte aligned: 4 positions per access
 };
 
 template <int NT, int NTHREADS>
@@ -212,18 +213,38 @@ __global__ void __launch_bounds__(NTHREADS) guide_forward_kernel(FwdParams pr) {
         }
     }
     cp_wait<0>();
+    // epilogue: D = gout * exp(-y); the thread's positions are two runs of 4 consecutive ones
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int m = m0 + (i < 4 ? tx * 4 + i : MT / 2 + tx * 4 + (i - 4));
-        if (m < pr.M) {
-            const int b = m / pr.HoWo, rem = m % pr.HoWo;
+    for (int half = 0; half < 2; half++) {
+        const int m = m0 + half * (MT / 2) + tx * 4;
+        if (m >= pr.M) continue;
+        const int b = m / pr.HoWo, rem = m % pr.HoWo;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int o = o0 + ty * 4 + j;
-                // padded channels have no upstream gradient: their D rows are zero
-                const float go = o < pr.O ? __ldg(pr.gout + ((size_t)b * pr.O + o) * pr.HoWo + rem) : 0.0f;
-                pr.D[((size_t)(g * 2 + 0) * pr.Opad + o) * pr.M + m] = go * expf(-accp[i][j]);
-                pr.D[((size_t)(g * 2 + 1) * pr.Opad + o) * pr.M + m] = go * expf(-accn[i][j]);
+        for (int j = 0; j < 4; j++) {
+            const int o = o0 + ty * 4 + j;
+            float *dp = pr.D + ((size_t)(g * 2 + 0) * pr.Opad + o) * pr.M + m;
+            float *dn = pr.D + ((size_t)(g * 2 + 1) * pr.Opad + o) * pr.M + m;
+            if (pr.vec_ok) {
+                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);  // padded channels have no upstream gradient
+                if (o < pr.O) go = __ldg((const float4 *)(pr.gout + ((size_t)b * pr.O + o) * pr.HoWo + rem));
+                float4 vp, vn;
+                vp.x = go.x * expf(-accp[half * 4 + 0][j]); vn.x = go.x * expf(-accn[half * 4 + 0][j]);
+                vp.y = go.y * expf(-accp[half * 4 + 1][j]); vn.y = go.y * expf(-accn[half * 4 + 1][j]);
+                vp.z = go.z * expf(-accp[half * 4 + 2][j]); vn.z = go.z * expf(-accn[half * 4 + 2][j]);
+                vp.w = go.w * expf(-accp[half * 4 + 3][j]); vn.w = go.w * expf(-accn[half * 4 + 3][j]);
+                *(float4 *)dp = vp;
+                *(float4 *)dn = vn;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int mi = m + i;
+                    if (mi < pr.M) {
+                        const int bi = mi / pr.HoWo, ri = mi % pr.HoWo;
+                        const float go = o < pr.O ? __ldg(pr.gout + ((size_t)bi * pr.O + o) * pr.HoWo + ri) : 0.0f;
+                        dp[i] = go * expf(-accp[half * 4 + i][j]);
+                        dn[i] = go * expf(-accn[half * 4 + i][j]);
+                    }
+                }
             }
         }
     }
@@ -242,7 +263,7 @@ struct WgradParams {
 };
 
 template <int KT>
-__global__ void __launch_bounds__(KT) guide_wgrad_kernel(WgradParams pr) {
+__global__ void __launch_bounds__(KT, KT <= 128 ? 3 : 2) guide_wgrad_kernel(WgradParams pr) {
     constexpr int NTHREADS = KT;           // (KT/8) member-threads x 8 channel-threads
     constexpr int KTH = KT / 8;
     constexpr int A_F = KT * WRS, D_F = WNT * WRS, ST_F = A_F + D_F;
@@ -314,20 +335,20 @@ __global__ void __launch_bounds__(KT) guide_wgrad_kernel(WgradParams pr) {
         const float *a_s = wsm + (size_t)(s % WSTAGE) * ST_F, *d_s = a_s + A_F;
 #pragma unroll 2
         for (int m4 = 0; m4 < WMC; m4 += 4) {
-            float4 av[8], dv[8];
+            float4 av[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) av[i] = *(const float4 *)(a_s + (kth + KTH * i) * WRS + m4);
 #pragma unroll
-            for (int j = 0; j < 8; j++) dv[j] = *(const float4 *)(d_s + (nth + 8 * j) * WRS + m4);
+            for (int j = 0; j < 8; j++) {
+                const float4 dv = *(const float4 *)(d_s + (nth + 8 * j) * WRS + m4);
 #pragma unroll
-            for (int i = 0; i < 8; i++)
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    acc[i][j] = fmaf(av[i].x, dv[j].x, acc[i][j]);
-                    acc[i][j] = fmaf(av[i].y, dv[j].y, acc[i][j]);
-                    acc[i][j] = fmaf(av[i].z, dv[j].z, acc[i][j]);
-                    acc[i][j] = fmaf(av[i].w, dv[j].w, acc[i][j]);
+                for (int i = 0; i < 8; i++) {
+                    acc[i][j] = fmaf(av[i].x, dv.x, acc[i][j]);
+                    acc[i][j] = fmaf(av[i].y, dv.y, acc[i][j]);
+                    acc[i][j] = fmaf(av[i].z, dv.z, acc[i][j]);
+                    acc[i][j] = fmaf(av[i].w, dv.w, acc[i][j]);
                 }
+            }
         }
     }
     cp_wait<0>();
@@ -721,6 +742,7 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
     fp.apad = apad; fp.wf = wf; fp.aoff = aoff; fp.gout = grad_out; fp.D = D;
     fp.M = d.M; fp.O = d.O; fp.Opad = d.Opad; fp.HoWo = d.HoWo; fp.Wo = d.Wo; fp.Wp = d.Wp; fp.K = d.K;
     fp.img = d.C * d.Hp * d.Wp;
+    fp.vec_ok = (d.M % 4 == 0) && (d.HoWo % 4 == 0) && (((uintptr_t)grad_out & 15) == 0);
     switch (g.NT) {
     case 16: rc = launch_guide_fwd<16, 128>(d, fp, s); break;
     case 32: rc = launch_guide_fwd<32, 256>(d, fp, s); break;
