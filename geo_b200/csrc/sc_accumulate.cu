@@ -17,8 +17,6 @@
 
 namespace geo {
 
-constexpr int KC = 16;      // members per stage
-constexpr int NSTAGE = 4;   // cp.async ring depth
 constexpr int TM = 8;       // positions per thread
 constexpr int TN = 4;       // output channels per thread
 
@@ -34,8 +32,10 @@ struct AccParams {
     int splits;           // CTAs along grid.z sharing one output tile; > 1 => atomic accumulation
 };
 
-__device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr));
+// 4-byte copy; with valid == false the destination word is zero-filled (source size 0)
+__device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr, bool valid = true) {
+    const int n = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_addr), "l"(gptr), "r"(n));
 }
 __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *gptr) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr));
@@ -46,7 +46,7 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
-template <int NT, int NTHREADS>
+template <int NT, int NTHREADS, int KC, int NSTAGE>
 struct Tile {
     static constexpr int TY = NT / TN;          // thread rows over channels
     static constexpr int TX = NTHREADS / TY;    // thread columns over positions
@@ -58,9 +58,9 @@ struct Tile {
     static_assert(TX % 8 == 0 && TY % 4 == 0, "warps are 8 positions x 4 channel rows");
 };
 
-template <int NT, int NTHREADS>
-__global__ void __launch_bounds__(NTHREADS, 384 / NTHREADS) accumulate_kernel(AccParams pr) {
-    using T = Tile<NT, NTHREADS>;
+template <int NT, int NTHREADS, int KC, int NSTAGE, int MINB>
+__global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr) {
+    using T = Tile<NT, NTHREADS, KC, NSTAGE>;
     constexpr int MT = T::MT, TX = T::TX;
     extern __shared__ __align__(16) uint32_t smem[];
 
@@ -109,11 +109,17 @@ __global__ void __launch_bounds__(NTHREADS, 384 / NTHREADS) accumulate_kernel(Ac
             const int rows = min(KC, pr.K - k0);
             const int32_t *aoff = pr.aoff + ld_g * pr.K + k0;
             const uint32_t *asrc = pr.as + ld_p * pr.pack_words;
+            // Rows past the end of the group are zero-filled: a zero activation word contributes
+            // nothing, so the consumer can always run all KC rows of a stage, fully unrolled.
 #pragma unroll
             for (int j = 0; j < MPT; j++) {
                 const int mcol = (t % MT) + j * NTHREADS;
-                for (int r = r0; r < rows; r += RSTEP)
-                    cp_async4(a_s + (uint32_t)(r * MT + mcol) * 4, asrc + abase[j] + __ldg(aoff + r));
+#pragma unroll
+                for (int i = 0; i < KC / RSTEP; i++) {
+                    const int r = r0 + i * RSTEP;
+                    const bool v = r < rows;
+                    cp_async4(a_s + (uint32_t)(r * MT + mcol) * 4, asrc + abase[j] + (v ? __ldg(aoff + r) : 0), v);
+                }
             }
             // weights: `rows` rows of NT*2 words = NT/2 16-byte chunks each
             constexpr int CPR = NT / 2;
@@ -150,11 +156,10 @@ __global__ void __launch_bounds__(NTHREADS, 384 / NTHREADS) accumulate_kernel(Ac
         const int buf = s % NSTAGE;
         const uint32_t *a_s = smem + (size_t)buf * T::STAGE_WORDS;
         const uint32_t *w_s = a_s + T::A_WORDS;
-        const int rows = min(KC, pr.K - cs_c * KC);
         const uint4 *a4 = (const uint4 *)a_s + tx;
         const uint4 *w4 = (const uint4 *)w_s + ty * 2;
-#pragma unroll 4
-        for (int r = 0; r < rows; r++) {
+#pragma unroll
+        for (int r = 0; r < KC; r++) {
             const uint4 a_lo = a4[r * (MT / 4)];
             const uint4 a_hi = a4[r * (MT / 4) + MT / 8];
             const uint4 w_a = w4[r * (NT / 2)];
@@ -203,14 +208,14 @@ __global__ void __launch_bounds__(NTHREADS, 384 / NTHREADS) accumulate_kernel(Ac
     }
 }
 
-template <int NT, int NTHREADS>
+template <int NT, int NTHREADS, int KC = 16, int NSTAGE = 4, int MINB = 384 / NTHREADS>
 static int launch_tile(const Geometry &g, AccParams pr, cudaStream_t s) {
-    using T = Tile<NT, NTHREADS>;
+    using T = Tile<NT, NTHREADS, KC, NSTAGE>;
     static bool configured[64] = {};
     int dev = 0;
     GEO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_kernel<NT, NTHREADS>,
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_kernel<NT, NTHREADS, KC, NSTAGE, MINB>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
         configured[dev] = true;
     }
@@ -224,7 +229,7 @@ static int launch_tile(const Geometry &g, AccParams pr, cudaStream_t s) {
     pr.splits = (int)splits;
     grid.z = (unsigned)splits;
     if (splits > 1) GEO_CUDA_CHECK(cudaMemsetAsync(pr.out, 0, (size_t)g.M * g.O * sizeof(int32_t), s));
-    accumulate_kernel<NT, NTHREADS><<<grid, NTHREADS, T::SMEM, s>>>(pr);
+    accumulate_kernel<NT, NTHREADS, KC, NSTAGE, MINB><<<grid, NTHREADS, T::SMEM, s>>>(pr);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -238,10 +243,13 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
     pr.pack_words = g.C * g.Hp * g.Wp;
     pr.img_words = g.P * pr.pack_words;
     pr.splits = 1;
+    // Long groups use 32-member stages (half as many barriers per LOP3); short ones 16-member
+    // stages, because a stage is always executed in full and its zero-filled tail rows are wasted.
+    const bool long_groups = g.K >= 64;
     switch (g.NT) {
     case 16: return g.M <= 2048 ? launch_tile<16, 64>(g, pr, s) : launch_tile<16, 128>(g, pr, s);
-    case 32: return launch_tile<32, 128>(g, pr, s);
-    default: return launch_tile<64, 128>(g, pr, s);
+    case 32: return long_groups ? launch_tile<32, 128, 32, 3>(g, pr, s) : launch_tile<32, 128>(g, pr, s);
+    default: return long_groups ? launch_tile<64, 128, 32, 3>(g, pr, s) : launch_tile<64, 128>(g, pr, s);
     }
 }
 

@@ -275,3 +275,68 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
 }
 
 }  // extern "C"
+
+// ---- 2x2 average pooling followed by hardtanh(0, 1) ------------------------------------------------
+// The activation between SC layers (network.py:168-184: x = tanh(pool(x)) with nn.AvgPool2d(2) and
+// nn.Hardtanh(0, 1)) as one pass in each direction.  Backward: the gradient passes where the pooled
+// value lies strictly inside (0, 1) and is spread evenly over the 2x2 window.
+namespace geo {
+namespace {
+
+__global__ void __launch_bounds__(256) pool_act_fwd_kernel(int planes, int H, int W, const float *__restrict__ x,
+                                                           float *__restrict__ y) {
+    const int Ho = H / 2, Wo = W / 2;
+    const long long total = (long long)planes * Ho * Wo;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const int ox = (int)(i % Wo), oy = (int)((i / Wo) % Ho);
+        const long long p = i / ((long long)Wo * Ho);
+        const float *s = x + (p * H + 2 * oy) * W + 2 * ox;
+        // same association as at::avg_pool2d: sum the window, then divide by its size
+        const float v = (s[0] + s[1] + s[W] + s[W + 1]) / 4.0f;
+        y[i] = fminf(fmaxf(v, 0.0f), 1.0f);
+    }
+}
+
+__global__ void __launch_bounds__(256) pool_act_bwd_kernel(int planes, int H, int W, const float *__restrict__ x,
+                                                           const float *__restrict__ gy, float *__restrict__ gx) {
+    const long long total = (long long)planes * H * W;
+    const int Ho = H / 2, Wo = W / 2;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const int xx = (int)(i % W), yy = (int)((i / W) % H);
+        const long long p = i / ((long long)W * H);
+        const int oy = yy >> 1, ox = xx >> 1;
+        float g = 0.0f;
+        if (oy < Ho && ox < Wo) {   // a trailing odd row / column is not covered by any window
+            const float *s = x + (p * H + 2 * oy) * W + 2 * ox;
+            const float v = (s[0] + s[1] + s[W] + s[W + 1]) / 4.0f;
+            if (v > 0.0f && v < 1.0f) g = gy[(p * Ho + oy) * Wo + ox] * 0.25f;
+        }
+        gx[i] = g;
+    }
+}
+
+}  // namespace
+}  // namespace geo
+
+extern "C" {
+
+int geo_sc_pool_act_forward(int planes, int height, int width, const float *x, float *y, void *stream) {
+    if (planes < 1 || height < 2 || width < 2) return fail(GEO_SC_ERR_SHAPE, "planes %d height %d width %d", planes, height, width);
+    if (!x || !y) return fail(GEO_SC_ERR_NULL, "x or y is NULL");
+    const long long total = (long long)planes * (height / 2) * (width / 2);
+    pool_act_fwd_kernel<<<bn_grid(total), 256, 0, (cudaStream_t)stream>>>(planes, height, width, x, y);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int geo_sc_pool_act_backward(int planes, int height, int width, const float *x, const float *grad_y, float *grad_x,
+                             void *stream) {
+    if (planes < 1 || height < 2 || width < 2) return fail(GEO_SC_ERR_SHAPE, "planes %d height %d width %d", planes, height, width);
+    if (!x || !grad_y || !grad_x) return fail(GEO_SC_ERR_NULL, "x, grad_y or grad_x is NULL");
+    const long long total = (long long)planes * height * width;
+    pool_act_bwd_kernel<<<bn_grid(total), 256, 0, (cudaStream_t)stream>>>(planes, height, width, x, grad_y, grad_x);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+}  // extern "C"

@@ -75,3 +75,23 @@ class BatchNorm1d_fixed(nn.BatchNorm1d):
 
     def forward(self, x):
         return _BatchNormFixed.apply(x, self.weight if self.affine else None, self.bias if self.affine else None, self)
+
+
+class _PoolHardtanh(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return ops.pool_act_forward(x).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        (x,) = ctx.saved_tensors
+        return ops.pool_act_backward(x, grad_y).to(x.dtype)
+
+
+class AvgPool2Hardtanh(nn.Module):
+    """``nn.Hardtanh(0, 1)(nn.AvgPool2d(2)(x))`` -- the activation between the reference's SC layers
+    (network.py:168-184) -- as one native pass in each direction."""
+
+    def forward(self, x):
+        return _PoolHardtanh.apply(x)

@@ -39,6 +39,7 @@ class CONV_tiny_add_partial(nn.Module):
         self.fc1 = layers.Conv2d_Add_Partial(64, num_classes, kernel_size=4, padding=0, bias=False)
         self.tanh = nn.Hardtanh(0, 1)
         self.pool = nn.AvgPool2d(2)
+        self.pool_tanh = layers.AvgPool2Hardtanh()   # pool followed by tanh, fused
         self.err = [7, 7, 7, 7]
         self.z_unit = [3, 3, 4, 4]
         self.load_unit = [2, 2, 2, 2]
@@ -66,8 +67,9 @@ class CONV_tiny_add_partial(nn.Module):
         for i, (conv, bn) in enumerate(((self.conv1, self.bn1), (self.conv2, self.bn2), (self.conv3, self.bn3))):
             x = bn(self._sc(conv, x, i))
             if self.relu:
-                x = F.relu(x)
-            x = self.tanh(self.pool(x))
+                x = self.tanh(self.pool(F.relu(x)))
+            else:
+                x = self.pool_tanh(x)
         x = self._sc(self.fc1, x, 3).view(-1, self.num_classes)
         return self.bn4(x)  # BN at the output stabilises training (network.py:188-189)
 
@@ -96,7 +98,7 @@ class VGG11_add_partial(nn.Module):
         self.bnf2 = layers.BatchNorm2d_fixed(512)
         self.bn_out = layers.BatchNorm1d_fixed(num_classes)
         self.tanh = nn.Hardtanh(0, 1)
-        self.pool = nn.AvgPool2d(2)
+        self.pool_tanh = layers.AvgPool2Hardtanh()
         n = len(self.WIDTHS) + 3
         self.err = [7] * n
         self.z_unit = [4] * n
@@ -116,9 +118,7 @@ class VGG11_add_partial(nn.Module):
     def forward(self, x, target=None):
         for i, (conv, bn) in enumerate(zip(self.convs, self.bns)):
             x = bn(self._sc(conv, x, i))
-            if i in self.POOL_AFTER:
-                x = self.pool(x)
-            x = self.tanh(x)
+            x = self.pool_tanh(x) if i in self.POOL_AFTER else self.tanh(x)
         n = len(self.convs)
         x = self.tanh(self.bnf1(self._sc(self.fc1, x, n)))
         x = self.tanh(self.bnf2(self._sc(self.fc2, x, n + 1)))

@@ -240,6 +240,32 @@ def bn_fixed_backward(x, grad_out, weight, mean, invstd, training, need_affine=T
     return gx, gw, gb
 
 
+def pool_act_forward(x):
+    """hardtanh(avg_pool2d(x, 2), 0, 1) for x [B,C,H,W]."""
+    _require_cuda(x)
+    xc = x.detach().to(torch.float32).contiguous()
+    B, C, H, W = xc.shape
+    with torch.cuda.device(xc.device):
+        y = torch.empty((B, C, H // 2, W // 2), dtype=torch.float32, device=xc.device)
+        check(_lib.lib().geo_sc_pool_act_forward(B * C, H, W, xc.data_ptr(), y.data_ptr(), _stream_ptr(xc.device)),
+              "geo_sc_pool_act_forward")
+    STATS.launches += 1
+    return y
+
+
+def pool_act_backward(x, grad_y):
+    _require_cuda(x, grad_y)
+    xc = x.detach().to(torch.float32).contiguous()
+    gy = grad_y.detach().to(torch.float32).contiguous()
+    B, C, H, W = xc.shape
+    with torch.cuda.device(xc.device):
+        gx = torch.empty_like(xc)
+        check(_lib.lib().geo_sc_pool_act_backward(B * C, H, W, xc.data_ptr(), gy.data_ptr(), gx.data_ptr(),
+                                                  _stream_ptr(xc.device)), "geo_sc_pool_act_backward")
+    STATS.launches += 1
+    return gx
+
+
 def act_streams_canonical(buf, desc):
     """View the activation-stream buffer as int32 [B,C,Hp,Wp,P] (the oracle's layout)."""
     P = (desc.bit_length + 31) // 32

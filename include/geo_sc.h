@@ -193,6 +193,15 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
                              const float *save_invstd_device, float *grad_x_device, float *grad_weight_device,
                              float *grad_bias_device, void *scratch_device, size_t scratch_bytes, void *stream);
 
+/* 2x2 average pooling (stride 2, a trailing odd row or column is dropped) followed by
+ * hardtanh(0, 1): the activation the reference puts between SC layers (network.py:168-184,
+ * nn.AvgPool2d(2) then nn.Hardtanh(0,1)), one pass per direction.  x is [planes][height][width]
+ * (planes = batch * channels), y [planes][height/2][width/2].  The backward pass recomputes the
+ * pooled value from x; the gradient passes where it lies strictly inside (0, 1). */
+int geo_sc_pool_act_forward(int planes, int height, int width, const float *x_device, float *y_device, void *stream);
+int geo_sc_pool_act_backward(int planes, int height, int width, const float *x_device, const float *grad_y_device,
+                             float *grad_x_device, void *stream);
+
 /* ---- host mirror of the stream generator ------------------------------------------------
  * Runs on the CPU with the same pattern tables and loading plan the kernels use, for one
  * integer level `value` in [0, bit_length): seed = (seed_base + seed_index) mod (L-1) + 1

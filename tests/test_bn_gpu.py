@@ -68,3 +68,20 @@ def test_bn_fixed_matches_reference_formulation(cuda_device, shape, training, af
         assert torch.allclose(m.bias.grad.cpu(), b_ref.grad, rtol=1e-4, atol=1e-5 * b_ref.grad.abs().max().item())
     assert torch.allclose(m.running_mean.cpu(), rm, rtol=1e-5, atol=1e-6)
     assert torch.allclose(m.running_var.cpu(), rv, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("shape", [(8, 5, 12, 12), (3, 4, 7, 9), (256, 32, 32, 32)])
+def test_pool_hardtanh_matches_pytorch(cuda_device, shape):
+    from geo_b200 import layers
+
+    g = torch.Generator().manual_seed(shape[2])
+    x = torch.rand(*shape, generator=g) * 2.4 - 0.7
+    go = torch.randn(shape[0], shape[1], shape[2] // 2, shape[3] // 2, generator=g)
+    xr = x.clone().requires_grad_(True)
+    yr = F.hardtanh(F.avg_pool2d(xr, 2), 0, 1)
+    yr.backward(go)
+    xd = x.to(cuda_device).requires_grad_(True)
+    y = layers.AvgPool2Hardtanh()(xd)
+    y.backward(go.to(cuda_device))
+    assert torch.allclose(y.detach().cpu(), yr.detach(), rtol=0, atol=1e-7)
+    assert torch.allclose(xd.grad.cpu(), xr.grad, rtol=0, atol=1e-7)
