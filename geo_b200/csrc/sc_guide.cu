@@ -19,6 +19,7 @@
 //   guide_dgrad_kernel   : conv of D with flipped w     M = input pixels, N = c_in block, K = ky*kx*2*c_out
 // D layout: [group][polarity][c_out_padded][position], position = (b*Ho + oy)*Wo + ox.
 #include "sc_common.h"
+#include "sc_guide_mma.h"
 
 namespace geo {
 
@@ -134,6 +135,7 @@ struct FwdParams {
     float *D;           // [G][2][Opad][M] = gout * exp(-y)
     int M, O, Opad, HoWo, Wo, Wp, K, img;
     int vec_ok;         // M and Ho*Wo multiples of 4 and gout 16-byte aligned: 4 positions per access
+    const int *inexact; // when set: run only if *inexact != 0 (otherwise the tensor-core kernel did the work)
 };
 
 template <int NT, int NTHREADS>
@@ -145,6 +147,7 @@ __global__ void __launch_bounds__(NTHREADS) guide_forward_kernel(FwdParams pr) {
     constexpr int WX = TX / 8;
     const int tx = (warp % WX) * 8 + (lane & 7), ty = (warp / WX) * 4 + (lane >> 3);
     const int m0 = blockIdx.x * MT, o0 = blockIdx.y * NT, g = blockIdx.z;
+    if (pr.inexact && *pr.inexact == 0) return;
 
     constexpr int MPT = MT > NTHREADS ? MT / NTHREADS : 1;
     constexpr int RSTEP = NTHREADS > MT ? NTHREADS / MT : 1;
@@ -603,13 +606,14 @@ int grid1d(long long total) {
 
 // ---- buffer plan -------------------------------------------------------------------------------------
 struct GuidePlan {
-    size_t d_bytes, apad_bytes, aoff_bytes, wf_bytes, wd_bytes, partial_bytes;
+    size_t d_bytes, apad_bytes, aoff_bytes, wf_bytes, wd_bytes, partial_bytes, mma_bytes;
     int S, slice_len, KT;
-    size_t total() const { return d_bytes + apad_bytes + aoff_bytes + wf_bytes + wd_bytes + partial_bytes; }
+    size_t total() const { return d_bytes + apad_bytes + aoff_bytes + wf_bytes + wd_bytes + partial_bytes + mma_bytes; }
 };
 
-GuidePlan guide_plan(const GuideDims &d) {
+GuidePlan guide_plan(const GuideDims &d, const Geometry &g) {
     GuidePlan p;
+    p.mma_bytes = mma_scratch_bytes(g);
     p.d_bytes = align_up((size_t)d.G * d.N2 * d.M * 4, 256);
     p.apad_bytes = align_up((size_t)d.B * d.C * d.Hp * d.Wp * 4, 256);
     p.aoff_bytes = align_up((size_t)d.G * d.K * 4, 256);
@@ -707,7 +711,7 @@ int geo_sc_guide_backward_bytes(const geo_sc_conv_desc *desc, size_t *scratch_by
         return fail(GEO_SC_ERR_TOO_LARGE, "guide tensors exceed 31-bit indexing (groups %d x channels %d x positions %d)",
                     d.G, d.N2, d.M);
     if (!scratch_bytes) return fail(GEO_SC_ERR_NULL, "scratch_bytes is NULL");
-    *scratch_bytes = guide_plan(d).total();
+    *scratch_bytes = guide_plan(d, g).total();
     return GEO_SC_OK;
 }
 
@@ -720,7 +724,7 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
     const GuideDims d = guide_dims(g);
     if ((long long)d.G * d.N2 * d.M > (1LL << 31) - 1 || (long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad > (1LL << 31) - 1)
         return fail(GEO_SC_ERR_TOO_LARGE, "guide tensors exceed 31-bit indexing");
-    const GuidePlan p = guide_plan(d);
+    const GuidePlan p = guide_plan(d, g);
     if (scratch_bytes < p.total() || ((uintptr_t)scratch & 255))
         return fail(GEO_SC_ERR_WORKSPACE, "guide scratch holds %zu bytes, %zu needed (256-byte aligned)", scratch_bytes,
                     p.total());
@@ -733,8 +737,15 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
     float *wf = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes);
     float *wd = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes);
     float *partial = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes + p.wd_bytes);
+    void *mma_scratch = base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes + p.wd_bytes + p.partial_bytes;
 
-    // 1. D = gout * exp(-y) for every group and polarity
+    // 1. D = gout * exp(-y) for every group and polarity: on the tensor cores when every input is
+    //    bf16-exact (decided on the device), else with the FFMA kernel
+    int *inexact = nullptr;
+    if (mma_eligible(g)) {
+        rc = launch_mma_forward(g, act, weight, grad_out, D, mma_scratch, &inexact, s);
+        if (rc) return rc;
+    }
     pad_act_kernel<<<grid1d((long long)d.B * d.C * d.Hp * d.Wp), 256, 0, s>>>(d, act, apad);
     guide_prep_fwd_kernel<<<grid1d((long long)d.G * d.K * d.Opad), 256, 0, s>>>(d, weight, wf, aoff);
     GEO_CUDA_CHECK(cudaGetLastError());
@@ -742,6 +753,7 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
     fp.apad = apad; fp.wf = wf; fp.aoff = aoff; fp.gout = grad_out; fp.D = D;
     fp.M = d.M; fp.O = d.O; fp.Opad = d.Opad; fp.HoWo = d.HoWo; fp.Wo = d.Wo; fp.Wp = d.Wp; fp.K = d.K;
     fp.img = d.C * d.Hp * d.Wp;
+    fp.inexact = inexact;
     fp.vec_ok = (d.M % 4 == 0) && (d.HoWo % 4 == 0) && (((uintptr_t)grad_out & 15) == 0);
     switch (g.NT) {
     case 16: rc = launch_guide_fwd<16, 128>(d, fp, s); break;

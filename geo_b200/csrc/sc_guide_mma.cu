@@ -1,0 +1,285 @@
+// Tensor-core path of the float guide (see sc_guide.cu for the mathematics).
+//
+// Activations and weights that went through the layers' 7-bit quantisation (utils_class.py:32-33)
+// are multiples of 1/128 below 1 in magnitude, hence exactly representable in bf16, and products of
+// two such values are exact in fp32.  For such inputs the guide's convolutions can run on the
+// tensor cores (mma.sync m16n8k16, bf16 operands, fp32 accumulation) without changing the result
+// beyond the order of the fp32 additions.  Whether the inputs qualify is decided on the device:
+// the preparation kernels raise a flag when they meet a value that bf16 cannot hold, and the
+// tensor-core kernels and the FFMA kernels of sc_guide.cu each return at once when the flag says
+// the other family is in charge -- no host synchronisation, so the sequence can live in a CUDA graph.
+//
+// Tensor-core accumulation rounds toward zero; to keep that bias out of long sums, the MMA
+// accumulators are flushed into ordinary fp32 registers (round-to-nearest adds) every few steps.
+//
+// Layouts: activations NHWC bf16 [B][Hp][Wp][Cp] (Cp = c_in rounded up to 8, zero filled), so that
+// the members of a filter tap are 16-byte chunks; weights [group][2*c_out_padded][Kp] with the
+// member index k' = tap * Cp + c contiguous.  Only the modes whose groups are whole filter taps
+// over all channels use this path (1d_bin: the taps of one filter column; full_or: all taps).
+#include <cuda_bf16.h>
+
+#include "sc_common.h"
+#include "sc_guide_mma.h"
+
+namespace geo {
+
+namespace {
+
+__device__ __forceinline__ void cp16z(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cpa_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Byte offset of 16-byte chunk `chunk` (0..3) of row `row` in a tile whose rows are 64 bytes
+// (32 bf16); the XOR keeps the 8 rows of an ldmatrix 8x8 block in 8 different bank groups.
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)(row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4));
+}
+
+// ---- preparation --------------------------------------------------------------------------------
+// NCHW fp32 -> padded NHWC bf16, raising *inexact if a value is not representable in bf16.
+__global__ void __launch_bounds__(256) mma_prep_act_kernel(MmaDims d, const float *__restrict__ act,
+                                                           __nv_bfloat16 *__restrict__ out, int *inexact) {
+    const long long total = (long long)d.B * d.Hp * d.Wp * d.Cp;
+    bool bad = false;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const int c = (int)(i % d.Cp);
+        long long r = i / d.Cp;
+        const int x = (int)(r % d.Wp); r /= d.Wp;
+        const int y = (int)(r % d.Hp);
+        const int b = (int)(r / d.Hp);
+        const int yi = y - d.ph, xi = x - d.pw;
+        float v = 0.0f;
+        if (c < d.C && yi >= 0 && yi < d.H && xi >= 0 && xi < d.W) v = act[(((size_t)b * d.C + c) * d.H + yi) * d.W + xi];
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        bad |= (__bfloat162float(h) != v);
+        out[i] = h;
+    }
+    if (bad) atomicOr(inexact, 1);
+}
+
+// Wb[g][n2][Kp] bf16, n2 = pol * Opad + o, k' = tap * Cp + c (taps of group g in order), zero padded.
+__global__ void __launch_bounds__(256) mma_prep_weight_kernel(MmaDims d, const float *__restrict__ w,
+                                                              __nv_bfloat16 *__restrict__ wb, int *inexact) {
+    const long long total = (long long)d.G * d.N2 * d.Kp;
+    bool bad = false;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const int kp = (int)(i % d.Kp);
+        const int n2 = (int)((i / d.Kp) % d.N2), g = (int)(i / ((long long)d.Kp * d.N2));
+        const int tap = kp / d.Cp, c = kp % d.Cp;
+        const int pol = n2 / d.Opad, o = n2 % d.Opad;
+        float v = 0.0f;
+        if (tap < d.taps && c < d.C && o < d.O) {
+            int ky, kx;
+            if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+            else { ky = tap / d.K3; kx = tap % d.K3; }
+            const float x = w[(((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx];
+            v = pol == 0 ? fminf(fmaxf(x, 0.0f), 100.0f) : -fminf(fmaxf(x, -100.0f), 0.0f);
+        }
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        bad |= (__bfloat162float(h) != v);
+        wb[i] = h;
+    }
+    if (bad) atomicOr(inexact, 1);
+}
+
+// ---- D = gout * exp(-conv) on the tensor cores -------------------------------------------------------
+// CTA: 128 positions x 64 columns (polarity, channel), 4 warps of 32 positions each.
+constexpr int MK = 32;        // members per stage (two k16 steps)
+constexpr int MSTAGE = 4;
+constexpr int MFLUSH = 8;     // k16 steps between flushes of the MMA accumulators
+
+__global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
+                                                          const __nv_bfloat16 *__restrict__ wb,
+                                                          const float *__restrict__ gout, float *__restrict__ D,
+                                                          const int *inexact) {
+    if (*inexact) return;   // the FFMA kernels handle inputs that bf16 cannot hold
+    constexpr int A_BYTES = 128 * 64, B_BYTES = 64 * 64, ST_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ __align__(128) unsigned char msm[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int m0 = blockIdx.x * 128, n0 = blockIdx.y * 64, g = blockIdx.z;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(msm);
+
+    // gather assignment: thread t copies chunk (t & 3) of rows (t >> 2) + 32 * i, i < 4
+    const int gchunk = t & 3;
+    long long rbase[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int m = m0 + (t >> 2) + 32 * i;
+        if (m >= d.M) m = d.M - 1;
+        const int b = m / d.HoWo, rem = m % d.HoWo;
+        const int oy = rem / d.Wo, ox = rem % d.Wo;
+        rbase[i] = (((long long)b * d.Hp + oy) * d.Wp + ox) * d.Cp;
+    }
+    const int kx_g = d.mode == GEO_SC_MODE_1D ? g : 0;
+    const int nchunks = d.Kp / MK;
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < nchunks) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % MSTAGE) * ST_BYTES, b_s = a_s + A_BYTES;
+            const int kp = ld * MK + gchunk * 8;     // first member of this thread's chunk
+            const int tap = kp / d.Cp, c = kp % d.Cp;
+            const bool kv = tap < d.taps;
+            int ky, kx;
+            if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = kx_g; }
+            else { ky = tap / d.K3; kx = tap % d.K3; }
+            const long long koff = kv ? ((long long)ky * d.Wp + kx) * d.Cp + c : 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = (t >> 2) + 32 * i;
+                cp16z(a_s + swz(row, gchunk), apad + rbase[i] + koff, kv);
+            }
+            // weights: 64 rows (columns n) x 4 chunks
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int row = (t >> 2) + 32 * i;
+                const __nv_bfloat16 *src = wb + ((size_t)g * d.N2 + n0 + row) * d.Kp + ld * MK + gchunk * 8;
+                cp16z(b_s + swz(row, gchunk), src, true);
+            }
+            ld++;
+        }
+        cpa_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < MSTAGE - 1; s++) issue();
+
+    float acc[2][8][4], sum[2][8][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 8; ni++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) { acc[mi][ni][q] = 0.f; sum[mi][ni][q] = 0.f; }
+
+    int since_flush = 0;
+    for (int s = 0; s < nchunks; s++) {
+        cpa_wait<MSTAGE - 2>();
+        __syncthreads();
+        issue();
+        const uint32_t a_s = sbase + (uint32_t)(s % MSTAGE) * ST_BYTES, b_s = a_s + A_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                // matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+                const int row = warp * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldsm_x4(af[mi], a_s + swz(row, ks * 2 + (lane >> 4)));
+            }
+#pragma unroll
+            for (int np = 0; np < 4; np++) {
+                // two n8 tiles per ldmatrix: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+                uint32_t bf[4];
+                const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldsm_x4(bf, b_s + swz(row, ks * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+                for (int mi = 0; mi < 2; mi++) {
+                    mma_bf16(acc[mi][np * 2 + 0], af[mi], bf[0], bf[1]);
+                    mma_bf16(acc[mi][np * 2 + 1], af[mi], bf[2], bf[3]);
+                }
+            }
+        }
+        since_flush += 2;
+        if (since_flush >= MFLUSH || s == nchunks - 1) {
+            since_flush = 0;
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 8; ni++)
+#pragma unroll
+                    for (int q = 0; q < 4; q++) { sum[mi][ni][q] += acc[mi][ni][q]; acc[mi][ni][q] = 0.f; }
+        }
+    }
+    cpa_wait<0>();
+
+    // epilogue: accumulator (mi, ni, q): row = lane/4 + 8*(q>>1), column = ni*8 + (lane%4)*2 + (q&1)
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int hr = 0; hr < 2; hr++) {
+            const int m = m0 + warp * 32 + mi * 16 + (lane >> 2) + hr * 8;
+            if (m >= d.M) continue;
+            const int b = m / d.HoWo, rem = m % d.HoWo;
+#pragma unroll
+            for (int ni = 0; ni < 8; ni++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int n2 = n0 + ni * 8 + (lane & 3) * 2 + e;
+                    const int o = n2 % d.Opad;
+                    const float go = o < d.O ? __ldg(gout + ((size_t)b * d.O + o) * d.HoWo + rem) : 0.0f;
+                    D[((size_t)g * d.N2 + n2) * d.M + m] = go * expf(-sum[mi][ni][hr * 2 + e]);
+                }
+        }
+}
+
+int grid1(long long total) {
+    long long b = (total + 255) / 256;
+    return (int)(b < 148 * 16 ? (b > 0 ? b : 1) : 148 * 16);
+}
+
+}  // namespace
+
+bool mma_eligible(const Geometry &g) {
+    // whole-tap groups only, and column tiles of 64 need at least 32 padded output channels
+    return (g.mode == GEO_SC_MODE_1D || g.mode == GEO_SC_MODE_FULL_OR) && g.Opad % 32 == 0;
+}
+
+MmaDims mma_dims(const Geometry &g) {
+    MmaDims d;
+    d.B = g.B; d.C = g.C; d.H = g.H; d.W = g.W; d.ph = g.pad_h; d.pw = g.pad_w; d.Hp = g.Hp; d.Wp = g.Wp;
+    d.O = g.O; d.K2 = g.K2; d.K3 = g.K3; d.Ho = g.Ho; d.Wo = g.Wo; d.HoWo = g.Ho * g.Wo;
+    d.mode = g.mode; d.G = g.G; d.Opad = g.Opad; d.N2 = 2 * g.Opad; d.M = (int)g.M;
+    d.Cp = (g.C + 7) / 8 * 8;
+    d.taps = g.mode == GEO_SC_MODE_1D ? g.K2 : g.K2 * g.K3;
+    d.Kp = (d.taps * d.Cp + MK - 1) / MK * MK;
+    return d;
+}
+
+size_t mma_scratch_bytes(const Geometry &g) {
+    if (!mma_eligible(g)) return 0;
+    const MmaDims d = mma_dims(g);
+    return align_up((size_t)d.B * d.Hp * d.Wp * d.Cp * 2, 256) + align_up((size_t)d.G * d.N2 * d.Kp * 2, 256) + 256;
+}
+
+// Prepares the bf16 operands and the exactness flag, then computes D (fp32, [G][N2][M]) if exact.
+int launch_mma_forward(const Geometry &g, const float *act, const float *weight, const float *gout, float *D,
+                       void *scratch, int **flag_out, cudaStream_t s) {
+    const MmaDims d = mma_dims(g);
+    char *base = (char *)scratch;
+    int *flag = (int *)base;
+    __nv_bfloat16 *apad = (__nv_bfloat16 *)(base + 256);
+    __nv_bfloat16 *wb = (__nv_bfloat16 *)(base + 256 + align_up((size_t)d.B * d.Hp * d.Wp * d.Cp * 2, 256));
+    GEO_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int), s));
+    mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * d.Cp), 256, 0, s>>>(d, act, apad, flag);
+    mma_prep_weight_kernel<<<grid1((long long)d.G * d.N2 * d.Kp), 256, 0, s>>>(d, weight, wb, flag);
+    constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64);
+    static bool done[64] = {};
+    int dev = 0;
+    GEO_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(mma_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+    dim3 grid((d.M + 127) / 128, d.N2 / 64, d.G);
+    mma_forward_kernel<<<grid, 128, smem, s>>>(d, apad, wb, gout, D, flag);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    *flag_out = flag;
+    return GEO_SC_OK;
+}
+
+}  // namespace geo

@@ -182,7 +182,7 @@ def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True)
                                                ga.data_ptr() if need_act else None,
                                                gw.data_ptr() if need_weight else None, scratch.data_ptr(),
                                                scratch.numel(), _stream_ptr(dev)), "geo_sc_guide_backward")
-    STATS.launches += 3 + (2 if need_weight else 0) + (2 if need_act else 0)
+    STATS.launches += 6 + (2 if need_weight else 0) + (2 if need_act else 0)
     return ga, gw
 
 
