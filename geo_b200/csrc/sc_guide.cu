@@ -263,6 +263,7 @@ struct WgradParams {
     float *partial;     // [S][G][K][N2]
     int M, N2, HoWo, Wo, Wp, K, G, img;
     int slice_len;      // positions per slice, multiple of WMC
+    const int *inexact; // when set: run only if *inexact != 0
 };
 
 template <int KT>
@@ -271,6 +272,7 @@ __global__ void __launch_bounds__(KT, KT <= 128 ? 3 : 2) guide_wgrad_kernel(Wgra
     constexpr int KTH = KT / 8;
     constexpr int A_F = KT * WRS, D_F = WNT * WRS, ST_F = A_F + D_F;
     extern __shared__ __align__(16) float wsm[];
+    if (pr.inexact && *pr.inexact == 0) return;
     const int t = threadIdx.x;
     const int kth = t % KTH, nth = t / KTH;
     const int g = blockIdx.z / ((pr.N2 + WNT - 1) / WNT), nt = blockIdx.z % ((pr.N2 + WNT - 1) / WNT);
@@ -375,6 +377,7 @@ __global__ void __launch_bounds__(128) guide_wgrad_smallk_kernel(WgradParams pr)
     constexpr int NTHREADS = 128, KS = 16;
     constexpr int A_F = KS * WRS, D_F = WNT * WRS, ST_F = A_F + D_F;
     extern __shared__ __align__(16) float wsm[];
+    if (pr.inexact && *pr.inexact == 0) return;
     const int t = threadIdx.x;
     const int ks = t % KS, nth = t / KS;
     const int ntiles = (pr.N2 + WNT - 1) / WNT;
@@ -459,7 +462,9 @@ __global__ void __launch_bounds__(128) guide_wgrad_smallk_kernel(WgradParams pr)
 
 // grad_w[o][c][ky][kx] = [w>=0] * sum_s partial[s][g][k][o] + [w<=0] * sum_s partial[s][g][k][Opad+o]
 __global__ void __launch_bounds__(256) guide_wgrad_reduce_kernel(GuideDims d, int S, const float *__restrict__ partial,
-                                                                 const float *__restrict__ w, float *__restrict__ gw) {
+                                                                 const float *__restrict__ w, float *__restrict__ gw,
+                                                                 const int *inexact) {
+    if (inexact && *inexact == 0) return;
     const long long total = (long long)d.G * d.K * d.O;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int o = (int)(i % d.O);
@@ -487,6 +492,7 @@ struct DgradParams {
     const float *wd;   // [J][R][cbpad]
     float *ga;         // [B][C][H][W]
     int M, N2, Ho, Wo, H, W, C, ph, pw, K2, K3, mode, cb, cbpad, Min, R;
+    const int *inexact; // when set: run only if *inexact != 0
 };
 
 template <int NT, int NTHREADS>
@@ -507,6 +513,7 @@ __global__ void __launch_bounds__(NTHREADS) guide_dgrad_kernel(DgradParams pr) {
         ty = t / TX;
     }
     const int m0 = blockIdx.x * MT, c0 = blockIdx.y * NT, j = blockIdx.z;
+    if (pr.inexact && *pr.inexact == 0) return;
     const int HoWo = pr.Ho * pr.Wo, HW = pr.H * pr.W;
 
     int pb[MPT], py[MPT], px[MPT];
@@ -739,11 +746,11 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
     float *partial = (float *)(base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes + p.wd_bytes);
     void *mma_scratch = base + p.d_bytes + p.apad_bytes + p.aoff_bytes + p.wf_bytes + p.wd_bytes + p.partial_bytes;
 
-    // 1. D = gout * exp(-y) for every group and polarity: on the tensor cores when every input is
-    //    bf16-exact (decided on the device), else with the FFMA kernel
+    // Tensor-core path: does the whole backward pass when every input is bf16-exact, which is
+    // decided on the device; the FFMA kernels below then return at once (and vice versa).
     int *inexact = nullptr;
     if (mma_eligible(g)) {
-        rc = launch_mma_forward(g, act, weight, grad_out, D, mma_scratch, &inexact, s);
+        rc = launch_mma_backward(g, act, weight, grad_out, grad_act, grad_weight, mma_scratch, &inexact, s);
         if (rc) return rc;
     }
     pad_act_kernel<<<grid1d((long long)d.B * d.C * d.Hp * d.Wp), 256, 0, s>>>(d, act, apad);
@@ -768,6 +775,7 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
         pr.apad = apad; pr.D = D; pr.aoff = aoff; pr.partial = partial;
         pr.M = d.M; pr.N2 = d.N2; pr.HoWo = d.HoWo; pr.Wo = d.Wo; pr.Wp = d.Wp; pr.K = d.K; pr.G = d.G;
         pr.img = d.C * d.Hp * d.Wp; pr.slice_len = p.slice_len;
+        pr.inexact = inexact;
         switch (p.KT) {
         case 16: {
             constexpr size_t smem = (size_t)WSTAGE * (16 * WRS + WNT * WRS) * 4;
@@ -784,7 +792,7 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
         default: rc = launch_guide_wgrad<192>(d, p, pr, s); break;
         }
         if (rc) return rc;
-        guide_wgrad_reduce_kernel<<<grid1d((long long)d.G * d.K * d.O), 256, 0, s>>>(d, p.S, partial, weight, grad_weight);
+        guide_wgrad_reduce_kernel<<<grid1d((long long)d.G * d.K * d.O), 256, 0, s>>>(d, p.S, partial, weight, grad_weight, inexact);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
     // 3. activation gradient
@@ -796,6 +804,7 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
         pr.M = d.M; pr.N2 = d.N2; pr.Ho = d.Ho; pr.Wo = d.Wo; pr.H = d.H; pr.W = d.W; pr.C = d.C; pr.ph = d.ph; pr.pw = d.pw;
         pr.K2 = d.K2; pr.K3 = d.K3; pr.mode = d.mode; pr.cb = d.cb; pr.cbpad = d.cbpad; pr.Min = d.Min;
         pr.R = d.K2 * d.K3 * d.N2;
+        pr.inexact = inexact;
         if (d.cbpad == 8) rc = launch_guide_dgrad<8, 64>(d, pr, s);
         else if (d.cbpad == 16) rc = launch_guide_dgrad<16, 128>(d, pr, s);
         else if (d.cbpad == 32) rc = launch_guide_dgrad<32, 128>(d, pr, s);

@@ -104,10 +104,19 @@ constexpr int MK = 32;        // members per stage (two k16 steps)
 constexpr int MSTAGE = 4;
 constexpr int MFLUSH = 8;     // k16 steps between flushes of the MMA accumulators
 
+// Splits v into three bf16 terms whose sum reproduces v to 24 bits.
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 &h0, __nv_bfloat16 &h1, __nv_bfloat16 &h2) {
+    h0 = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h0);
+    h1 = __float2bfloat16_rn(r1);
+    h2 = __float2bfloat16_rn(r1 - __bfloat162float(h1));
+}
+
+// Output: Dh[plane][g][m][n2] bf16, plane = term of the 3-way split of D = gout * exp(-y).
 __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
                                                           const __nv_bfloat16 *__restrict__ wb,
-                                                          const float *__restrict__ gout, float *__restrict__ D,
-                                                          const int *inexact) {
+                                                          const float *__restrict__ gout,
+                                                          __nv_bfloat16 *__restrict__ Dh, const int *inexact) {
     if (*inexact) return;   // the FFMA kernels handle inputs that bf16 cannot hold
     constexpr int A_BYTES = 128 * 64, B_BYTES = 64 * 64, ST_BYTES = A_BYTES + B_BYTES;
     extern __shared__ __align__(128) unsigned char msm[];
@@ -215,14 +224,328 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
             const int m = m0 + warp * 32 + mi * 16 + (lane >> 2) + hr * 8;
             if (m >= d.M) continue;
             const int b = m / d.HoWo, rem = m % d.HoWo;
+            const size_t plane = (size_t)d.G * d.M * d.N2;
+            __nv_bfloat16 *row = Dh + ((size_t)g * d.M + m) * d.N2;
 #pragma unroll
-            for (int ni = 0; ni < 8; ni++)
+            for (int ni = 0; ni < 8; ni++) {
+                const int n2 = n0 + ni * 8 + (lane & 3) * 2;
+                __nv_bfloat162 p0, p1, p2;
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    const int n2 = n0 + ni * 8 + (lane & 3) * 2 + e;
-                    const int o = n2 % d.Opad;
+                    const int o = (n2 + e) % d.Opad;
                     const float go = o < d.O ? __ldg(gout + ((size_t)b * d.O + o) * d.HoWo + rem) : 0.0f;
-                    D[((size_t)g * d.N2 + n2) * d.M + m] = go * expf(-sum[mi][ni][hr * 2 + e]);
+                    const float v = go * expf(-sum[mi][ni][hr * 2 + e]);
+                    __nv_bfloat16 h0, h1, h2;
+                    split3(v, h0, h1, h2);
+                    if (e == 0) { p0.x = h0; p1.x = h1; p2.x = h2; }
+                    else { p0.y = h0; p1.y = h1; p2.y = h2; }
+                }
+                *(__nv_bfloat162 *)(row + n2) = p0;
+                *(__nv_bfloat162 *)(row + plane + n2) = p1;
+                *(__nv_bfloat162 *)(row + 2 * plane + n2) = p2;
+            }
+        }
+}
+
+// ---- weight gradient on the tensor cores ----------------------------------------------------------------
+// partial[slice][g][k'][n2] = sum over the slice's positions of a[m, k'] * D[m, n2] (three split terms).
+// CTA: 64 members x 64 columns, 2 warps of 32 members each; a stage holds 32 positions.
+constexpr int WP = 32;        // positions per stage
+constexpr int WSTG = 3;
+
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// rows of 128 bytes (64 bf16), 8 chunks of 16 bytes
+__device__ __forceinline__ uint32_t swz128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+__global__ void __launch_bounds__(64) mma_wgrad_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
+                                                       const __nv_bfloat16 *__restrict__ Dh, float *__restrict__ partial,
+                                                       int slice_len, const int *inexact) {
+    if (*inexact) return;
+    constexpr int A_BYTES = WP * 128, D_BYTES = WP * 128, ST_BYTES = A_BYTES + 3 * D_BYTES;
+    extern __shared__ __align__(128) unsigned char wsm2[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int ntiles = d.N2 / 64;
+    const int g = blockIdx.z / ntiles, n0 = (blockIdx.z % ntiles) * 64;
+    const int k0 = blockIdx.y * 64;
+    const int mbeg = blockIdx.x * slice_len, mend = min(d.M, mbeg + slice_len);
+    const int nst = (mend - mbeg + WP - 1) / WP;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(wsm2);
+    const size_t plane = (size_t)d.G * d.M * d.N2;
+
+    // this thread's chunk of members: tap and channel are fixed for the whole kernel
+    const int gchunk = t & 7;
+    const int kp = k0 + gchunk * 8;
+    const int tap = kp / d.Cp, cch = kp % d.Cp;
+    const bool kvalid = tap < d.taps;
+    int ky, kx;
+    if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+    else { ky = tap / d.K3; kx = tap % d.K3; }
+    const long long koff = kvalid ? ((long long)ky * d.Wp + kx) * d.Cp + cch : 0;
+
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < nst) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % WSTG) * ST_BYTES, d_s = a_s + A_BYTES;
+            const int mc = mbeg + ld * WP;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = (t >> 3) + 8 * i;
+                const int m = mc + row;
+                const bool v = m < mend;
+                const int mm = v ? m : mbeg;
+                const int b = mm / d.HoWo, rem = mm % d.HoWo;
+                const long long rb = (((long long)b * d.Hp + rem / d.Wo) * d.Wp + rem % d.Wo) * d.Cp;
+                cp16z(a_s + swz128(row, gchunk), apad + rb + koff, v && kvalid);
+                const __nv_bfloat16 *src = Dh + ((size_t)g * d.M + mm) * d.N2 + n0 + gchunk * 8;
+#pragma unroll
+                for (int p = 0; p < 3; p++) cp16z(d_s + p * D_BYTES + swz128(row, gchunk), src + p * plane, v);
+            }
+            ld++;
+        }
+        cpa_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < WSTG - 1; s++) issue();
+
+    float acc[2][8][4], sum[2][8][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 8; ni++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) { acc[mi][ni][q] = 0.f; sum[mi][ni][q] = 0.f; }
+
+    int since_flush = 0;
+    for (int s = 0; s < nst; s++) {
+        cpa_wait<WSTG - 2>();
+        __syncthreads();
+        issue();
+        const uint32_t a_s = sbase + (uint32_t)(s % WSTG) * ST_BYTES, d_s = a_s + A_BYTES;
+#pragma unroll
+        for (int ps = 0; ps < 2; ps++) {   // two runs of 16 positions
+            const int p0 = ps * 16;
+            uint32_t af[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                // transposed 8x8 blocks: (m 0-7, k' 0-7), (m 0-7, k' 8-15), (m 8-15, k' 0-7), (m 8-15, k' 8-15)
+                const int row = p0 + (lane & 7) + (lane >> 4) * 8;
+                const int chunk = warp * 4 + mi * 2 + ((lane >> 3) & 1);
+                ldsm_x4_t(af[mi], a_s + swz128(row, chunk));
+            }
+#pragma unroll
+            for (int p = 0; p < 3; p++) {
+#pragma unroll
+                for (int np = 0; np < 4; np++) {
+                    // (m 0-7, n tile 2np), (m 8-15, n tile 2np), (m 0-7, n tile 2np+1), (m 8-15, n tile 2np+1)
+                    uint32_t bf[4];
+                    const int row = p0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    ldsm_x4_t(bf, d_s + p * D_BYTES + swz128(row, np * 2 + (lane >> 4)));
+#pragma unroll
+                    for (int mi = 0; mi < 2; mi++) {
+                        mma_bf16(acc[mi][np * 2 + 0], af[mi], bf[0], bf[1]);
+                        mma_bf16(acc[mi][np * 2 + 1], af[mi], bf[2], bf[3]);
+                    }
+                }
+            }
+        }
+        since_flush += 2;
+        if (since_flush >= MFLUSH || s == nst - 1) {
+            since_flush = 0;
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 8; ni++)
+#pragma unroll
+                    for (int q = 0; q < 4; q++) { sum[mi][ni][q] += acc[mi][ni][q]; acc[mi][ni][q] = 0.f; }
+        }
+    }
+    cpa_wait<0>();
+    float *dst = partial + ((size_t)blockIdx.x * d.G + g) * d.Kp * d.N2;
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int hr = 0; hr < 2; hr++) {
+            const int k = k0 + warp * 32 + mi * 16 + (lane >> 2) + hr * 8;
+            if (k >= d.Kp) continue;
+#pragma unroll
+            for (int ni = 0; ni < 8; ni++) {
+                const int n2 = n0 + ni * 8 + (lane & 3) * 2;
+                *(float2 *)(dst + (size_t)k * d.N2 + n2) = make_float2(sum[mi][ni][hr * 2], sum[mi][ni][hr * 2 + 1]);
+            }
+        }
+}
+
+// grad_w[o][c][ky][kx] = [w>=0] * sum_s partial[s][g][k'][o] + [w<=0] * sum_s partial[s][g][k'][Opad+o]
+__global__ void __launch_bounds__(256) mma_wgrad_reduce_kernel(MmaDims d, int S, const float *__restrict__ partial,
+                                                               const float *__restrict__ w, float *__restrict__ gw,
+                                                               const int *inexact) {
+    if (*inexact) return;
+    const long long total = (long long)d.G * d.taps * d.C * d.O;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const int o = (int)(i % d.O);
+        long long r = i / d.O;
+        const int c = (int)(r % d.C); r /= d.C;
+        const int tap = (int)(r % d.taps), g = (int)(r / d.taps);
+        int ky, kx;
+        if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+        else { ky = tap / d.K3; kx = tap % d.K3; }
+        const int kp = tap * d.Cp + c;
+        const size_t stride = (size_t)d.G * d.Kp * d.N2;
+        const float *p = partial + ((size_t)g * d.Kp + kp) * d.N2;
+        float sp = 0.f, sn = 0.f;
+        for (int s = 0; s < S; s++) {
+            sp += p[s * stride + o];
+            sn += p[s * stride + d.Opad + o];
+        }
+        const size_t wi = (((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx;
+        const float wv = w[wi];
+        gw[wi] = (wv >= 0.f && wv <= 100.f ? sp : 0.f) + (wv <= 0.f && wv >= -100.f ? sn : 0.f);
+    }
+}
+
+// ---- activation gradient on the tensor cores ---------------------------------------------------------------
+// grad_a[pix][c] = sum over taps and columns n2 of D[g(tap)][pos(pix, tap)][n2] * Wd[c][tap*N2 + n2]
+// Wd[c][r] bf16: +w+ for the positive columns, -(w-) for the negative ones, zero padded to Cn channels.
+__global__ void __launch_bounds__(256) mma_prep_wd_kernel(MmaDims d, int Cn, const float *__restrict__ w,
+                                                          __nv_bfloat16 *__restrict__ wd) {
+    const int R = d.K2 * d.K3 * d.N2;
+    const long long total = (long long)Cn * R;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const int r = (int)(i % R), c = (int)(i / R);
+        const int n2 = r % d.N2, tap = r / d.N2, ky = tap / d.K3, kx = tap % d.K3;
+        const int pol = n2 / d.Opad, o = n2 % d.Opad;
+        float v = 0.0f;
+        if (c < d.C && o < d.O) {
+            const float x = w[(((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx];
+            v = pol == 0 ? fminf(fmaxf(x, 0.0f), 100.0f) : fminf(fmaxf(x, -100.0f), 0.0f);
+        }
+        wd[i] = __float2bfloat16_rn(v);
+    }
+}
+
+constexpr int DSTG = 3;
+
+__global__ void __launch_bounds__(128) mma_dgrad_kernel(MmaDims d, int Cn, const __nv_bfloat16 *__restrict__ Dh,
+                                                        const __nv_bfloat16 *__restrict__ wd, float *__restrict__ ga,
+                                                        const int *inexact) {
+    if (*inexact) return;
+    constexpr int A_BYTES = 128 * 64, B_BYTES = 32 * 64, ST_BYTES = 3 * A_BYTES + B_BYTES;
+    extern __shared__ __align__(128) unsigned char dsm2[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int p0 = blockIdx.x * 128, c0 = blockIdx.y * 32;
+    const int HW = d.H * d.W, Min = d.B * HW;
+    const int R = d.K2 * d.K3 * d.N2;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dsm2);
+    const size_t plane = (size_t)d.G * d.M * d.N2;
+
+    const int gchunk = t & 3;
+    int pb[4], py[4], px[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int pix = p0 + (t >> 2) + 32 * i;
+        const bool v = pix < Min;
+        if (!v) pix = 0;
+        const int b = pix / HW, rem = pix % HW;
+        pb[i] = v ? b : -1;
+        py[i] = rem / d.W + d.ph;
+        px[i] = rem % d.W + d.pw;
+    }
+    const int spt = d.N2 / 32;             // stages per tap
+    const int nst = d.K2 * d.K3 * spt;
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < nst) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % DSTG) * ST_BYTES, b_s = a_s + 3 * A_BYTES;
+            const int tap = ld / spt, n2 = (ld % spt) * 32 + gchunk * 8;
+            const int ky = tap / d.K3, kx = tap % d.K3;
+            const int g = d.mode == GEO_SC_MODE_1D ? kx : 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = (t >> 2) + 32 * i;
+                const int oy = py[i] - ky, ox = px[i] - kx;
+                const bool v = pb[i] >= 0 && oy >= 0 && oy < d.Ho && ox >= 0 && ox < d.Wo;
+                const size_t m = v ? (size_t)pb[i] * d.HoWo + oy * d.Wo + ox : 0;
+                const __nv_bfloat16 *src = Dh + ((size_t)g * d.M + m) * d.N2 + n2;
+#pragma unroll
+                for (int p = 0; p < 3; p++) cp16z(a_s + p * A_BYTES + swz(row, gchunk), src + p * plane, v);
+            }
+            {   // weights: 32 rows (channels) x 4 chunks = 128 copies, one per thread
+                const int row = t >> 2;
+                const __nv_bfloat16 *src = wd + (size_t)(c0 + row) * R + (size_t)ld * 32 + gchunk * 8;
+                cp16z(b_s + swz(row, gchunk), src, true);
+            }
+            ld++;
+        }
+        cpa_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < DSTG - 1; s++) issue();
+
+    float acc[2][4][4], sum[2][4][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) { acc[mi][ni][q] = 0.f; sum[mi][ni][q] = 0.f; }
+
+    int since_flush = 0;
+    for (int s = 0; s < nst; s++) {
+        cpa_wait<DSTG - 2>();
+        __syncthreads();
+        issue();
+        const uint32_t a_s = sbase + (uint32_t)(s % DSTG) * ST_BYTES, b_s = a_s + 3 * A_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            uint32_t bf[2][4];
+#pragma unroll
+            for (int np = 0; np < 2; np++) {
+                const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldsm_x4(bf[np], b_s + swz(row, ks * 2 + ((lane >> 3) & 1)));
+            }
+#pragma unroll
+            for (int p = 0; p < 3; p++)
+#pragma unroll
+                for (int mi = 0; mi < 2; mi++) {
+                    uint32_t af[4];
+                    const int row = warp * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    ldsm_x4(af, a_s + p * A_BYTES + swz(row, ks * 2 + (lane >> 4)));
+#pragma unroll
+                    for (int np = 0; np < 2; np++) {
+                        mma_bf16(acc[mi][np * 2 + 0], af, bf[np][0], bf[np][1]);
+                        mma_bf16(acc[mi][np * 2 + 1], af, bf[np][2], bf[np][3]);
+                    }
+                }
+        }
+        since_flush += 2;
+        if (since_flush >= MFLUSH || s == nst - 1) {
+            since_flush = 0;
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+                    for (int q = 0; q < 4; q++) { sum[mi][ni][q] += acc[mi][ni][q]; acc[mi][ni][q] = 0.f; }
+        }
+    }
+    cpa_wait<0>();
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int hr = 0; hr < 2; hr++) {
+            const int pix = p0 + warp * 32 + mi * 16 + (lane >> 2) + hr * 8;
+            if (pix >= Min) continue;
+            const int b = pix / HW, rem = pix % HW;
+#pragma unroll
+            for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int c = c0 + ni * 8 + (lane & 3) * 2 + e;
+                    if (c < d.C) ga[((size_t)b * d.C + c) * HW + rem] = sum[mi][ni][hr * 2 + e];
                 }
         }
 }
@@ -250,35 +573,102 @@ MmaDims mma_dims(const Geometry &g) {
     return d;
 }
 
-size_t mma_scratch_bytes(const Geometry &g) {
-    if (!mma_eligible(g)) return 0;
-    const MmaDims d = mma_dims(g);
-    return align_up((size_t)d.B * d.Hp * d.Wp * d.Cp * 2, 256) + align_up((size_t)d.G * d.N2 * d.Kp * 2, 256) + 256;
+namespace {
+
+struct MmaPlan {
+    size_t flag_bytes, apad_bytes, wb_bytes, dh_bytes, wd_bytes, partial_bytes;
+    int S, slice_len, Cn;
+    size_t total() const { return flag_bytes + apad_bytes + wb_bytes + dh_bytes + wd_bytes + partial_bytes; }
+};
+
+MmaPlan mma_plan(const MmaDims &d) {
+    MmaPlan p;
+    p.flag_bytes = 256;
+    p.apad_bytes = align_up((size_t)d.B * d.Hp * d.Wp * d.Cp * 2, 256);
+    p.wb_bytes = align_up((size_t)d.G * d.N2 * d.Kp * 2, 256);
+    p.dh_bytes = align_up((size_t)3 * d.G * d.M * d.N2 * 2, 256);
+    p.Cn = (d.C + 31) / 32 * 32;
+    p.wd_bytes = align_up((size_t)p.Cn * d.K2 * d.K3 * d.N2 * 2, 256);
+    const long long tiles = (long long)d.G * ((d.Kp + 63) / 64) * (d.N2 / 64);
+    long long S = (148LL * 8 + tiles - 1) / tiles;
+    const long long maxS = (d.M + WP - 1) / WP;
+    if (S > maxS) S = maxS;
+    if (S < 1) S = 1;
+    long long len = (d.M + S - 1) / S;
+    len = (len + WP - 1) / WP * WP;
+    p.slice_len = (int)len;
+    p.S = (int)((d.M + len - 1) / len);
+    p.partial_bytes = align_up((size_t)p.S * d.G * d.Kp * d.N2 * 4, 256);
+    return p;
 }
 
-// Prepares the bf16 operands and the exactness flag, then computes D (fp32, [G][N2][M]) if exact.
-int launch_mma_forward(const Geometry &g, const float *act, const float *weight, const float *gout, float *D,
-                       void *scratch, int **flag_out, cudaStream_t s) {
-    const MmaDims d = mma_dims(g);
-    char *base = (char *)scratch;
-    int *flag = (int *)base;
-    __nv_bfloat16 *apad = (__nv_bfloat16 *)(base + 256);
-    __nv_bfloat16 *wb = (__nv_bfloat16 *)(base + 256 + align_up((size_t)d.B * d.Hp * d.Wp * d.Cp * 2, 256));
-    GEO_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int), s));
-    mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * d.Cp), 256, 0, s>>>(d, act, apad, flag);
-    mma_prep_weight_kernel<<<grid1((long long)d.G * d.N2 * d.Kp), 256, 0, s>>>(d, weight, wb, flag);
-    constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64);
-    static bool done[64] = {};
+template <typename Kern>
+int opt_in_smem(Kern kern, size_t bytes, bool *done) {
     int dev = 0;
     GEO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !done[dev]) {
-        GEO_CUDA_CHECK(cudaFuncSetAttribute(mma_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
         if (dev >= 0 && dev < 64) done[dev] = true;
     }
-    dim3 grid((d.M + 127) / 128, d.N2 / 64, d.G);
-    mma_forward_kernel<<<grid, 128, smem, s>>>(d, apad, wb, gout, D, flag);
-    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+}  // namespace
+
+size_t mma_scratch_bytes(const Geometry &g) {
+    if (!mma_eligible(g)) return 0;
+    return mma_plan(mma_dims(g)).total();
+}
+
+// Whole backward pass on the tensor cores; every kernel returns at once if an input turned out
+// not to be bf16-exact (*flag_out != 0 after the preparation kernels), in which case the caller's
+// FFMA kernels, which test the same flag the other way round, do the work.
+int launch_mma_backward(const Geometry &g, const float *act, const float *weight, const float *gout, float *grad_act,
+                        float *grad_weight, void *scratch, int **flag_out, cudaStream_t s) {
+    const MmaDims d = mma_dims(g);
+    const MmaPlan p = mma_plan(d);
+    char *base = (char *)scratch;
+    int *flag = (int *)base;
+    __nv_bfloat16 *apad = (__nv_bfloat16 *)(base + p.flag_bytes);
+    __nv_bfloat16 *wb = (__nv_bfloat16 *)(base + p.flag_bytes + p.apad_bytes);
+    __nv_bfloat16 *Dh = (__nv_bfloat16 *)(base + p.flag_bytes + p.apad_bytes + p.wb_bytes);
+    __nv_bfloat16 *wd = (__nv_bfloat16 *)(base + p.flag_bytes + p.apad_bytes + p.wb_bytes + p.dh_bytes);
+    float *partial = (float *)(base + p.flag_bytes + p.apad_bytes + p.wb_bytes + p.dh_bytes + p.wd_bytes);
     *flag_out = flag;
+    GEO_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int), s));
+    mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * d.Cp), 256, 0, s>>>(d, act, apad, flag);
+    mma_prep_weight_kernel<<<grid1((long long)d.G * d.N2 * d.Kp), 256, 0, s>>>(d, weight, wb, flag);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    {
+        constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64);
+        static bool done[64] = {};
+        int rc = opt_in_smem(mma_forward_kernel, smem, done);
+        if (rc) return rc;
+        dim3 grid((d.M + 127) / 128, d.N2 / 64, d.G);
+        mma_forward_kernel<<<grid, 128, smem, s>>>(d, apad, wb, gout, Dh, flag);
+        GEO_CUDA_CHECK(cudaGetLastError());
+    }
+    if (grad_weight) {
+        constexpr size_t smem = (size_t)WSTG * (WP * 128 * 4);
+        static bool done[64] = {};
+        int rc = opt_in_smem(mma_wgrad_kernel, smem, done);
+        if (rc) return rc;
+        dim3 grid(p.S, (d.Kp + 63) / 64, d.G * (d.N2 / 64));
+        mma_wgrad_kernel<<<grid, 64, smem, s>>>(d, apad, Dh, partial, p.slice_len, flag);
+        mma_wgrad_reduce_kernel<<<grid1((long long)d.G * d.taps * d.C * d.O), 256, 0, s>>>(d, p.S, partial, weight,
+                                                                                      grad_weight, flag);
+        GEO_CUDA_CHECK(cudaGetLastError());
+    }
+    if (grad_act) {
+        mma_prep_wd_kernel<<<grid1((long long)p.Cn * d.K2 * d.K3 * d.N2), 256, 0, s>>>(d, p.Cn, weight, wd);
+        constexpr size_t smem = (size_t)DSTG * (3 * 128 * 64 + 32 * 64);
+        static bool done[64] = {};
+        int rc = opt_in_smem(mma_dgrad_kernel, smem, done);
+        if (rc) return rc;
+        dim3 grid((d.B * d.H * d.W + 127) / 128, p.Cn / 32);
+        mma_dgrad_kernel<<<grid, 128, smem, s>>>(d, p.Cn, Dh, wd, grad_act, flag);
+        GEO_CUDA_CHECK(cudaGetLastError());
+    }
     return GEO_SC_OK;
 }
 

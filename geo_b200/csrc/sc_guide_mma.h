@@ -16,7 +16,7 @@ struct MmaDims {
 bool mma_eligible(const Geometry &g);
 MmaDims mma_dims(const Geometry &g);
 size_t mma_scratch_bytes(const Geometry &g);
-int launch_mma_forward(const Geometry &g, const float *act, const float *weight, const float *gout, float *D,
-                       void *scratch, int **flag_out, cudaStream_t s);
+int launch_mma_backward(const Geometry &g, const float *act, const float *weight, const float *gout, float *grad_act,
+                        float *grad_weight, void *scratch, int **flag_out, cudaStream_t s);
 
 }  // namespace geo

@@ -52,6 +52,32 @@ def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
     _close(ga.cpu(), ga_ref, f"{mode} grad_act")
 
 
+@pytest.mark.parametrize("mode", ["1d_bin", "full_or"])
+def test_guide_gradients_for_inputs_that_bf16_cannot_hold(cuda_device, mode):
+    """Unquantised inputs: the tensor-core path must stand down (its exactness argument does not
+    apply) and the fp32 FFMA kernels must produce the gradients."""
+    from geo_b200 import ops
+    from oracle import guide as oracle_guide
+
+    g = torch.Generator().manual_seed(99)
+    a = torch.rand(3, 16, 9, 9, generator=g)
+    w = (torch.rand(40, 16, 3, 3, generator=g) * 2 - 1) * 0.3
+    desc = ops.desc_for(a, w, 128, mode, (1, 1))
+    go = torch.randn(*ops.out_shape(desc), generator=g)
+    ga_ref, gw_ref = oracle_guide.guide_grads(a, w, go, mode, 1, 1)
+    ga, gw = ops.guide_backward(a.to(cuda_device), w.to(cuda_device), go.to(cuda_device), desc)
+    _close(gw.cpu(), gw_ref, f"{mode} grad_weight (fp32 inputs)")
+    _close(ga.cpu(), ga_ref, f"{mode} grad_act (fp32 inputs)")
+    # one inexact value among exact ones is enough to switch paths
+    a2 = q7(a)
+    a2[1, 3, 4, 4] = 0.123456
+    w2 = q7(w)
+    ga_ref, gw_ref = oracle_guide.guide_grads(a2, w2, go, mode, 1, 1)
+    ga, gw = ops.guide_backward(a2.to(cuda_device), w2.to(cuda_device), go.to(cuda_device), desc)
+    _close(gw.cpu(), gw_ref, f"{mode} grad_weight (one inexact value)")
+    _close(ga.cpu(), ga_ref, f"{mode} grad_act (one inexact value)")
+
+
 def test_layer_autograd_matches_reference_semantics(cuda_device, oracle_lib):
     """conv2d_generic: value = SC counts / L (bit-exact), gradient = guide gradient."""
     from geo_b200 import functional as sc_f
