@@ -558,15 +558,15 @@ int grid1(long long total) {
 }  // namespace
 
 bool mma_eligible(const Geometry &g) {
-    // whole-tap groups only, and column tiles of 64 need at least 32 padded output channels
-    return (g.mode == GEO_SC_MODE_1D || g.mode == GEO_SC_MODE_FULL_OR) && g.Opad % 32 == 0;
+    return g.mode == GEO_SC_MODE_1D || g.mode == GEO_SC_MODE_FULL_OR;   // whole-tap groups only
 }
 
 MmaDims mma_dims(const Geometry &g) {
     MmaDims d;
     d.B = g.B; d.C = g.C; d.H = g.H; d.W = g.W; d.ph = g.pad_h; d.pw = g.pad_w; d.Hp = g.Hp; d.Wp = g.Wp;
     d.O = g.O; d.K2 = g.K2; d.K3 = g.K3; d.Ho = g.Ho; d.Wo = g.Wo; d.HoWo = g.Ho * g.Wo;
-    d.mode = g.mode; d.G = g.G; d.Opad = g.Opad; d.N2 = 2 * g.Opad; d.M = (int)g.M;
+    // the guide's own channel padding: column tiles are 64 wide = 32 channels x 2 polarities
+    d.mode = g.mode; d.G = g.G; d.Opad = (g.O + 31) / 32 * 32; d.N2 = 2 * d.Opad; d.M = (int)g.M;
     d.Cp = (g.C + 7) / 8 * 8;
     d.taps = g.mode == GEO_SC_MODE_1D ? g.K2 : g.K2 * g.K3;
     d.Kp = (d.taps * d.Cp + MK - 1) / MK * MK;
