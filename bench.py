@@ -205,7 +205,8 @@ def run_native(args):
                        if args.workload == "tiny_cnn" else
                        f"vgg11: VGG-11-style SC CNN training step, batch {B}/GPU, L={BIT_LENGTH}, 1d_bin, lfsr, SGD",
                        "per_gpu_batch": B, "global_batch": B * world, "parallelism": f"dp{world}",
-                       "launch": "eager" if args.no_graph else "whole step replayed as one CUDA graph",
+                       "launch": "eager" if args.no_graph else ("whole step replayed as one CUDA graph" if world == 1 else
+                                                             "two CUDA graphs per step (forward+backward, update) around the NCCL all-reduce"),
                        "l2": "per-step working set (activation streams, guide tensors) exceeds the 126 MB L2; "
                              "4 input batches rotated; no explicit flush"},
             "e2e": {"value": images / (e2e_ms * 1e-3), "unit": "images/s",

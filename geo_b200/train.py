@@ -34,6 +34,7 @@ class TrainStep:
         # into one CUDA graph on first use and replayed afterwards; shapes must then stay fixed.
         self.use_graph = graph
         self._graph = None
+        self._graph_update = None
         self._static = None
 
     def __call__(self, inputs, targets):
@@ -45,6 +46,12 @@ class TrainStep:
         sx.copy_(inputs, non_blocking=True)
         sy.copy_(targets, non_blocking=True)
         self._graph.replay()
+        if self._graph_update is not None:
+            # the gradient exchange runs between the two graphs, outside any capture: collectives
+            # inside a capture depend on the communication library's capture support and a rank
+            # that fails to capture leaves its peers waiting
+            self.grad_hook(self.params)
+            self._graph_update.replay()
         return sloss, sout
 
     def _capture(self, inputs, targets):
@@ -57,12 +64,29 @@ class TrainStep:
         torch.cuda.current_stream(sx.device).wait_stream(side)
         torch.cuda.synchronize(sx.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            sloss, sout = self._step(sx.clone(), sy)
+        self._graph_update = None
+        if self.grad_hook is None:
+            with torch.cuda.graph(graph):
+                sloss, sout = self._step(sx.clone(), sy)
+        else:
+            with torch.cuda.graph(graph):
+                sloss, sout = self._forward_backward(sx.clone(), sy)
+            self.grad_hook(self.params)
+            update = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(update, pool=graph.pool()):
+                self._update()
+            self._graph_update = update
         self._graph = graph
         self._static = (sx, sy, sloss, sout)
 
     def _step(self, inputs, targets):
+        out = self._forward_backward(inputs, targets)
+        if self.grad_hook is not None:
+            self.grad_hook(self.params)
+        self._update()
+        return out
+
+    def _forward_backward(self, inputs, targets):
         model = self.model
         model.train()
         output = model(inputs)
@@ -70,8 +94,9 @@ class TrainStep:
         for p in self.params:
             p.grad = None
         loss.backward()
-        if self.grad_hook is not None:
-            self.grad_hook(self.params)
+        return loss.detach(), output.detach()
+
+    def _update(self):
         with torch.no_grad():
             for m in self.sc_modules:
                 m.weight.data.copy_(m.weight_org)
@@ -84,4 +109,3 @@ class TrainStep:
             for m in self.sc_modules:
                 m.weight_org.copy_(m.weight.data.clamp(-1, 0.999))
             self.optimizer.zero_grad(set_to_none=True)
-        return loss.detach(), output.detach()
