@@ -37,6 +37,9 @@ __device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr, 
     const int n = valid ? 4 : 0;
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_addr), "l"(gptr), "r"(n));
 }
+__device__ __forceinline__ void cp_async4_full(uint32_t smem_addr, const void *gptr) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr));
+}
 __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *gptr) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr));
 }
@@ -111,22 +114,40 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
             const uint32_t *asrc = pr.as + ld_p * pr.pack_words;
             // Rows past the end of the group are zero-filled: a zero activation word contributes
             // nothing, so the consumer can always run all KC rows of a stage, fully unrolled.
+            // Full stages (the common case) take a path without per-row predicates.
+            constexpr int CPR = NT / 2;                       // 16-byte weight chunks per row
+            constexpr int WROWS = NTHREADS / CPR;             // weight rows covered per pass
+            static_assert(NTHREADS % CPR == 0 && KC % WROWS == 0, "weight tile must divide evenly");
+            const uint32_t *wsrc = pr.ws + ((size_t)(ld_p * pr.G + ld_g) * pr.K + k0) * pr.Opad * 2 + o0 * 2 +
+                                   (size_t)(t / CPR) * pr.Opad * 2 + (t % CPR) * 4;
+            const uint32_t w_dst = w_s + (uint32_t)((t / CPR) * NT * 2 + (t % CPR) * 4) * 4;
+            if (rows == KC) {
 #pragma unroll
-            for (int j = 0; j < MPT; j++) {
-                const int mcol = (t % MT) + j * NTHREADS;
+                for (int j = 0; j < MPT; j++) {
+                    const uint32_t *src = asrc + abase[j];
+                    const uint32_t dst = a_s + (uint32_t)((t % MT) + j * NTHREADS + r0 * MT) * 4;
 #pragma unroll
-                for (int i = 0; i < KC / RSTEP; i++) {
-                    const int r = r0 + i * RSTEP;
-                    const bool v = r < rows;
-                    cp_async4(a_s + (uint32_t)(r * MT + mcol) * 4, asrc + abase[j] + (v ? __ldg(aoff + r) : 0), v);
+                    for (int i = 0; i < KC / RSTEP; i++)
+                        cp_async4_full(dst + (uint32_t)(i * RSTEP * MT) * 4, src + __ldg(aoff + r0 + i * RSTEP));
                 }
-            }
-            // weights: `rows` rows of NT*2 words = NT/2 16-byte chunks each
-            constexpr int CPR = NT / 2;
-            const uint32_t *wsrc = pr.ws + ((size_t)(ld_p * pr.G + ld_g) * pr.K + k0) * pr.Opad * 2 + o0 * 2;
-            for (int i = t; i < rows * CPR; i += NTHREADS) {
-                const int r = i / CPR, ch = i % CPR;
-                cp_async16(w_s + (uint32_t)(r * NT * 2 + ch * 4) * 4, wsrc + (size_t)r * pr.Opad * 2 + ch * 4);
+#pragma unroll
+                for (int i = 0; i < KC / WROWS; i++)
+                    cp_async16(w_dst + (uint32_t)(i * WROWS * NT * 2) * 4, wsrc + (size_t)i * WROWS * pr.Opad * 2);
+            } else {
+#pragma unroll
+                for (int j = 0; j < MPT; j++) {
+                    const int mcol = (t % MT) + j * NTHREADS;
+#pragma unroll
+                    for (int i = 0; i < KC / RSTEP; i++) {
+                        const int r = r0 + i * RSTEP;
+                        const bool v = r < rows;
+                        cp_async4(a_s + (uint32_t)(r * MT + mcol) * 4, asrc + abase[j] + (v ? __ldg(aoff + r) : 0), v);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < KC / WROWS; i++)
+                    if (t / CPR + i * WROWS < rows)
+                        cp_async16(w_dst + (uint32_t)(i * WROWS * NT * 2) * 4, wsrc + (size_t)i * WROWS * pr.Opad * 2);
             }
             ld_s++;
             if (++ld_c == chunks) {
