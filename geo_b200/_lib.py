@@ -56,7 +56,7 @@ def lib():
     L.geo_sc_generate_act_streams.argtypes = [dp, vp, vp, sz, vp]
     L.geo_sc_accumulate.argtypes = [dp, vp, vp, vp, vp]
     i32p = ctypes.POINTER(ctypes.c_int32)
-    L.geo_sc_group_geometry.argtypes = [dp, i32p, i32p, i32p, i32p]
+    L.geo_sc_group_geometry.argtypes = [dp, i32p, i32p, i32p, i32p, i32p]
     L.geo_sc_host_stream.argtypes = [i32] * 7 + [vp]
     L.geo_sc_static_scratch_bytes.restype = ctypes.c_size_t
     L.geo_sc_conv2d_forward_static.argtypes = [dp, vp, vp, vp, vp]
@@ -103,10 +103,16 @@ def size_query(fn_name, desc):
 
 
 def group_geometry(desc):
-    g, k, nt, op = (ctypes.c_int32(0) for _ in range(4))
-    check(lib().geo_sc_group_geometry(ctypes.byref(desc), ctypes.byref(g), ctypes.byref(k), ctypes.byref(nt),
-                                      ctypes.byref(op)), "geo_sc_group_geometry")
-    return g.value, k.value, nt.value, op.value
+    """(groups, members, c_out tile, padded c_out) of the prepared-weight layout."""
+    return group_geometry_full(desc)[:2] + group_geometry_full(desc)[3:]
+
+
+def group_geometry_full(desc):
+    """(groups, members, members as laid out (padded to 16), c_out tile, padded c_out)."""
+    g, k, kp, nt, op = (ctypes.c_int32(0) for _ in range(5))
+    check(lib().geo_sc_group_geometry(ctypes.byref(desc), ctypes.byref(g), ctypes.byref(k), ctypes.byref(kp),
+                                      ctypes.byref(nt), ctypes.byref(op)), "geo_sc_group_geometry")
+    return g.value, k.value, kp.value, nt.value, op.value
 
 
 def host_stream(bit_length, value, seed_base, seed_index, total_width=7, load_width=8, load_wait=1):

@@ -26,18 +26,13 @@ struct AccParams {
     const int32_t *aoff;  // [G][K]
     int32_t *out;         // [B][O][Ho][Wo]
     int M, O, Opad, HoWo, Wo, Wp;
-    int P, G, K;
+    int P, G, K;          // K: members per group as laid out (padded to a multiple of 16)
     int img_words;        // P*C*Hp*Wp
     int pack_words;       // C*Hp*Wp
     int splits;           // CTAs along grid.z sharing one output tile; > 1 => atomic accumulation
 };
 
-// 4-byte copy; with valid == false the destination word is zero-filled (source size 0)
-__device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr, bool valid = true) {
-    const int n = valid ? 4 : 0;
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_addr), "l"(gptr), "r"(n));
-}
-__device__ __forceinline__ void cp_async4_full(uint32_t smem_addr, const void *gptr) {
+__device__ __forceinline__ void cp_async4(uint32_t smem_addr, const void *gptr) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr));
 }
 __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *gptr) {
@@ -93,7 +88,7 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
     }
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
-    const int chunks = (pr.K + KC - 1) / KC;
+    const int chunks = pr.K / KC;   // pr.K is the padded member count, a multiple of KC
     // This CTA owns the (pack, group) pairs [pair0, pair1) of the P*G pairs; the sum over pairs is
     // an integer sum, so splitting it over CTAs and adding atomically is exact and order-free.
     const int pairs = pr.P * pr.G;
@@ -109,46 +104,31 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
             const uint32_t a_s = smem_base + (uint32_t)buf * T::STAGE_WORDS * 4;
             const uint32_t w_s = a_s + T::A_WORDS * 4;
             const int k0 = ld_c * KC;
-            const int rows = min(KC, pr.K - k0);
             const int32_t *aoff = pr.aoff + ld_g * pr.K + k0;
             const uint32_t *asrc = pr.as + ld_p * pr.pack_words;
-            // Rows past the end of the group are zero-filled: a zero activation word contributes
-            // nothing, so the consumer can always run all KC rows of a stage, fully unrolled.
-            // Full stages (the common case) take a path without per-row predicates.
+            // The prepared layout pads every group to a multiple of 16 members with all-zero weight
+            // streams (and offset 0), so every stage is full: no per-row predicates, and the
+            // consumer always runs all KC rows of a stage, fully unrolled.
             constexpr int CPR = NT / 2;                       // 16-byte weight chunks per row
             constexpr int WROWS = NTHREADS / CPR;             // weight rows covered per pass
-            static_assert(NTHREADS % CPR == 0 && KC % WROWS == 0, "weight tile must divide evenly");
+            static_assert(NTHREADS % CPR == 0, "weight rows are covered by whole passes");
+    constexpr int WPASS = (KC + WROWS - 1) / WROWS;
             const uint32_t *wsrc = pr.ws + ((size_t)(ld_p * pr.G + ld_g) * pr.K + k0) * pr.Opad * 2 + o0 * 2 +
                                    (size_t)(t / CPR) * pr.Opad * 2 + (t % CPR) * 4;
             const uint32_t w_dst = w_s + (uint32_t)((t / CPR) * NT * 2 + (t % CPR) * 4) * 4;
-            if (rows == KC) {
 #pragma unroll
-                for (int j = 0; j < MPT; j++) {
-                    const uint32_t *src = asrc + abase[j];
-                    const uint32_t dst = a_s + (uint32_t)((t % MT) + j * NTHREADS + r0 * MT) * 4;
+            for (int j = 0; j < MPT; j++) {
+                const uint32_t *src = asrc + abase[j];
+                const uint32_t dst = a_s + (uint32_t)((t % MT) + j * NTHREADS + r0 * MT) * 4;
 #pragma unroll
-                    for (int i = 0; i < KC / RSTEP; i++)
-                        cp_async4_full(dst + (uint32_t)(i * RSTEP * MT) * 4, src + __ldg(aoff + r0 + i * RSTEP));
-                }
-#pragma unroll
-                for (int i = 0; i < KC / WROWS; i++)
-                    cp_async16(w_dst + (uint32_t)(i * WROWS * NT * 2) * 4, wsrc + (size_t)i * WROWS * pr.Opad * 2);
-            } else {
-#pragma unroll
-                for (int j = 0; j < MPT; j++) {
-                    const int mcol = (t % MT) + j * NTHREADS;
-#pragma unroll
-                    for (int i = 0; i < KC / RSTEP; i++) {
-                        const int r = r0 + i * RSTEP;
-                        const bool v = r < rows;
-                        cp_async4(a_s + (uint32_t)(r * MT + mcol) * 4, asrc + abase[j] + (v ? __ldg(aoff + r) : 0), v);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < KC / WROWS; i++)
-                    if (t / CPR + i * WROWS < rows)
-                        cp_async16(w_dst + (uint32_t)(i * WROWS * NT * 2) * 4, wsrc + (size_t)i * WROWS * pr.Opad * 2);
+                for (int i = 0; i < (KC + RSTEP - 1) / RSTEP; i++)
+                    if (KC % RSTEP == 0 || r0 + i * RSTEP < KC)
+                        cp_async4(dst + (uint32_t)(i * RSTEP * MT) * 4, src + __ldg(aoff + r0 + i * RSTEP));
             }
+#pragma unroll
+            for (int i = 0; i < WPASS; i++)
+                if (KC % WROWS == 0 || t / CPR + i * WROWS < KC)
+                    cp_async16(w_dst + (uint32_t)(i * WROWS * NT * 2) * 4, wsrc + (size_t)i * WROWS * pr.Opad * 2);
             ld_s++;
             if (++ld_c == chunks) {
                 ld_c = 0;
@@ -188,24 +168,30 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
             const uint32_t a[TM] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
             const uint32_t wp[TN] = {w_a.x, w_a.z, w_b.x, w_b.z};
             const uint32_t wn[TN] = {w_a.y, w_a.w, w_b.y, w_b.w};
+            if (r == 0 && cs_c == 0) {   // first member of a group starts the OR chains afresh
 #pragma unroll
-            for (int i = 0; i < TM; i++)
+                for (int i = 0; i < TM; i++)
 #pragma unroll
-                for (int j = 0; j < TN; j++) {
-                    accp[i][j] |= a[i] & wp[j];
-                    accn[i][j] |= a[i] & wn[j];
-                }
+                    for (int j = 0; j < TN; j++) {
+                        accp[i][j] = a[i] & wp[j];
+                        accn[i][j] = a[i] & wn[j];
+                    }
+            } else {
+#pragma unroll
+                for (int i = 0; i < TM; i++)
+#pragma unroll
+                    for (int j = 0; j < TN; j++) {
+                        accp[i][j] |= a[i] & wp[j];
+                        accn[i][j] |= a[i] & wn[j];
+                    }
+            }
         }
         if (++cs_c == chunks) {  // group finished: binary accumulation of its popcounts
             cs_c = 0;
 #pragma unroll
             for (int i = 0; i < TM; i++)
 #pragma unroll
-                for (int j = 0; j < TN; j++) {
-                    osum[i][j] += __popc(accp[i][j]) - __popc(accn[i][j]);
-                    accp[i][j] = 0;
-                    accn[i][j] = 0;
-                }
+                for (int j = 0; j < TN; j++) osum[i][j] += __popc(accp[i][j]) - __popc(accn[i][j]);
         }
     }
     cp_async_wait<0>();
@@ -260,13 +246,26 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
     AccParams pr;
     pr.as = astream; pr.ws = wstream; pr.aoff = aoff; pr.out = out;
     pr.M = (int)g.M; pr.O = g.O; pr.Opad = g.Opad; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
-    pr.P = g.P; pr.G = g.G; pr.K = g.K;
+    pr.P = g.P; pr.G = g.G; pr.K = g.Kp;
     pr.pack_words = g.C * g.Hp * g.Wp;
     pr.img_words = g.P * pr.pack_words;
     pr.splits = 1;
     // Long groups use 32-member stages (half as many barriers per LOP3); short ones 16-member
     // stages, because a stage is always executed in full and its zero-filled tail rows are wasted.
-    const bool long_groups = g.K >= 64;
+    const bool long_groups = g.Kp >= 64 && g.Kp % 32 == 0;
+    if (g.Kp < 16) {   // short groups: one stage per group, 4 / 8 / 12 members
+        switch (g.NT * 100 + g.Kp) {
+        case 1604: return launch_tile<16, 128, 4, 6>(g, pr, s);
+        case 1608: return launch_tile<16, 128, 8, 6>(g, pr, s);
+        case 1612: return launch_tile<16, 128, 12, 4>(g, pr, s);
+        case 3204: return launch_tile<32, 128, 4, 6>(g, pr, s);
+        case 3208: return launch_tile<32, 128, 8, 6>(g, pr, s);
+        case 3212: return launch_tile<32, 128, 12, 4>(g, pr, s);
+        case 6404: return launch_tile<64, 128, 4, 6>(g, pr, s);
+        case 6408: return launch_tile<64, 128, 8, 6>(g, pr, s);
+        default: return launch_tile<64, 128, 12, 4>(g, pr, s);
+        }
+    }
     switch (g.NT) {
     case 16: return g.M <= 2048 ? launch_tile<16, 64>(g, pr, s) : launch_tile<16, 128>(g, pr, s);
     case 32: return long_groups ? launch_tile<32, 128, 32, 3>(g, pr, s) : launch_tile<32, 128>(g, pr, s);

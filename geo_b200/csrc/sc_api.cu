@@ -73,17 +73,20 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     const long long lim = (1LL << 31) - 1;
     long long M = (long long)g->B * g->Ho * g->Wo;
     long long aw = (long long)g->B * g->P * g->C * g->Hp * g->Wp;
-    long long ww = (long long)g->P * G * K * g->Opad * 2;
+    // members as laid out: short groups are padded to a multiple of 4 (one stage holds the whole
+    // group), longer ones to a multiple of 16 (stages of 16 or 32 members)
+    const long long Kp = K <= 16 ? (K + 3) / 4 * 4 : (K + 15) / 16 * 16;
+    long long ww = (long long)g->P * G * Kp * g->Opad * 2;
     long long ow = M * g->O;
     long long iw = (long long)g->B * g->C * g->H * g->W;
-    if (G > lim || K > lim || M > lim || aw > lim || ww > lim || ow > lim || iw > lim || G * K > lim)
+    if (G > lim || Kp > lim || M > lim || aw > lim || ww > lim || ow > lim || iw > lim || G * Kp > lim)
         return fail(GEO_SC_ERR_TOO_LARGE,
                     "an index exceeds 31 bits (positions %lld, act words %lld, weight words %lld, outputs %lld)", M, aw,
                     ww, ow);
-    g->G = (int)G; g->K = (int)K; g->M = M;
+    g->G = (int)G; g->K = (int)K; g->Kp = (int)Kp; g->M = M;
     g->act_stream_words = (size_t)aw;
     g->w_stream_words = (size_t)ww;
-    g->aoff_entries = (size_t)(G * K);
+    g->aoff_entries = (size_t)(G * Kp);
     return GEO_SC_OK;
 }
 
@@ -147,13 +150,14 @@ const char *geo_sc_last_error(void) { return g_err; }
 
 int geo_sc_init(void) { return ensure_tables(); }
 
-int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *cout_tile,
-                          int32_t *cout_padded) {
+int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *members_padded,
+                          int32_t *cout_tile, int32_t *cout_padded) {
     Geometry g;
     int rc = make_geometry(desc, &g);
     if (rc) return rc;
     if (groups) *groups = g.G;
     if (members) *members = g.K;
+    if (members_padded) *members_padded = g.Kp;
     if (cout_tile) *cout_tile = g.NT;
     if (cout_padded) *cout_padded = g.Opad;
     return GEO_SC_OK;

@@ -24,6 +24,7 @@ struct Geometry {
     int mode;
     int z;                   // OR-group width in channels (yz mode)
     int G, K;                // binary-accumulated groups, OR-accumulated members per group
+    int Kp;                  // members per group as laid out: K rounded up to 4 (K <= 16) or 16, zero streams
     int NT;                  // c_out tile of the accumulate kernel
     int Opad;                // c_out rounded up to NT
     int tw, lu, lw_w, lw_a;  // progressive loading

@@ -91,7 +91,7 @@ int ensure_tables() {
 struct GenParams {
     int B, C, H, W, pad_h, pad_w, Hp, Wp;
     int O, K2, K3;
-    int L, P, mode, z, G, K, Opad;
+    int L, P, mode, z, G, K, Kp, Opad;
     int RW;
 };
 
@@ -99,7 +99,7 @@ static GenParams gen_params(const Geometry &g) {
     GenParams p;
     p.B = g.B; p.C = g.C; p.H = g.H; p.W = g.W; p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.Hp = g.Hp; p.Wp = g.Wp;
     p.O = g.O; p.K2 = g.K2; p.K3 = g.K3;
-    p.L = g.L; p.P = g.P; p.mode = g.mode; p.z = g.z; p.G = g.G; p.K = g.K; p.Opad = g.Opad;
+    p.L = g.L; p.P = g.P; p.mode = g.mode; p.z = g.z; p.G = g.G; p.K = g.K; p.Kp = g.Kp; p.Opad = g.Opad;
     p.RW = row_words(g.L);
     return p;
 }
@@ -151,13 +151,13 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
     uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RW);
     load_tables(s_pat, s_q0, gp.L, gp.RW);
 
-    const long long total = (long long)gp.G * gp.K * gp.Opad;
+    const long long total = (long long)gp.G * gp.Kp * gp.Opad;
     const float fL = (float)gp.L;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const int o = (int)(idx % gp.Opad);
         const int gk = (int)(idx / gp.Opad);
-        const int k = gk % gp.K, g = gk / gp.K;
+        const int k = gk % gp.Kp, g = gk / gp.Kp;   // k >= K: padding member, zero streams
         int c, ky, kx, sidx;
         switch (gp.mode) {
         case GEO_SC_MODE_1D: kx = g; c = k / gp.K2; ky = k % gp.K2; sidx = k; break;
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
         }
         default: c = k / (gp.K2 * gp.K3); ky = (k / gp.K3) % gp.K2; kx = k % gp.K3; sidx = k; break;
         }
-        const bool valid = c < gp.C;
+        const bool valid = c < gp.C && k < gp.K;
         if (o == 0) aoff[gk] = valid ? (c * gp.Hp + ky) * gp.Wp + kx : 0;
         int Vp = 0, Vn = 0;
         if (valid && o < gp.O) {
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
             uint2 v;
             v.x = Vp ? stream_word(s_pat, gp.RW, gp.L, Vp, qp, p, plan) : 0u;
             v.y = Vn ? stream_word(s_pat, gp.RW, gp.L, Vn, qn, p, plan) : 0u;
-            *(uint2 *)(ws + ((((size_t)p * gp.G + g) * gp.K + k) * gp.Opad + o) * 2) = v;
+            *(uint2 *)(ws + ((((size_t)p * gp.G + g) * gp.Kp + k) * gp.Opad + o) * 2) = v;
         }
     }
 }
@@ -238,7 +238,7 @@ int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream,
     LoadPlan plan;
     make_load_plan(g.L, g.tw, g.lu, g.lw_w, &plan);
     const size_t smem = (size_t)g.L * gp.RW * 4 + (size_t)g.L * 2;
-    const long long total = (long long)g.G * g.K * g.Opad;
+    const long long total = (long long)g.G * g.Kp * g.Opad;
     prepare_weights_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, w, wstream, aoff);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;

@@ -277,11 +277,11 @@ def act_streams_canonical(buf, desc):
 
 def weight_streams_canonical(buf, desc):
     """Decode the prepared-weight buffer to int32 [2,O,C,K2,K3,P] (the oracle's layout)."""
-    G, K, NT, Opad = _lib.group_geometry(desc)
+    G, K, Kp, NT, Opad = _lib.group_geometry_full(desc)
     P = (desc.bit_length + 31) // 32
     O, C, K2, K3 = desc.c_out, desc.c_in, desc.k_h, desc.k_w
-    n = P * G * K * Opad * 2
-    v = buf[: n * 4].view(torch.int32).view(P, G, K, Opad, 2)[:, :, :, :O, :]
+    n = P * G * Kp * Opad * 2
+    v = buf[: n * 4].view(torch.int32).view(P, G, Kp, Opad, 2)[:, :, :K, :O, :]
     mode = desc.mode
     if mode == _lib.MODE_1D:        # g = kx, k = c*K2+ky
         v = v.reshape(P, K3, C, K2, O, 2).permute(5, 4, 2, 3, 1, 0)

@@ -118,9 +118,10 @@ int geo_sc_conv2d_forward_static(const geo_sc_conv_desc *desc, const float *act_
  *
  * geo_sc_prepare_weights replaces the stream_generation_transpose_* kernels
  * (sc_cuda_kernel.cu:91-349).  Prepared layout: uint32 words
- * [pack][group][member][c_out_padded][2] (last index 0 = positive stream, seed base 67;
- * 1 = negative, base 37), followed by an int32 table [group][member] of activation
- * offsets; c_out_padded = c_out rounded up to the kernel's c_out tile
+ * [pack][group][member_padded][c_out_padded][2] (last index 0 = positive stream, seed base 67;
+ * 1 = negative, base 37), followed by an int32 table [group][member_padded] of activation
+ * offsets; members are padded (see geo_sc_group_geometry) with zero streams, c_out_padded = c_out
+ * rounded up to the kernel's c_out tile
  * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.
  *
  * geo_sc_generate_act_streams replaces the generation loops at
@@ -138,9 +139,11 @@ int geo_sc_generate_act_streams(const geo_sc_conv_desc *desc, const float *act_d
 int geo_sc_accumulate(const geo_sc_conv_desc *desc, const void *astream_device, const void *wprep_device,
                       int32_t *out_device, void *stream);
 
-/* Geometry of the prepared-weight layout: groups, members per group, c_out tile. */
-int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *cout_tile,
-                          int32_t *cout_padded);
+/* Geometry of the prepared-weight layout: groups, members per group (logical, and as laid out:
+ * rounded up to a multiple of 4 (up to 16 members) or of 16, with all-zero streams), c_out tile,
+ * padded c_out. */
+int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *members_padded,
+                          int32_t *cout_tile, int32_t *cout_padded);
 
 /* ---- SC linear layer ---------------------------------------------------------------
  * act [batch][features] . weight [out_features][features]^T with OR accumulation inside
