@@ -23,6 +23,8 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# where the reference's source tree is mounted, when it is (build of oracle/_ref, fixture generation)
+REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 BUILD_DIR = os.path.join(HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libsc_oracle.so")
 

@@ -28,6 +28,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
+REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 
 
 def _torch_flags():
@@ -113,7 +114,7 @@ def build_cuda(ref_root):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("GEO_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=REFERENCE_ROOT)
     ap.add_argument("--no-cuda", action="store_true")
     args = ap.parse_args(argv)
     if not os.path.isdir(args.reference):

@@ -70,11 +70,13 @@ def ref_sc_extension_cuda():
     return _cuda_mod
 
 
-def reference_python(ref_root="/root/reference"):
+def reference_python(ref_root=None):
     """Import the reference's ``utils_functional`` from its own tree (fixture generation
     only; the tree does not exist where the GPU tests run).  ``sc_extension`` resolves to
     the reference CPU build; ``sc_extension_cuda`` to an empty stand-in, because no GPU
     code can run where fixtures are generated."""
+    if ref_root is None:
+        from . import REFERENCE_ROOT as ref_root
     if "utils_functional" in sys.modules and getattr(sys.modules["utils_functional"], "__geo_ref__", False):
         return sys.modules["utils_functional"]
     cpu = ref_sc_extension()

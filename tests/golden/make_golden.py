@@ -106,7 +106,7 @@ def make_training_step_golden():
     import types
 
     uf = ref_loader.reference_python()
-    ref_root = "/root/reference"
+    from oracle import REFERENCE_ROOT as ref_root
     for name in ("bokeh", "bokeh.io", "bokeh.plotting", "bokeh.layouts"):   # utils.py imports them, unused here
         m = types.ModuleType(name)
         m.output_file = m.save = m.show = m.figure = m.column = None

@@ -9,7 +9,7 @@ runs its three deterministic entry points
     conv2d_add_yz_variable_acc(...)               yz_bin   (sc_cuda.cpp:34-45)
 
 with and without progressive loading on small inputs and stores inputs and outputs in
-``<out>/ref_cuda_modes.npz`` (copy it into tests/golden/).  Shapes avoid the two
+``<out_dir>/ref_cuda_modes.npz`` (default: next to this script).  Shapes avoid the two
 configurations in which the reference reads or strides outside what it wrote: z_bin needs
 k_w <= c_in (seed array of c_in*k_h entries indexed by ky*k_w+kx, sc_cuda_kernel.cu:322-324)
 and yz_bin needs c_in divisible by z_unit (pack stride, sc_cuda_kernel.cu:251).
@@ -62,7 +62,7 @@ def cases():
 
 
 def main():
-    out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.dirname(HERE)), "gpurun_out")
+    out_dir = sys.argv[1] if len(sys.argv) > 1 else HERE
     os.makedirs(out_dir, exist_ok=True)
     ext = ref_loader.ref_sc_extension_cuda()
     assert ext is not None, "oracle/_ref/cuda/ref_sc_extension_cuda.so missing (run oracle/build_ref.py)"
