@@ -35,6 +35,7 @@ class TrainStep:
         self.use_graph = graph
         self._graph = None
         self._graph_update = None
+        self._split_hook = False
         self._static = None
 
     def __call__(self, inputs, targets):
@@ -50,7 +51,10 @@ class TrainStep:
             # the gradient exchange runs between the two graphs, outside any capture: collectives
             # inside a capture depend on the communication library's capture support and a rank
             # that fails to capture leaves its peers waiting
-            self.grad_hook(self.params)
+            if self._split_hook:
+                self.grad_hook.reduce()
+            else:
+                self.grad_hook(self.params)
             self._graph_update.replay()
         return sloss, sout
 
@@ -69,11 +73,21 @@ class TrainStep:
             with torch.cuda.graph(graph):
                 sloss, sout = self._step(sx.clone(), sy)
         else:
+            # a hook that offers pack / reduce / unpack keeps its copies inside the graphs
+            hook = self.grad_hook
+            self._split_hook = all(hasattr(hook, n) for n in ("pack", "reduce", "unpack"))
             with torch.cuda.graph(graph):
                 sloss, sout = self._forward_backward(sx.clone(), sy)
-            self.grad_hook(self.params)
+                if self._split_hook:
+                    hook.pack(self.params)
+            if self._split_hook:
+                hook.reduce()
+            else:
+                hook(self.params)
             update = torch.cuda.CUDAGraph()
             with torch.cuda.graph(update, pool=graph.pool()):
+                if self._split_hook:
+                    hook.unpack(self.params)
                 self._update()
             self._graph_update = update
         self._graph = graph

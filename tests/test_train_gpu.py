@@ -47,6 +47,39 @@ def test_graph_replay_equals_eager_steps(cuda_device):
         assert torch.equal(a, b) and torch.equal(a, c)
 
 
+def test_two_graph_step_with_packed_gradient_exchange(cuda_device):
+    """The data-parallel hook's pack / unpack phases live inside the two graphs and only the
+    collective runs between them; with a one-rank process group the result must equal the
+    hook-free step exactly."""
+    import torch.distributed as dist
+
+    from geo_b200.dp import GradientAllReduce
+    from geo_b200.train import TrainStep
+
+    created = False
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{29600 + os.getpid() % 300}", rank=0, world_size=1)
+        created = True
+    try:
+        g = torch.Generator().manual_seed(4)
+        x = torch.rand(16, 3, 32, 32, generator=g).to(cuda_device)
+        y = torch.randint(0, 10, (16,), generator=g).to(cuda_device)
+        results = []
+        for hook in (None, GradientAllReduce(1)):
+            net = _model(cuda_device, seed=1)
+            step = TrainStep(net, graph=True, grad_hook=hook)
+            for _ in range(3):
+                loss, _ = step(x.clone(), y)
+            torch.cuda.synchronize()
+            results.append((float(loss), [p.detach().clone() for p in net.parameters()]))
+        assert results[0][0] == results[1][0]
+        for a, b in zip(results[0][1], results[1][1]):
+            assert torch.equal(a, b)
+    finally:
+        if created:
+            dist.destroy_process_group()
+
+
 def test_gpu_step_matches_reference_cpu_step(cuda_device):
     """Same check as the CPU host-stack test, but through the CUDA kernels (load_unit 8, as the
     reference's CPU kernel has no progressive loading)."""
