@@ -69,10 +69,12 @@ def lib():
     L.geo_sc_pool_act_backward.argtypes = [i32, i32, i32, vp, vp, vp, vp]
     L.geo_sc_guide_backward_bytes.argtypes = [dp, szp]
     L.geo_sc_guide_backward.argtypes = [dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    L.geo_sc_guide_backward_quantized.argtypes = [dp, vp, vp, vp, vp, vp, vp, sz, vp]
     L.geo_sc_measure_lop3_peak.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
     for n in ("geo_sc_conv2d_forward", "geo_sc_linear_forward", "geo_sc_prepare_weights",
               "geo_sc_generate_act_streams", "geo_sc_accumulate", "geo_sc_group_geometry", "geo_sc_host_stream",
-              "geo_sc_measure_lop3_peak", "geo_sc_guide_backward_bytes", "geo_sc_guide_backward", "geo_sc_bn_fixed_scratch_bytes",
+              "geo_sc_measure_lop3_peak", "geo_sc_guide_backward_bytes", "geo_sc_guide_backward",
+              "geo_sc_guide_backward_quantized", "geo_sc_bn_fixed_scratch_bytes",
               "geo_sc_bn_fixed_forward", "geo_sc_bn_fixed_backward", "geo_sc_pool_act_forward",
               "geo_sc_pool_act_backward"):
         getattr(L, n).restype = i32

@@ -722,8 +722,25 @@ int geo_sc_guide_backward_bytes(const geo_sc_conv_desc *desc, size_t *scratch_by
     return GEO_SC_OK;
 }
 
-int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const float *weight, const float *grad_out,
-                          float *grad_act, float *grad_weight, void *scratch, size_t scratch_bytes, void *stream) {
+}  // extern "C"
+
+namespace geo {
+namespace {
+
+// Overwrites the gradients with NaN when the caller's promise of bf16-exact inputs did not hold.
+__global__ void guide_poison_kernel(float *ga, long long na, float *gw, long long nw, const int *inexact) {
+    if (!*inexact) return;
+    const float nan = __int_as_float(0x7fc00000);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < na + nw; i += stride) {
+        if (i < na) ga[i] = nan;
+        else gw[i - na] = nan;
+    }
+}
+
+int guide_backward_impl(const geo_sc_conv_desc *desc, const float *act, const float *weight, const float *grad_out,
+                        float *grad_act, float *grad_weight, void *scratch, size_t scratch_bytes, void *stream,
+                        bool promised_exact) {
     Geometry g;
     int rc = make_geometry(desc, &g);
     if (rc) return rc;
@@ -752,6 +769,13 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
     if (mma_eligible(g)) {
         rc = launch_mma_backward(g, act, weight, grad_out, grad_act, grad_weight, mma_scratch, &inexact, s);
         if (rc) return rc;
+        if (promised_exact) {
+            const long long na = grad_act ? (long long)d.B * d.C * d.H * d.W : 0;
+            const long long nw = grad_weight ? (long long)d.O * d.C * d.K2 * d.K3 : 0;
+            guide_poison_kernel<<<148, 256, 0, s>>>(grad_act, na, grad_weight, nw, inexact);
+            GEO_CUDA_CHECK(cudaGetLastError());
+            return GEO_SC_OK;
+        }
     }
     pad_act_kernel<<<grid1d((long long)d.B * d.C * d.Hp * d.Wp), 256, 0, s>>>(d, act, apad);
     guide_prep_fwd_kernel<<<grid1d((long long)d.G * d.K * d.Opad), 256, 0, s>>>(d, weight, wf, aoff);
@@ -812,6 +836,22 @@ int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const 
         if (rc) return rc;
     }
     return GEO_SC_OK;
+}
+
+}  // namespace
+}  // namespace geo
+
+extern "C" {
+
+int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act, const float *weight, const float *grad_out,
+                          float *grad_act, float *grad_weight, void *scratch, size_t scratch_bytes, void *stream) {
+    return guide_backward_impl(desc, act, weight, grad_out, grad_act, grad_weight, scratch, scratch_bytes, stream, false);
+}
+
+int geo_sc_guide_backward_quantized(const geo_sc_conv_desc *desc, const float *act, const float *weight,
+                                    const float *grad_out, float *grad_act, float *grad_weight, void *scratch,
+                                    size_t scratch_bytes, void *stream) {
+    return guide_backward_impl(desc, act, weight, grad_out, grad_act, grad_weight, scratch, scratch_bytes, stream, true);
 }
 
 }  // extern "C"

@@ -48,7 +48,9 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
 
     Keyword arguments (defaults as in the reference): ``bit_length`` 128, ``prec`` 128,
     ``share`` True, ``generator`` None, ``forward`` 'full_or', ``legacy`` False, ``load_unit`` 8,
-    ``load_wait_w`` 1, ``load_wait_a`` 1, ``z_unit`` 1024.
+    ``load_wait_w`` 1, ``load_wait_a`` 1, ``z_unit`` 1024.  One extension over the reference:
+    ``quantized`` (default False) promises that both operands went through :func:`quantize` with
+    ``prec`` <= 8, which lets the backward pass run on the tensor-core kernels alone.
 
     ``padding`` follows the reference's convention ``F.pad(x, (p[0], p[0], p[1], p[1]))``: the
     last dimension is padded by ``padding[0]``, dimension 2 by ``padding[1]``
@@ -86,7 +88,8 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
         load_wait_a = load_wait_w  # one load_wait for both operands (sc_cuda.cpp:47-63)
     return sc_conv2d_with_guide(activation, weight, int(bit_length), forward, pad_h=p1, pad_w=p0,
                                 z_unit=int(z_unit), total_width=prec_default, load_width=int(load_unit),
-                                load_wait_w=int(load_wait_w), load_wait_a=int(load_wait_a))
+                                load_wait_w=int(load_wait_w), load_wait_a=int(load_wait_a),
+                                quantized=bool(kwargs.get("quantized", False)))
 
 
 def linear_generic(activation, weight, **kwargs):

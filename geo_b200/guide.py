@@ -20,12 +20,13 @@ from . import ops
 class _SCConv2dGuide(torch.autograd.Function):
     @staticmethod
     def forward(ctx, activation, weight, bit_length, mode, pad_h, pad_w, z_unit, total_width, load_width,
-                load_wait_w, load_wait_a):
+                load_wait_w, load_wait_a, quantized=False):
         kw = dict(z_unit=z_unit, total_width=total_width, load_width=load_width, load_wait_w=load_wait_w,
                   load_wait_a=load_wait_a)
         counts = ops.sc_conv2d_staged(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
         need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if need_a or need_w:
+            ctx.quantized = bool(quantized)
             ctx.desc = ops.desc_for(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
             ctx.save_for_backward(activation, weight)
         return counts.to(torch.float32) / bit_length
@@ -34,16 +35,17 @@ class _SCConv2dGuide(torch.autograd.Function):
     def backward(ctx, grad_out):
         activation, weight = ctx.saved_tensors
         ga, gw = ops.guide_backward(activation, weight, grad_out, ctx.desc, ctx.needs_input_grad[0],
-                                    ctx.needs_input_grad[1])
+                                    ctx.needs_input_grad[1], quantized=ctx.quantized)
         if ga is not None:
             ga = ga.to(activation.dtype)
         if gw is not None:
             gw = gw.to(weight.dtype)
-        return (ga, gw) + (None,) * 9
+        return (ga, gw) + (None,) * 10
 
 
 def sc_conv2d_with_guide(activation, weight, bit_length, mode, pad_h=0, pad_w=0, z_unit=1024, total_width=7,
-                         load_width=8, load_wait_w=1, load_wait_a=1):
-    """SC conv2d value with the guide's gradient; ``pad_h`` / ``pad_w`` pad dimensions 2 / 3."""
+                         load_width=8, load_wait_w=1, load_wait_a=1, quantized=False):
+    """SC conv2d value with the guide's gradient; ``pad_h`` / ``pad_w`` pad dimensions 2 / 3.
+    ``quantized``: the caller's promise of :func:`geo_b200.ops.guide_backward`."""
     return _SCConv2dGuide.apply(activation, weight, bit_length, mode, pad_h, pad_w, z_unit, total_width, load_width,
-                                load_wait_w, load_wait_a)
+                                load_wait_w, load_wait_a, quantized)

@@ -25,7 +25,8 @@ class Conv2d_Add_Partial(nn.Conv2d):
         self.weight.data = sc_f.quantize(self.weight_org, prec=prec)
         return sc_f.conv2d_generic(input, self.weight, bit_length=2 ** err, padding=self.padding, stride=self.stride,
                                    forward=forward, generator=generator, legacy=legacy, z_unit=z_unit,
-                                   load_unit=load_unit, load_wait_w=load_wait_w, load_wait_a=load_wait_a)
+                                   load_unit=load_unit, load_wait_w=load_wait_w, load_wait_a=load_wait_a,
+                                   quantized=prec <= 8)  # k / 2^prec with |k| < 2^8 is exact in bf16
 
 
 class _BatchNormFixed(torch.autograd.Function):

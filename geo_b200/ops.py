@@ -162,8 +162,12 @@ def accumulate(astreams, wprep, desc, out=None):
     return out
 
 
-def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True):
-    """Gradient of the float guide: (grad_act or None, grad_weight or None)."""
+def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True, quantized=False):
+    """Gradient of the float guide: (grad_act or None, grad_weight or None).
+
+    ``quantized=True`` is the caller's promise that ``act`` and ``weight`` are multiples of 2^-8
+    (or coarser) inside [-1, 1]; the tensor-core kernels then run alone, and a broken promise
+    yields NaN gradients (checked on the device)."""
     _require_cuda(act, weight, grad_out)
     a = act.detach().to(torch.float32).contiguous()
     w = weight.detach().to(torch.float32).contiguous()
@@ -178,11 +182,16 @@ def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True)
             if need_act else None
         gw = torch.empty((desc.c_out, desc.c_in, desc.k_h, desc.k_w), dtype=torch.float32, device=dev) \
             if need_weight else None
-        check(_lib.lib().geo_sc_guide_backward(ctypes.byref(desc), a.data_ptr(), w.data_ptr(), go.data_ptr(),
-                                               ga.data_ptr() if need_act else None,
-                                               gw.data_ptr() if need_weight else None, scratch.data_ptr(),
-                                               scratch.numel(), _stream_ptr(dev)), "geo_sc_guide_backward")
-    STATS.launches += 6 + (2 if need_weight else 0) + (2 if need_act else 0)
+        name = "geo_sc_guide_backward_quantized" if quantized else "geo_sc_guide_backward"
+        check(getattr(_lib.lib(), name)(ctypes.byref(desc), a.data_ptr(), w.data_ptr(), go.data_ptr(),
+                                        ga.data_ptr() if need_act else None,
+                                        gw.data_ptr() if need_weight else None, scratch.data_ptr(),
+                                        scratch.numel(), _stream_ptr(dev)), name)
+    per_family = 3 + (2 if need_weight else 0) + (2 if need_act else 0)   # prep x2, forward, wgrad+reduce, prep+dgrad
+    if desc.mode in (MODES["1d_bin"], MODES["full_or"]):
+        STATS.launches += per_family + (1 if quantized else per_family)
+    else:
+        STATS.launches += per_family
     return ga, gw
 
 

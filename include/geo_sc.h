@@ -171,6 +171,15 @@ int geo_sc_guide_backward_bytes(const geo_sc_conv_desc *desc, size_t *scratch_by
 int geo_sc_guide_backward(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
                           const float *grad_out_device, float *grad_act_device, float *grad_weight_device,
                           void *scratch_device, size_t scratch_bytes, void *stream);
+/* Same call for a caller that has already quantised act and weight the way the reference's layer
+ * does before it calls the guide (Conv2d_Add_Partial.forward, utils_class.py:190-204: multiples of
+ * 2^-prec with prec <= 8 inside [-1, 1], which bf16 holds exactly).  For the 1d_bin and full_or
+ * modes only the tensor-core kernels are then launched; should the promise not hold (checked on
+ * the device) the requested gradients are filled with NaN instead of being computed by the fp32
+ * kernels.  Other modes behave exactly like geo_sc_guide_backward. */
+int geo_sc_guide_backward_quantized(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
+                                    const float *grad_out_device, float *grad_act_device, float *grad_weight_device,
+                                    void *scratch_device, size_t scratch_bytes, void *stream);
 
 /* ---- quantised batch normalisation between SC layers -------------------------------------------
  * Replaces BatchNorm2d_fixed / BatchNorm1d_fixed (utils_class.py:37-93), which the reference

@@ -16,7 +16,7 @@ def install(monkeypatch):
         y = oracle.conv2d(act.detach(), weight.detach(), bit_length, mode, pad_h=padding[0], pad_w=padding[1], **kw)
         return torch.from_numpy(y)
 
-    def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True):
+    def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True, quantized=False):
         ga, gw = oracle_guide.guide_grads(act.detach(), weight.detach(), grad_out, _MODE_NAMES[desc.mode],
                                           desc.pad_h, desc.pad_w, z_unit=desc.z_unit)
         return (ga if need_act else None), (gw if need_weight else None)

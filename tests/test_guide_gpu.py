@@ -78,6 +78,33 @@ def test_guide_gradients_for_inputs_that_bf16_cannot_hold(cuda_device, mode):
     _close(ga.cpu(), ga_ref, f"{mode} grad_act (one inexact value)")
 
 
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or"])
+def test_guide_backward_with_quantised_inputs_promise(cuda_device, mode):
+    """geo_sc_guide_backward_quantized: same gradients as the general entry point (bit for bit) for
+    inputs that keep the promise; NaN gradients, not silently wrong ones, for inputs that break it
+    in the modes the tensor-core kernels serve."""
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(31)
+    a = q7(torch.rand(4, 12, 10, 10, generator=g)).to(cuda_device)
+    w = q7((torch.rand(24, 12, 3, 3, generator=g) * 2 - 1) * 0.4).to(cuda_device)
+    desc = ops.desc_for(a, w, 128, mode, (1, 1), z_unit=4)
+    go = torch.randn(*ops.out_shape(desc), generator=g).to(cuda_device)
+    ga0, gw0 = ops.guide_backward(a, w, go, desc)
+    ga1, gw1 = ops.guide_backward(a, w, go, desc, quantized=True)
+    assert torch.equal(ga0, ga1) and torch.equal(gw0, gw1)
+    _, gw2 = ops.guide_backward(a, w, go, desc, need_act=False, quantized=True)
+    assert torch.equal(gw0, gw2)
+    bad = a.clone()
+    bad[0, 0, 0, 0] = 0.123456
+    ga3, gw3 = ops.guide_backward(bad, w, go, desc, quantized=True)
+    if mode in ("1d_bin", "full_or"):
+        assert torch.isnan(ga3).all() and torch.isnan(gw3).all()
+    else:
+        ga4, gw4 = ops.guide_backward(bad, w, go, desc)
+        assert torch.equal(ga3, ga4) and torch.equal(gw3, gw4)
+
+
 def test_layer_autograd_matches_reference_semantics(cuda_device, oracle_lib):
     """conv2d_generic: value = SC counts / L (bit-exact), gradient = guide gradient."""
     from geo_b200 import functional as sc_f
