@@ -113,23 +113,26 @@ __device__ __forceinline__ void split3(float v, __nv_bfloat16 &h0, __nv_bfloat16
 }
 
 // Output: Dh[plane][g][m][n2] bf16, plane = term of the 3-way split of D = gout * exp(-y).
-__global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
-                                                          const __nv_bfloat16 *__restrict__ wb,
-                                                          const float *__restrict__ gout,
-                                                          __nv_bfloat16 *__restrict__ Dh, const int *inexact) {
+// MI = m16 tiles per warp: 2 (4 warps) or 1 (8 warps, half the accumulators per thread).
+template <int MI>
+__global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
+                                                               const __nv_bfloat16 *__restrict__ wb,
+                                                               const float *__restrict__ gout,
+                                                               __nv_bfloat16 *__restrict__ Dh, const int *inexact) {
     if (*inexact) return;   // the FFMA kernels handle inputs that bf16 cannot hold
+    constexpr int NTH = 256 / MI, AROWS = 512 / NTH, BROWS = 256 / NTH, RSTEP = NTH / 4;
     constexpr int A_BYTES = 128 * 64, B_BYTES = 64 * 64, ST_BYTES = A_BYTES + B_BYTES;
     extern __shared__ __align__(128) unsigned char msm[];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int m0 = blockIdx.x * 128, n0 = blockIdx.y * 64, g = blockIdx.z;
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(msm);
 
-    // gather assignment: thread t copies chunk (t & 3) of rows (t >> 2) + 32 * i, i < 4
+    // gather assignment: thread t copies chunk (t & 3) of rows (t >> 2) + RSTEP * i
     const int gchunk = t & 3;
-    long long rbase[4];
+    long long rbase[AROWS];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        int m = m0 + (t >> 2) + 32 * i;
+    for (int i = 0; i < AROWS; i++) {
+        int m = m0 + (t >> 2) + RSTEP * i;
         if (m >= d.M) m = d.M - 1;
         const int b = m / d.HoWo, rem = m % d.HoWo;
         const int oy = rem / d.Wo, ox = rem % d.Wo;
@@ -149,14 +152,14 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
             else { ky = tap / d.K3; kx = tap % d.K3; }
             const long long koff = kv ? ((long long)ky * d.Wp + kx) * d.Cp + c : 0;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int row = (t >> 2) + 32 * i;
+            for (int i = 0; i < AROWS; i++) {
+                const int row = (t >> 2) + RSTEP * i;
                 cp16z(a_s + swz(row, gchunk), apad + rbase[i] + koff, kv);
             }
             // weights: 64 rows (columns n) x 4 chunks
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const int row = (t >> 2) + 32 * i;
+            for (int i = 0; i < BROWS; i++) {
+                const int row = (t >> 2) + RSTEP * i;
                 const __nv_bfloat16 *src = wb + ((size_t)g * d.N2 + n0 + row) * d.Kp + ld * MK + gchunk * 8;
                 cp16z(b_s + swz(row, gchunk), src, true);
             }
@@ -167,9 +170,9 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
 #pragma unroll
     for (int s = 0; s < MSTAGE - 1; s++) issue();
 
-    float acc[2][8][4], sum[2][8][4];
+    float acc[MI][8][4], sum[MI][8][4];
 #pragma unroll
-    for (int mi = 0; mi < 2; mi++)
+    for (int mi = 0; mi < MI; mi++)
 #pragma unroll
         for (int ni = 0; ni < 8; ni++)
 #pragma unroll
@@ -183,11 +186,11 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
         const uint32_t a_s = sbase + (uint32_t)(s % MSTAGE) * ST_BYTES, b_s = a_s + A_BYTES;
 #pragma unroll
         for (int ks = 0; ks < 2; ks++) {
-            uint32_t af[2][4];
+            uint32_t af[MI][4];
 #pragma unroll
-            for (int mi = 0; mi < 2; mi++) {
+            for (int mi = 0; mi < MI; mi++) {
                 // matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
-                const int row = warp * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int row = warp * (16 * MI) + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
                 ldsm_x4(af[mi], a_s + swz(row, ks * 2 + (lane >> 4)));
             }
 #pragma unroll
@@ -197,7 +200,7 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
                 const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
                 ldsm_x4(bf, b_s + swz(row, ks * 2 + ((lane >> 3) & 1)));
 #pragma unroll
-                for (int mi = 0; mi < 2; mi++) {
+                for (int mi = 0; mi < MI; mi++) {
                     mma_bf16(acc[mi][np * 2 + 0], af[mi], bf[0], bf[1]);
                     mma_bf16(acc[mi][np * 2 + 1], af[mi], bf[2], bf[3]);
                 }
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
         if (since_flush >= MFLUSH || s == nchunks - 1) {
             since_flush = 0;
 #pragma unroll
-            for (int mi = 0; mi < 2; mi++)
+            for (int mi = 0; mi < MI; mi++)
 #pragma unroll
                 for (int ni = 0; ni < 8; ni++)
 #pragma unroll
@@ -218,10 +221,10 @@ __global__ void __launch_bounds__(128) mma_forward_kernel(MmaDims d, const __nv_
 
     // epilogue: accumulator (mi, ni, q): row = lane/4 + 8*(q>>1), column = ni*8 + (lane%4)*2 + (q&1)
 #pragma unroll
-    for (int mi = 0; mi < 2; mi++)
+    for (int mi = 0; mi < MI; mi++)
 #pragma unroll
         for (int hr = 0; hr < 2; hr++) {
-            const int m = m0 + warp * 32 + mi * 16 + (lane >> 2) + hr * 8;
+            const int m = m0 + warp * (16 * MI) + mi * 16 + (lane >> 2) + hr * 8;
             if (m >= d.M) continue;
             const int b = m / d.HoWo, rem = m % d.HoWo;
             const size_t plane = (size_t)d.G * d.M * d.N2;
@@ -380,31 +383,236 @@ __global__ void __launch_bounds__(64) mma_wgrad_kernel(MmaDims d, const __nv_bfl
 }
 
 // grad_w[o][c][ky][kx] = [w>=0] * sum_s partial[s][g][k'][o] + [w<=0] * sum_s partial[s][g][k'][Opad+o]
+// A block reduces 32 consecutive outputs (lane = output, so that the reads are coalesced along o);
+// its 8 warps take the slices s = warp, warp + 8, ... and are combined in a fixed order.
 __global__ void __launch_bounds__(256) mma_wgrad_reduce_kernel(MmaDims d, int S, const float *__restrict__ partial,
                                                                const float *__restrict__ w, float *__restrict__ gw,
                                                                const int *inexact) {
     if (*inexact) return;
+    __shared__ float red[2][8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long total = (long long)d.G * d.taps * d.C * d.O;
-    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
-        const int o = (int)(i % d.O);
-        long long r = i / d.O;
-        const int c = (int)(r % d.C); r /= d.C;
-        const int tap = (int)(r % d.taps), g = (int)(r / d.taps);
-        int ky, kx;
-        if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
-        else { ky = tap / d.K3; kx = tap % d.K3; }
-        const int kp = tap * d.Cp + c;
-        const size_t stride = (size_t)d.G * d.Kp * d.N2;
-        const float *p = partial + ((size_t)g * d.Kp + kp) * d.N2;
+    for (long long base = (long long)blockIdx.x * 32; base < total; base += (long long)gridDim.x * 32) {
+        const long long i = base + lane;
         float sp = 0.f, sn = 0.f;
-        for (int s = 0; s < S; s++) {
-            sp += p[s * stride + o];
-            sn += p[s * stride + d.Opad + o];
+        size_t wi = 0;
+        if (i < total) {
+            const int o = (int)(i % d.O);
+            long long r = i / d.O;
+            const int c = (int)(r % d.C); r /= d.C;
+            const int tap = (int)(r % d.taps), g = (int)(r / d.taps);
+            int ky, kx;
+            if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+            else { ky = tap / d.K3; kx = tap % d.K3; }
+            const int kp = tap * d.Cp + c;
+            const size_t stride = (size_t)d.G * d.Kp * d.N2;
+            const float *p = partial + ((size_t)g * d.Kp + kp) * d.N2;
+            for (int s = warp; s < S; s += 8) {
+                sp += p[s * stride + o];
+                sn += p[s * stride + d.Opad + o];
+            }
+            wi = (((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx;
         }
-        const size_t wi = (((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx;
-        const float wv = w[wi];
-        gw[wi] = (wv >= 0.f && wv <= 100.f ? sp : 0.f) + (wv <= 0.f && wv >= -100.f ? sn : 0.f);
+        red[0][warp][lane] = sp;
+        red[1][warp][lane] = sn;
+        __syncthreads();
+        if (warp == 0 && i < total) {
+            sp = red[0][0][lane]; sn = red[1][0][lane];
+#pragma unroll
+            for (int k = 1; k < 8; k++) { sp += red[0][k][lane]; sn += red[1][k][lane]; }
+            const float wv = w[wi];
+            gw[wi] = (wv >= 0.f && wv <= 100.f ? sp : 0.f) + (wv <= 0.f && wv >= -100.f ? sn : 0.f);
+        }
+        __syncthreads();
     }
+}
+
+// ---- forward and weight gradient in one kernel (no activation gradient wanted, short groups) ---------
+// When a group has at most 64 padded members and only grad_weight is asked for (the first layer of a
+// network), D never leaves the registers.  The forward product is computed transposed,
+// y^T = Wb . a^T, with the columns n2 as MMA rows and the positions as MMA columns, so that the
+// accumulator fragments of D^T = gout * exp(-y^T), split into three bf16 terms, are exactly the A
+// fragments of gw^T[n2][k'] += D^T[n2][m] . a[m][k'].
+// CTA: 8 warps on tiles of 128 positions x 64 columns; warp = 16 columns (warp & 3) x 64 positions
+// (warp >> 2); a CTA walks a contiguous range of position tiles and writes two slices of partial sums.
+constexpr int FSTG = 3;
+
+template <int KS>
+__device__ __forceinline__ uint32_t swz_rows(int row, int chunk) {
+    return KS == 4 ? swz128(row, chunk) : swz(row, chunk);
+}
+
+template <int KS>   // k16 steps over the members of a group: Kp = 16 * KS, KS = 2 or 4
+__global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
+                                                                  const __nv_bfloat16 *__restrict__ wb,
+                                                                  const float *__restrict__ gout,
+                                                                  float *__restrict__ partial, int tiles_per_cta,
+                                                                  int vec_ok, const int *inexact) {
+    if (*inexact) return;
+    constexpr int ROWB = KS * 32, CPR = KS * 2;            // bytes and 16-byte chunks per tile row
+    constexpr int A_BYTES = 128 * ROWB;
+    constexpr int RPT = 128 * CPR / 256;                    // rows a thread gathers per stage
+    constexpr int RSTEP = 256 / CPR;
+    extern __shared__ __align__(128) unsigned char fsm[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int wn = warp & 3, wp = warp >> 2;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int n0 = blockIdx.y * 64, g = blockIdx.z;
+    const int ntiles = (d.M + 127) / 128;
+    const int tbeg = min(ntiles, (int)blockIdx.x * tiles_per_cta), tend = min(ntiles, tbeg + tiles_per_cta);
+    const int nt = tend - tbeg;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(fsm);
+    const uint32_t w_s = sbase + FSTG * A_BYTES;
+
+    // gather assignment: thread t copies chunk t % CPR (one tap, 8 channels) of rows t / CPR + RSTEP * i
+    const int gchunk = t % CPR;
+    const int kp = gchunk * 8;
+    const int tap = kp / d.Cp, cch = kp % d.Cp;
+    const bool kvalid = tap < d.taps;
+    int ky, kx;
+    if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+    else { ky = tap / d.K3; kx = tap % d.K3; }
+    const long long koff = kvalid ? ((long long)ky * d.Wp + kx) * d.Cp + cch : 0;
+
+    int ld = 0;
+    auto issue = [&]() {
+        if (ld < nt) {
+            const uint32_t a_s = sbase + (uint32_t)(ld % FSTG) * A_BYTES;
+            const int mc = (tbeg + ld) * 128;
+#pragma unroll
+            for (int i = 0; i < RPT; i++) {
+                const int row = t / CPR + RSTEP * i;
+                const int m = mc + row;
+                const bool v = m < d.M;
+                const int mm = v ? m : 0;
+                const int b = mm / d.HoWo, rem = mm % d.HoWo;
+                const long long rb = (((long long)b * d.Hp + rem / d.Wo) * d.Wp + rem % d.Wo) * d.Cp;
+                cp16z(a_s + swz_rows<KS>(row, gchunk), apad + rb + koff, v && kvalid);
+            }
+            ld++;
+        }
+        cpa_commit();
+    };
+    // the group's weights (64 columns x Kp members) travel with the first stage
+    if (t < 64 * CPR) {
+        const int row = t / CPR;
+        cp16z(w_s + swz_rows<KS>(row, gchunk), wb + ((size_t)g * d.N2 + n0 + row) * d.Kp + gchunk * 8, true);
+    }
+    if (64 * CPR > 256 && t + 256 < 64 * CPR) {
+        const int row = (t + 256) / CPR;
+        cp16z(w_s + swz_rows<KS>(row, gchunk), wb + ((size_t)g * d.N2 + n0 + row) * d.Kp + gchunk * 8, true);
+    }
+#pragma unroll
+    for (int s = 0; s < FSTG - 1; s++) issue();
+    cpa_wait<FSTG - 2>();
+    __syncthreads();
+    uint32_t wf[KS][4];   // A fragments of the forward product: this warp's 16 columns, all members
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        const int row = wn * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldsm_x4(wf[ks], w_s + swz_rows<KS>(row, ks * 2 + (lane >> 4)));
+    }
+
+    float gacc[2 * KS][4], gsum[2 * KS][4];
+#pragma unroll
+    for (int j = 0; j < 2 * KS; j++)
+#pragma unroll
+        for (int q = 0; q < 4; q++) { gacc[j][q] = 0.f; gsum[j][q] = 0.f; }
+
+    // gout rows of this thread's two columns (n2 = n0 + wn*16 + gq and + 8)
+    int orow[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+        const int o = (n0 + wn * 16 + gq + hr * 8) % d.Opad;
+        orow[hr] = o < d.O ? o : -1;
+    }
+
+    for (int s = 0; s < nt; s++) {
+        cpa_wait<FSTG - 2>();
+        __syncthreads();
+        issue();
+        const uint32_t a_s = sbase + (uint32_t)(s % FSTG) * A_BYTES;
+        // position of this thread's first element in the tile, as (image, offset in the image)
+        int m = (tbeg + s) * 128 + wp * 64 + 2 * tq;
+        int b = m / d.HoWo, rem = m % d.HoWo;
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {   // 16 positions = one k16 step of the weight-gradient product
+            // forward: acc[jj] = y^T for columns (gq, gq+8) and positions wp*64 + kk*16 + jj*8 + 2*tq, +1
+            float acc[2][4];
+#pragma unroll
+            for (int jj = 0; jj < 2; jj++)
+#pragma unroll
+                for (int q = 0; q < 4; q++) acc[jj][q] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                uint32_t bf[4];
+                const int row = wp * 64 + kk * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldsm_x4(bf, a_s + swz_rows<KS>(row, ks * 2 + ((lane >> 3) & 1)));
+                mma_bf16(acc[0], wf[ks], bf[0], bf[1]);
+                mma_bf16(acc[1], wf[ks], bf[2], bf[3]);
+            }
+            uint32_t af[3][4];
+#pragma unroll
+            for (int jj = 0; jj < 2; jj++) {
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    float g0 = 0.f, g1 = 0.f;
+                    if (orow[hr] >= 0 && m < d.M) {
+                        const float *src = gout + ((size_t)b * d.O + orow[hr]) * d.HoWo + rem;
+                        if (vec_ok) {
+                            const float2 v2 = __ldg((const float2 *)src);
+                            g0 = v2.x; g1 = v2.y;
+                        } else {
+                            g0 = __ldg(src);
+                            if (m + 1 < d.M)
+                                g1 = rem + 1 < d.HoWo ? __ldg(src + 1)
+                                                      : __ldg(gout + ((size_t)(b + 1) * d.O + orow[hr]) * d.HoWo);
+                        }
+                    }
+                    const float v0 = g0 * expf(-acc[jj][hr * 2 + 0]);
+                    const float v1 = g1 * expf(-acc[jj][hr * 2 + 1]);
+                    // three-term bf16 split of both values at once
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                    const uint32_t p0 = *(uint32_t *)&h;
+                    const float r0 = v0 - __uint_as_float(p0 << 16), r1 = v1 - __uint_as_float(p0 & 0xffff0000u);
+                    h = __floats2bfloat162_rn(r0, r1);
+                    const uint32_t p1 = *(uint32_t *)&h;
+                    const float s0 = r0 - __uint_as_float(p1 << 16), s1 = r1 - __uint_as_float(p1 & 0xffff0000u);
+                    h = __floats2bfloat162_rn(s0, s1);
+                    const uint32_t p2 = *(uint32_t *)&h;
+                    af[0][jj * 2 + hr] = p0; af[1][jj * 2 + hr] = p1; af[2][jj * 2 + hr] = p2;
+                }
+                m += 8; rem += 8;
+                while (rem >= d.HoWo) { rem -= d.HoWo; b++; }
+            }
+#pragma unroll
+            for (int np = 0; np < KS; np++) {
+                // transposed blocks: (m 0-7, k' tile 2np), (m 8-15, k' tile 2np), (m 0-7, tile 2np+1), (m 8-15, tile 2np+1)
+                uint32_t bt[4];
+                const int row = wp * 64 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldsm_x4_t(bt, a_s + swz_rows<KS>(row, np * 2 + (lane >> 4)));
+#pragma unroll
+                for (int p = 0; p < 3; p++) {
+                    mma_bf16(gacc[np * 2 + 0], af[p], bt[0], bt[1]);
+                    mma_bf16(gacc[np * 2 + 1], af[p], bt[2], bt[3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 2 * KS; j++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) { gsum[j][q] += gacc[j][q]; gacc[j][q] = 0.f; }
+    }
+    cpa_wait<0>();
+    // gsum[j][q]: column n2 = n0 + wn*16 + gq + 8*(q>>1), member k' = j*8 + 2*tq + (q&1)
+    float *dst = partial + ((size_t)(blockIdx.x * 2 + wp) * d.G + g) * d.Kp * d.N2;
+#pragma unroll
+    for (int j = 0; j < 2 * KS; j++)
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int n2 = n0 + wn * 16 + gq + 8 * (q >> 1), k = j * 8 + 2 * tq + (q & 1);
+            dst[(size_t)k * d.N2 + n2] = gsum[j][q];
+        }
 }
 
 // ---- activation gradient on the tensor cores ---------------------------------------------------------------
@@ -578,6 +786,7 @@ namespace {
 struct MmaPlan {
     size_t flag_bytes, apad_bytes, wb_bytes, dh_bytes, wd_bytes, partial_bytes;
     int S, slice_len, Cn;
+    int fused_ctas, fused_tiles;   // one-kernel forward + weight gradient: CTAs per (group, column tile), tiles per CTA
     size_t total() const { return flag_bytes + apad_bytes + wb_bytes + dh_bytes + wd_bytes + partial_bytes; }
 };
 
@@ -598,7 +807,15 @@ MmaPlan mma_plan(const MmaDims &d) {
     len = (len + WP - 1) / WP * WP;
     p.slice_len = (int)len;
     p.S = (int)((d.M + len - 1) / len);
-    p.partial_bytes = align_up((size_t)p.S * d.G * d.Kp * d.N2 * 4, 256);
+    // the fused kernel: two resident CTAs per SM, each writing two slices
+    const long long mt = (d.M + 127) / 128;
+    long long X = 148LL * 2 / ((long long)d.G * (d.N2 / 64));
+    if (X < 1) X = 1;
+    if (X > mt) X = mt;
+    p.fused_tiles = (int)((mt + X - 1) / X);
+    p.fused_ctas = (int)((mt + p.fused_tiles - 1) / p.fused_tiles);
+    const int smax = d.Kp <= 64 && 2 * p.fused_ctas > p.S ? 2 * p.fused_ctas : p.S;
+    p.partial_bytes = align_up((size_t)smax * d.G * d.Kp * d.N2 * 4, 256);
     return p;
 }
 
@@ -639,13 +856,35 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
     mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * d.Cp), 256, 0, s>>>(d, act, apad, flag);
     mma_prep_weight_kernel<<<grid1((long long)d.G * d.N2 * d.Kp), 256, 0, s>>>(d, weight, wb, flag);
     GEO_CUDA_CHECK(cudaGetLastError());
+    const int reduce_blocks = (int)std::min<long long>(((long long)d.G * d.taps * d.C * d.O + 31) / 32, 148 * 8);
+    if (grad_weight && !grad_act && d.Kp <= 64) {
+        // forward and weight gradient in one kernel, D stays in registers
+        const int vec_ok = d.HoWo % 2 == 0 && ((uintptr_t)gout & 7) == 0;
+        dim3 grid(p.fused_ctas, d.N2 / 64, d.G);
+        if (d.Kp == 64) {
+            constexpr size_t smem = (size_t)FSTG * 128 * 128 + 64 * 128;
+            static bool done[64] = {};
+            int rc = opt_in_smem(mma_fused_wgrad_kernel<4>, smem, done);
+            if (rc) return rc;
+            mma_fused_wgrad_kernel<4><<<grid, 256, smem, s>>>(d, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag);
+        } else {
+            constexpr size_t smem = (size_t)FSTG * 128 * 64 + 64 * 64;
+            static bool done[64] = {};
+            int rc = opt_in_smem(mma_fused_wgrad_kernel<2>, smem, done);
+            if (rc) return rc;
+            mma_fused_wgrad_kernel<2><<<grid, 256, smem, s>>>(d, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag);
+        }
+        mma_wgrad_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(d, 2 * p.fused_ctas, partial, weight, grad_weight, flag);
+        GEO_CUDA_CHECK(cudaGetLastError());
+        return GEO_SC_OK;
+    }
     {
         constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64);
         static bool done[64] = {};
-        int rc = opt_in_smem(mma_forward_kernel, smem, done);
+        int rc = opt_in_smem(mma_forward_kernel<1>, smem, done);
         if (rc) return rc;
         dim3 grid((d.M + 127) / 128, d.N2 / 64, d.G);
-        mma_forward_kernel<<<grid, 128, smem, s>>>(d, apad, wb, gout, Dh, flag);
+        mma_forward_kernel<1><<<grid, 256, smem, s>>>(d, apad, wb, gout, Dh, flag);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
     if (grad_weight) {
@@ -655,8 +894,7 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         if (rc) return rc;
         dim3 grid(p.S, (d.Kp + 63) / 64, d.G * (d.N2 / 64));
         mma_wgrad_kernel<<<grid, 64, smem, s>>>(d, apad, Dh, partial, p.slice_len, flag);
-        mma_wgrad_reduce_kernel<<<grid1((long long)d.G * d.taps * d.C * d.O), 256, 0, s>>>(d, p.S, partial, weight,
-                                                                                      grad_weight, flag);
+        mma_wgrad_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(d, p.S, partial, weight, grad_weight, flag);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
     if (grad_act) {
