@@ -59,7 +59,7 @@ def _time(fn, reps):
     return ts[len(ts) // 2]
 
 
-def run_config(name, batch=None, reps=10, peak=None, device="cuda:0", guide=False):
+def run_config(name, batch=None, reps=10, peak=None, device="cuda:0", guide=False, first_layer=False):
     ash, wsh, pad, L, mode, lu, lw, z = CONFIGS[name]
     if batch:
         ash = (batch,) + tuple(ash[1:])
@@ -81,7 +81,9 @@ def run_config(name, batch=None, reps=10, peak=None, device="cuda:0", guide=Fals
     t_g = None
     if guide:
         go = torch.randn(ops.out_shape(d), generator=g).to(dev)
-        t_g = _time(lambda: ops.guide_backward(a, w, go, d), reps)
+        # first_layer: what the first layer of a network asks for (no activation gradient, inputs
+        # already quantised by the layer)
+        t_g = _time(lambda: ops.guide_backward(a, w, go, d, need_act=not first_layer, quantized=first_layer), reps)
     rate = lop3 / (t_c * 1e-3)
     G, K, NT, Opad = _lib.group_geometry(d)
     return {"config": name, "act": list(ash), "weight": list(wsh), "L": L, "mode": mode, "groups": G, "members": K,
@@ -99,6 +101,8 @@ def main(argv=None):
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--no-peak", action="store_true")
     ap.add_argument("--guide", action="store_true", help="also time the fp32 guide backward (dgrad + wgrad)")
+    ap.add_argument("--first-layer", action="store_true",
+                    help="with --guide: weight gradient only, inputs promised quantised")
     a = ap.parse_args(argv)
     names = a.config or ["c1", "c2conv1", "c2conv2", "c2conv3", "c2fc1", "c4_1d", "c4_full_or"]
     peak = None
@@ -106,7 +110,7 @@ def main(argv=None):
         peak, _ = ops.measure_lop3_peak()
         print(json.dumps({"lop3_peak_per_s": peak, "lanes_per_clk_per_sm_at_1965MHz": peak / 148 / 1.965e9}))
     for n in names:
-        print(json.dumps(run_config(n, a.batch, a.reps, peak, guide=a.guide)), flush=True)
+        print(json.dumps(run_config(n, a.batch, a.reps, peak, guide=a.guide, first_layer=a.first_layer)), flush=True)
 
 
 if __name__ == "__main__":

@@ -435,24 +435,40 @@ __global__ void __launch_bounds__(256) mma_wgrad_reduce_kernel(MmaDims d, int S,
 // fragments of gw^T[n2][k'] += D^T[n2][m] . a[m][k'].
 // CTA: 8 warps on tiles of 128 positions x 64 columns; warp = 16 columns (warp & 3) x 64 positions
 // (warp >> 2); a CTA walks a contiguous range of position tiles and writes two slices of partial sums.
-constexpr int FSTG = 3;
+constexpr int GSTRIDE = 136;   // floats per staged gout row: 128 positions + 8, so that 8 rows x 32 bytes tile the banks
+
+__device__ __forceinline__ void cp4z(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
 
 template <int KS>
 __device__ __forceinline__ uint32_t swz_rows(int row, int chunk) {
     return KS == 4 ? swz128(row, chunk) : swz(row, chunk);
 }
 
-template <int KS>   // k16 steps over the members of a group: Kp = 16 * KS, KS = 2 or 4
+template <int KS, int OROWS>
+struct FusedCfg {
+    static constexpr int STAGES = OROWS == 32 ? 3 : 2;
+    static constexpr int A_BYTES = 128 * KS * 32, G_BYTES = OROWS * GSTRIDE * 4, ST_BYTES = A_BYTES + G_BYTES;
+    static constexpr int W_BYTES = 64 * KS * 32;
+    static constexpr size_t SMEM = (size_t)STAGES * ST_BYTES + W_BYTES;
+};
+
+// KS: k16 steps over the padded members of a group (Kp = 16 * KS, 2 or 4).  OROWS: distinct gout rows
+// behind a 64-column tile: 32 when c_out <= 32 (both polarities of the same channels), else 64.
+template <int KS, int OROWS>
 __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
                                                                   const __nv_bfloat16 *__restrict__ wb,
                                                                   const float *__restrict__ gout,
                                                                   float *__restrict__ partial, int tiles_per_cta,
                                                                   int vec_ok, const int *inexact) {
     if (*inexact) return;
-    constexpr int ROWB = KS * 32, CPR = KS * 2;            // bytes and 16-byte chunks per tile row
-    constexpr int A_BYTES = 128 * ROWB;
-    constexpr int RPT = 128 * CPR / 256;                    // rows a thread gathers per stage
+    using Cfg = FusedCfg<KS, OROWS>;
+    constexpr int CPR = KS * 2;                             // 16-byte chunks per activation row
+    constexpr int RPT = 128 * CPR / 256;                    // activation rows a thread gathers per stage
     constexpr int RSTEP = 256 / CPR;
+    constexpr int FSTG = Cfg::STAGES;
     extern __shared__ __align__(128) unsigned char fsm[];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int wn = warp & 3, wp = warp >> 2;
@@ -461,10 +477,11 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
     const int ntiles = (d.M + 127) / 128;
     const int tbeg = min(ntiles, (int)blockIdx.x * tiles_per_cta), tend = min(ntiles, tbeg + tiles_per_cta);
     const int nt = tend - tbeg;
+    const int kpairs = (d.taps * d.Cp + 15) / 16;           // k16 steps that hold real members
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(fsm);
-    const uint32_t w_s = sbase + FSTG * A_BYTES;
+    const uint32_t w_s = sbase + FSTG * Cfg::ST_BYTES;
 
-    // gather assignment: thread t copies chunk t % CPR (one tap, 8 channels) of rows t / CPR + RSTEP * i
+    // activation gather: thread t copies chunk t % CPR (one tap, 8 channels) of rows t / CPR + RSTEP * i
     const int gchunk = t % CPR;
     const int kp = gchunk * 8;
     const int tap = kp / d.Cp, cch = kp % d.Cp;
@@ -477,7 +494,7 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
     int ld = 0;
     auto issue = [&]() {
         if (ld < nt) {
-            const uint32_t a_s = sbase + (uint32_t)(ld % FSTG) * A_BYTES;
+            const uint32_t a_s = sbase + (uint32_t)(ld % FSTG) * Cfg::ST_BYTES, g_s = a_s + Cfg::A_BYTES;
             const int mc = (tbeg + ld) * 128;
 #pragma unroll
             for (int i = 0; i < RPT; i++) {
@@ -489,17 +506,45 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
                 const long long rb = (((long long)b * d.Hp + rem / d.Wo) * d.Wp + rem % d.Wo) * d.Cp;
                 cp16z(a_s + swz_rows<KS>(row, gchunk), apad + rb + koff, v && kvalid);
             }
+            // gout: rows = channels behind the column tile, 4 positions (t & 31) per copy
+            const int m4 = mc + (t & 31) * 4;
+            if (vec_ok) {
+                const bool v = m4 < d.M;
+                const int mm = v ? m4 : 0;
+                const int b = mm / d.HoWo, rem = mm % d.HoWo;
+#pragma unroll
+                for (int i = 0; i < OROWS / 8; i++) {
+                    const int r = (t >> 5) + 8 * i;
+                    const int o = (n0 + r) % d.Opad;
+                    const bool ov = v && o < d.O;
+                    cp16z(g_s + (uint32_t)(r * GSTRIDE + (t & 31) * 4) * 4,
+                          gout + ((size_t)b * d.O + (ov ? o : 0)) * d.HoWo + rem, ov);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int m = m4 + e;
+                    const bool v = m < d.M;
+                    const int mm = v ? m : 0;
+                    const int b = mm / d.HoWo, rem = mm % d.HoWo;
+#pragma unroll
+                    for (int i = 0; i < OROWS / 8; i++) {
+                        const int r = (t >> 5) + 8 * i;
+                        const int o = (n0 + r) % d.Opad;
+                        const bool ov = v && o < d.O;
+                        cp4z(g_s + (uint32_t)(r * GSTRIDE + (t & 31) * 4 + e) * 4,
+                             gout + ((size_t)b * d.O + (ov ? o : 0)) * d.HoWo + rem, ov);
+                    }
+                }
+            }
             ld++;
         }
         cpa_commit();
     };
     // the group's weights (64 columns x Kp members) travel with the first stage
-    if (t < 64 * CPR) {
-        const int row = t / CPR;
-        cp16z(w_s + swz_rows<KS>(row, gchunk), wb + ((size_t)g * d.N2 + n0 + row) * d.Kp + gchunk * 8, true);
-    }
-    if (64 * CPR > 256 && t + 256 < 64 * CPR) {
-        const int row = (t + 256) / CPR;
+#pragma unroll
+    for (int i = 0; i < 64 * CPR / 256; i++) {
+        const int row = t / CPR + RSTEP * i;
         cp16z(w_s + swz_rows<KS>(row, gchunk), wb + ((size_t)g * d.N2 + n0 + row) * d.Kp + gchunk * 8, true);
     }
 #pragma unroll
@@ -519,22 +564,17 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
 #pragma unroll
         for (int q = 0; q < 4; q++) { gacc[j][q] = 0.f; gsum[j][q] = 0.f; }
 
-    // gout rows of this thread's two columns (n2 = n0 + wn*16 + gq and + 8)
-    int orow[2];
+    // staged gout rows of this thread's two columns (n2 = n0 + wn*16 + gq and + 8)
+    uint32_t grow[2];
 #pragma unroll
-    for (int hr = 0; hr < 2; hr++) {
-        const int o = (n0 + wn * 16 + gq + hr * 8) % d.Opad;
-        orow[hr] = o < d.O ? o : -1;
-    }
+    for (int hr = 0; hr < 2; hr++) grow[hr] = (uint32_t)(((wn * 16 + gq + hr * 8) % OROWS) * GSTRIDE + wp * 64 + 2 * tq) * 4;
 
     for (int s = 0; s < nt; s++) {
         cpa_wait<FSTG - 2>();
         __syncthreads();
         issue();
-        const uint32_t a_s = sbase + (uint32_t)(s % FSTG) * A_BYTES;
-        // position of this thread's first element in the tile, as (image, offset in the image)
-        int m = (tbeg + s) * 128 + wp * 64 + 2 * tq;
-        int b = m / d.HoWo, rem = m % d.HoWo;
+        const uint32_t a_s = sbase + (uint32_t)(s % FSTG) * Cfg::ST_BYTES;
+        const unsigned char *g_p = fsm + (size_t)(s % FSTG) * Cfg::ST_BYTES + Cfg::A_BYTES;
 #pragma unroll
         for (int kk = 0; kk < 4; kk++) {   // 16 positions = one k16 step of the weight-gradient product
             // forward: acc[jj] = y^T for columns (gq, gq+8) and positions wp*64 + kk*16 + jj*8 + 2*tq, +1
@@ -545,32 +585,22 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
                 for (int q = 0; q < 4; q++) acc[jj][q] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < KS; ks++) {
-                uint32_t bf[4];
-                const int row = wp * 64 + kk * 16 + (lane & 7) + (lane >> 4) * 8;
-                ldsm_x4(bf, a_s + swz_rows<KS>(row, ks * 2 + ((lane >> 3) & 1)));
-                mma_bf16(acc[0], wf[ks], bf[0], bf[1]);
-                mma_bf16(acc[1], wf[ks], bf[2], bf[3]);
+                if (ks < kpairs) {
+                    uint32_t bf[4];
+                    const int row = wp * 64 + kk * 16 + (lane & 7) + (lane >> 4) * 8;
+                    ldsm_x4(bf, a_s + swz_rows<KS>(row, ks * 2 + ((lane >> 3) & 1)));
+                    mma_bf16(acc[0], wf[ks], bf[0], bf[1]);
+                    mma_bf16(acc[1], wf[ks], bf[2], bf[3]);
+                }
             }
             uint32_t af[3][4];
 #pragma unroll
-            for (int jj = 0; jj < 2; jj++) {
+            for (int jj = 0; jj < 2; jj++)
 #pragma unroll
                 for (int hr = 0; hr < 2; hr++) {
-                    float g0 = 0.f, g1 = 0.f;
-                    if (orow[hr] >= 0 && m < d.M) {
-                        const float *src = gout + ((size_t)b * d.O + orow[hr]) * d.HoWo + rem;
-                        if (vec_ok) {
-                            const float2 v2 = __ldg((const float2 *)src);
-                            g0 = v2.x; g1 = v2.y;
-                        } else {
-                            g0 = __ldg(src);
-                            if (m + 1 < d.M)
-                                g1 = rem + 1 < d.HoWo ? __ldg(src + 1)
-                                                      : __ldg(gout + ((size_t)(b + 1) * d.O + orow[hr]) * d.HoWo);
-                        }
-                    }
-                    const float v0 = g0 * expf(-acc[jj][hr * 2 + 0]);
-                    const float v1 = g1 * expf(-acc[jj][hr * 2 + 1]);
+                    const float2 go = *(const float2 *)(g_p + grow[hr] + (kk * 16 + jj * 8) * 4);
+                    const float v0 = go.x * expf(-acc[jj][hr * 2 + 0]);
+                    const float v1 = go.y * expf(-acc[jj][hr * 2 + 1]);
                     // three-term bf16 split of both values at once
                     __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
                     const uint32_t p0 = *(uint32_t *)&h;
@@ -582,19 +612,18 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
                     const uint32_t p2 = *(uint32_t *)&h;
                     af[0][jj * 2 + hr] = p0; af[1][jj * 2 + hr] = p1; af[2][jj * 2 + hr] = p2;
                 }
-                m += 8; rem += 8;
-                while (rem >= d.HoWo) { rem -= d.HoWo; b++; }
-            }
 #pragma unroll
             for (int np = 0; np < KS; np++) {
-                // transposed blocks: (m 0-7, k' tile 2np), (m 8-15, k' tile 2np), (m 0-7, tile 2np+1), (m 8-15, tile 2np+1)
-                uint32_t bt[4];
-                const int row = wp * 64 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldsm_x4_t(bt, a_s + swz_rows<KS>(row, np * 2 + (lane >> 4)));
+                if (np < kpairs) {
+                    // transposed blocks: (m 0-7, k' tile 2np), (m 8-15, k' tile 2np), (m 0-7, tile 2np+1), (m 8-15, tile 2np+1)
+                    uint32_t bt[4];
+                    const int row = wp * 64 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    ldsm_x4_t(bt, a_s + swz_rows<KS>(row, np * 2 + (lane >> 4)));
 #pragma unroll
-                for (int p = 0; p < 3; p++) {
-                    mma_bf16(gacc[np * 2 + 0], af[p], bt[0], bt[1]);
-                    mma_bf16(gacc[np * 2 + 1], af[p], bt[2], bt[3]);
+                    for (int p = 0; p < 3; p++) {
+                        mma_bf16(gacc[np * 2 + 0], af[p], bt[0], bt[1]);
+                        mma_bf16(gacc[np * 2 + 1], af[p], bt[2], bt[3]);
+                    }
                 }
             }
         }
@@ -837,6 +866,18 @@ size_t mma_scratch_bytes(const Geometry &g) {
     return mma_plan(mma_dims(g)).total();
 }
 
+template <int KS, int OROWS>
+int launch_fused(const MmaDims &d, dim3 grid, const __nv_bfloat16 *apad, const __nv_bfloat16 *wb, const float *gout,
+                 float *partial, int tiles, int vec_ok, const int *flag, cudaStream_t s) {
+    static bool done[64] = {};
+    int rc = opt_in_smem(mma_fused_wgrad_kernel<KS, OROWS>, FusedCfg<KS, OROWS>::SMEM, done);
+    if (rc) return rc;
+    mma_fused_wgrad_kernel<KS, OROWS><<<grid, 256, FusedCfg<KS, OROWS>::SMEM, s>>>(d, apad, wb, gout, partial, tiles,
+                                                                                  vec_ok, flag);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
 // Whole backward pass on the tensor cores; every kernel returns at once if an input turned out
 // not to be bf16-exact (*flag_out != 0 after the preparation kernels), in which case the caller's
 // FFMA kernels, which test the same flag the other way round, do the work.
@@ -859,21 +900,17 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
     const int reduce_blocks = (int)std::min<long long>(((long long)d.G * d.taps * d.C * d.O + 31) / 32, 148 * 8);
     if (grad_weight && !grad_act && d.Kp <= 64) {
         // forward and weight gradient in one kernel, D stays in registers
-        const int vec_ok = d.HoWo % 2 == 0 && ((uintptr_t)gout & 7) == 0;
+        const int vec_ok = d.HoWo % 4 == 0 && ((uintptr_t)gout & 15) == 0;   // 16-byte copies of 4 positions
         dim3 grid(p.fused_ctas, d.N2 / 64, d.G);
+        int rc;
         if (d.Kp == 64) {
-            constexpr size_t smem = (size_t)FSTG * 128 * 128 + 64 * 128;
-            static bool done[64] = {};
-            int rc = opt_in_smem(mma_fused_wgrad_kernel<4>, smem, done);
-            if (rc) return rc;
-            mma_fused_wgrad_kernel<4><<<grid, 256, smem, s>>>(d, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag);
+            rc = d.Opad == 32 ? launch_fused<4, 32>(d, grid, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag, s)
+                              : launch_fused<4, 64>(d, grid, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag, s);
         } else {
-            constexpr size_t smem = (size_t)FSTG * 128 * 64 + 64 * 64;
-            static bool done[64] = {};
-            int rc = opt_in_smem(mma_fused_wgrad_kernel<2>, smem, done);
-            if (rc) return rc;
-            mma_fused_wgrad_kernel<2><<<grid, 256, smem, s>>>(d, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag);
+            rc = d.Opad == 32 ? launch_fused<2, 32>(d, grid, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag, s)
+                              : launch_fused<2, 64>(d, grid, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag, s);
         }
+        if (rc) return rc;
         mma_wgrad_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(d, 2 * p.fused_ctas, partial, weight, grad_weight, flag);
         GEO_CUDA_CHECK(cudaGetLastError());
         return GEO_SC_OK;
