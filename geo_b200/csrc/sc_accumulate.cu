@@ -227,12 +227,17 @@ static int launch_tile(const Geometry &g, AccParams pr, cudaStream_t s) {
         configured[dev] = true;
     }
     dim3 grid((unsigned)((g.M + T::MT - 1) / T::MT), (unsigned)(g.Opad / NT), 1);
-    // Aim for several CTAs per SM so that the tail of the last wave is short.
-    const long long tiles = (long long)grid.x * grid.y, want = 148LL * 8;
-    long long splits = (want + tiles - 1) / tiles;
+    // CTAs along grid.z share an output tile and split its (pack, group) pairs.  The split count is
+    // the one that minimises (waves of resident CTAs) x (work of the longest CTA), where a CTA's
+    // fixed cost (pipeline fill, epilogue) is put at 12 members' worth of work.
+    const long long tiles = (long long)grid.x * grid.y, slots = 148LL * MINB;
     const long long pairs = (long long)g.P * g.G;
-    if (splits > pairs) splits = pairs;
-    if (splits < 1) splits = 1;
+    long long splits = 1, best = -1;
+    for (long long c = 1; c <= pairs && c <= 32; c++) {
+        const long long waves = (tiles * c + slots - 1) / slots;
+        const long long cost = waves * (((pairs + c - 1) / c) * g.Kp + 12);
+        if (best < 0 || cost < best) { best = cost; splits = c; }
+    }
     pr.splits = (int)splits;
     grid.z = (unsigned)splits;
     if (splits > 1) GEO_CUDA_CHECK(cudaMemsetAsync(pr.out, 0, (size_t)g.M * g.O * sizeof(int32_t), s));
