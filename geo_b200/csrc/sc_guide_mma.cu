@@ -18,6 +18,8 @@
 // over all channels use this path (1d_bin: the taps of one filter column; full_or: all taps).
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 #include "sc_common.h"
 #include "sc_guide_mma.h"
 
@@ -383,17 +385,22 @@ __global__ void __launch_bounds__(64) mma_wgrad_kernel(MmaDims d, const __nv_bfl
 }
 
 // grad_w[o][c][ky][kx] = [w>=0] * sum_s partial[s][g][k'][o] + [w<=0] * sum_s partial[s][g][k'][Opad+o]
-// A block reduces 32 consecutive outputs (lane = output, so that the reads are coalesced along o);
-// its 8 warps take the slices s = warp, warp + 8, ... and are combined in a fixed order.
+// A warp handles 32 consecutive outputs (lane = output, so that the reads are coalesced along o); SW
+// warps share them, taking the slices s = sub, sub + SW, ..., and are combined in a fixed order.
+template <int SW>
 __global__ void __launch_bounds__(256) mma_wgrad_reduce_kernel(MmaDims d, int S, const float *__restrict__ partial,
                                                                const float *__restrict__ w, float *__restrict__ gw,
                                                                const int *inexact) {
     if (*inexact) return;
     __shared__ float red[2][8][32];
+    constexpr int GROUPS = 8 / SW;                        // sets of 32 outputs per block and pass
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = warp % SW, grp = warp / SW;
     const long long total = (long long)d.G * d.taps * d.C * d.O;
-    for (long long base = (long long)blockIdx.x * 32; base < total; base += (long long)gridDim.x * 32) {
-        const long long i = base + lane;
+    const long long per_pass = (long long)gridDim.x * GROUPS * 32;
+    const size_t stride = (size_t)d.G * d.Kp * d.N2;
+    for (long long pass0 = 0; pass0 < total; pass0 += per_pass) {
+        const long long i = pass0 + ((long long)blockIdx.x * GROUPS + grp) * 32 + lane;
         float sp = 0.f, sn = 0.f;
         size_t wi = 0;
         if (i < total) {
@@ -404,26 +411,41 @@ __global__ void __launch_bounds__(256) mma_wgrad_reduce_kernel(MmaDims d, int S,
             int ky, kx;
             if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
             else { ky = tap / d.K3; kx = tap % d.K3; }
-            const int kp = tap * d.Cp + c;
-            const size_t stride = (size_t)d.G * d.Kp * d.N2;
-            const float *p = partial + ((size_t)g * d.Kp + kp) * d.N2;
-            for (int s = warp; s < S; s += 8) {
-                sp += p[s * stride + o];
-                sn += p[s * stride + d.Opad + o];
+            const float *p = partial + ((size_t)g * d.Kp + tap * d.Cp + c) * d.N2 + o;
+#pragma unroll 4
+            for (int s = sub; s < S; s += SW) {
+                sp += p[s * stride];
+                sn += p[s * stride + d.Opad];
             }
             wi = (((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx;
         }
-        red[0][warp][lane] = sp;
-        red[1][warp][lane] = sn;
-        __syncthreads();
-        if (warp == 0 && i < total) {
-            sp = red[0][0][lane]; sn = red[1][0][lane];
+        if (SW > 1) {
+            red[0][warp][lane] = sp;
+            red[1][warp][lane] = sn;
+            __syncthreads();
+            if (sub == 0) {
 #pragma unroll
-            for (int k = 1; k < 8; k++) { sp += red[0][k][lane]; sn += red[1][k][lane]; }
+                for (int k = 1; k < SW; k++) { sp += red[0][warp + k][lane]; sn += red[1][warp + k][lane]; }
+            }
+        }
+        if (sub == 0 && i < total) {
             const float wv = w[wi];
             gw[wi] = (wv >= 0.f && wv <= 100.f ? sp : 0.f) + (wv <= 0.f && wv >= -100.f ? sn : 0.f);
         }
-        __syncthreads();
+        if (SW > 1) __syncthreads();
+    }
+}
+
+void launch_wgrad_reduce(const MmaDims &d, int S, const float *partial, const float *w, float *gw, const int *flag,
+                         cudaStream_t s) {
+    const long long sets = ((long long)d.G * d.taps * d.C * d.O + 31) / 32;
+    const int sw = S <= 4 ? 1 : (S <= 16 ? 2 : (S <= 64 ? 4 : 8));
+    const int blocks = (int)std::min<long long>((sets * sw + 7) / 8, 148 * 16);
+    switch (sw) {
+    case 1: mma_wgrad_reduce_kernel<1><<<blocks, 256, 0, s>>>(d, S, partial, w, gw, flag); break;
+    case 2: mma_wgrad_reduce_kernel<2><<<blocks, 256, 0, s>>>(d, S, partial, w, gw, flag); break;
+    case 4: mma_wgrad_reduce_kernel<4><<<blocks, 256, 0, s>>>(d, S, partial, w, gw, flag); break;
+    default: mma_wgrad_reduce_kernel<8><<<blocks, 256, 0, s>>>(d, S, partial, w, gw, flag); break;
     }
 }
 
@@ -897,7 +919,6 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
     mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * d.Cp), 256, 0, s>>>(d, act, apad, flag);
     mma_prep_weight_kernel<<<grid1((long long)d.G * d.N2 * d.Kp), 256, 0, s>>>(d, weight, wb, flag);
     GEO_CUDA_CHECK(cudaGetLastError());
-    const int reduce_blocks = (int)std::min<long long>(((long long)d.G * d.taps * d.C * d.O + 31) / 32, 148 * 8);
     if (grad_weight && !grad_act && d.Kp <= 64) {
         // forward and weight gradient in one kernel, D stays in registers
         const int vec_ok = d.HoWo % 4 == 0 && ((uintptr_t)gout & 15) == 0;   // 16-byte copies of 4 positions
@@ -911,7 +932,7 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
                               : launch_fused<2, 64>(d, grid, apad, wb, gout, partial, p.fused_tiles, vec_ok, flag, s);
         }
         if (rc) return rc;
-        mma_wgrad_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(d, 2 * p.fused_ctas, partial, weight, grad_weight, flag);
+        launch_wgrad_reduce(d, 2 * p.fused_ctas, partial, weight, grad_weight, flag, s);
         GEO_CUDA_CHECK(cudaGetLastError());
         return GEO_SC_OK;
     }
@@ -931,7 +952,7 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         if (rc) return rc;
         dim3 grid(p.S, (d.Kp + 63) / 64, d.G * (d.N2 / 64));
         mma_wgrad_kernel<<<grid, 64, smem, s>>>(d, apad, Dh, partial, p.slice_len, flag);
-        mma_wgrad_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(d, p.S, partial, weight, grad_weight, flag);
+        launch_wgrad_reduce(d, p.S, partial, weight, grad_weight, flag, s);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
     if (grad_act) {
