@@ -318,7 +318,31 @@ __global__ void __launch_bounds__(256) pool_act_bwd_kernel(int planes, int H, in
 }  // namespace
 }  // namespace geo
 
+namespace geo {
+namespace {
+// y = clamp(rint(x * 2^prec), -(2^prec - 1), 2^prec - 1) / 2^prec; NaN stays NaN
+__global__ void __launch_bounds__(256) quantize_kernel(const float *x, float *y, long long n, float levels, float inv) {
+    const long long stride = (long long)gridDim.x * 256;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+        const float v = x[i];
+        const float q = fminf(fmaxf(rintf(v * levels), 1.0f - levels), levels - 1.0f) * inv;
+        y[i] = v != v ? v : q;
+    }
+}
+}  // namespace
+}  // namespace geo
+
 extern "C" {
+
+int geo_sc_quantize(const float *x, float *y, size_t n, int prec, void *stream) {
+    if (prec < 0 || prec > 23) return fail(GEO_SC_ERR_SHAPE, "prec %d outside 0..23", prec);
+    if (n == 0) return GEO_SC_OK;
+    if (!x || !y) return fail(GEO_SC_ERR_NULL, "x or y is NULL");
+    const float levels = (float)(1 << prec);
+    quantize_kernel<<<bn_grid((long long)n), 256, 0, (cudaStream_t)stream>>>(x, y, (long long)n, levels, 1.0f / levels);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
 
 int geo_sc_pool_act_forward(int planes, int height, int width, const float *x, float *y, void *stream) {
     if (planes < 1 || height < 2 || width < 2) return fail(GEO_SC_ERR_SHAPE, "planes %d height %d width %d", planes, height, width);

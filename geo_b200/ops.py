@@ -249,6 +249,18 @@ def bn_fixed_backward(x, grad_out, weight, mean, invstd, training, need_affine=T
     return gx, gw, gb
 
 
+def quantize(x, prec):
+    """clamp(round(x * 2^prec), +-(2^prec - 1)) / 2^prec of a CUDA tensor as one kernel."""
+    _require_cuda(x)
+    xc = x.detach().to(torch.float32).contiguous()
+    with torch.cuda.device(xc.device):
+        y = torch.empty_like(xc)
+        check(_lib.lib().geo_sc_quantize(xc.data_ptr(), y.data_ptr(), xc.numel(), int(prec), _stream_ptr(xc.device)),
+              "geo_sc_quantize")
+    STATS.launches += 1
+    return y
+
+
 def pool_act_forward(x):
     """hardtanh(avg_pool2d(x, 2), 0, 1) for x [B,C,H,W]."""
     _require_cuda(x)

@@ -205,6 +205,12 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
                              const float *save_invstd_device, float *grad_x_device, float *grad_weight_device,
                              float *grad_bias_device, void *scratch_device, size_t scratch_bytes, void *stream);
 
+/* ---- fixed-point rounding of activations and weights ----------------------------------------------
+ * Replaces quantize (utils_functional.py:33-39), which the reference evaluates as four element-wise
+ * PyTorch ops: y = clamp(round_half_even(x * 2^prec), -(2^prec - 1), 2^prec - 1) / 2^prec, one kernel.
+ * x and y: device, n floats; y may be x.  prec 0..23. */
+int geo_sc_quantize(const float *x_device, float *y_device, size_t n, int prec, void *stream);
+
 /* 2x2 average pooling (stride 2, a trailing odd row or column is dropped) followed by
  * hardtanh(0, 1): the activation the reference puts between SC layers (network.py:168-184,
  * nn.AvgPool2d(2) then nn.Hardtanh(0,1)), one pass per direction.  x is [planes][height][width]

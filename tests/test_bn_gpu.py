@@ -85,3 +85,25 @@ def test_pool_hardtanh_matches_pytorch(cuda_device, shape):
     y.backward(go.to(cuda_device))
     assert torch.allclose(y.detach().cpu(), yr.detach(), rtol=0, atol=1e-7)
     assert torch.allclose(xd.grad.cpu(), xr.grad, rtol=0, atol=1e-7)
+
+
+def test_native_quantize_equals_the_elementwise_formula(cuda_device):
+    """geo_sc_quantize against (x * 2^p).round().clamp(...) / 2^p (utils_functional.py:33-39), bit for bit:
+    ties (round half to even), values beyond the clamp, negative zero, infinities, NaN, ragged sizes."""
+    from geo_b200 import functional as sc_f
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    for prec in (0, 1, 7, 8, 12):
+        levels = 2 ** prec
+        x = torch.cat([
+            (torch.rand(100003, generator=g) * 4 - 2),
+            (torch.arange(-3 * levels, 3 * levels + 1, dtype=torch.float32) + 0.5) / levels,   # every tie
+            torch.tensor([0.0, -0.0, 1.0, -1.0, float("inf"), float("-inf"), float("nan"), 1e-30, -1e-30, 3e38]),
+        ]).to(cuda_device)
+        want = (x * levels).round().clamp(-levels + 1, levels - 1) / levels
+        got = ops.quantize(x, prec)
+        assert torch.equal(torch.nan_to_num(got, nan=123.0), torch.nan_to_num(want, nan=123.0)), prec
+        assert torch.equal(torch.isnan(got), torch.isnan(want))
+        assert torch.equal(sc_f.quantize(x, prec=prec).isnan(), want.isnan())
+    assert ops.quantize(torch.empty(0, device=cuda_device), 7).numel() == 0
