@@ -38,7 +38,8 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 }
 
 // mode 0: sum(x)   mode 1: sum((x - mean)^2)   -> partial[c][s]
-template <int MODE>
+// VEC: rows of HW floats are read as float4 (HW % 4 == 0, 16-byte aligned base).
+template <int MODE, bool VEC>
 __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnDims d, const float *__restrict__ x,
                                                                const float *__restrict__ mean,
                                                                float *__restrict__ partial) {
@@ -47,12 +48,27 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnDims d, const f
     const int b0 = (int)((long long)d.B * s / d.S), b1 = (int)((long long)d.B * (s + 1) / d.S);
     const float mu = MODE == 1 ? mean[c] : 0.f;
     float acc = 0.f;
-    const long long n = (long long)(b1 - b0) * d.HW;
-    for (long long i = threadIdx.x; i < n; i += BN_THREADS) {
-        const int b = b0 + (int)(i / d.HW), p = (int)(i % d.HW);
-        const float v = x[((size_t)b * d.C + c) * d.HW + p];
-        if (MODE == 0) acc += v;
-        else acc = fmaf(v - mu, v - mu, acc);
+    if (VEC) {
+        const unsigned q = (unsigned)d.HW >> 2, n = (unsigned)(b1 - b0) * q;
+        float a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (unsigned i = threadIdx.x; i < n; i += BN_THREADS) {
+            const unsigned b = b0 + i / q, p = i % q;
+            const float4 v = __ldg((const float4 *)(x + ((size_t)b * d.C + c) * d.HW) + p);
+            if (MODE == 0) { acc += v.x; a1 += v.y; a2 += v.z; a3 += v.w; }
+            else {
+                acc = fmaf(v.x - mu, v.x - mu, acc); a1 = fmaf(v.y - mu, v.y - mu, a1);
+                a2 = fmaf(v.z - mu, v.z - mu, a2); a3 = fmaf(v.w - mu, v.w - mu, a3);
+            }
+        }
+        acc = (acc + a1) + (a2 + a3);
+    } else {
+        const unsigned n = (unsigned)(b1 - b0) * (unsigned)d.HW;
+        for (unsigned i = threadIdx.x; i < n; i += BN_THREADS) {
+            const unsigned b = b0 + i / (unsigned)d.HW, p = i % (unsigned)d.HW;
+            const float v = x[((size_t)b * d.C + c) * d.HW + p];
+            if (MODE == 0) acc += v;
+            else acc = fmaf(v - mu, v - mu, acc);
+        }
     }
     const float tot = block_sum(acc, red);
     if (threadIdx.x == 0) partial[c * d.S + s] = tot;
@@ -123,17 +139,30 @@ __global__ void __launch_bounds__(BN_THREADS) bn_fold_kernel(BnDims d, int train
     }
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(BnDims d, const float *__restrict__ x,
                                                               const float *__restrict__ wq, const float *__restrict__ bq,
                                                               float *__restrict__ out) {
-    const long long total = (long long)d.B * d.C * d.HW;
-    for (long long i = (long long)blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * BN_THREADS) {
-        const int c = (int)((i / d.HW) % d.C);
-        out[i] = x[i] * wq[c] + bq[c];
+    const unsigned stride = gridDim.x * BN_THREADS;
+    if (VEC) {
+        const unsigned q = (unsigned)d.HW >> 2, total = (unsigned)d.B * d.C * q;
+        for (unsigned i = blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += stride) {
+            const unsigned c = (i / q) % (unsigned)d.C;
+            const float w = wq[c], b = bq[c];
+            const float4 v = __ldg((const float4 *)x + i);
+            ((float4 *)out)[i] = make_float4(v.x * w + b, v.y * w + b, v.z * w + b, v.w * w + b);
+        }
+    } else {
+        const unsigned total = (unsigned)d.B * d.C * d.HW;
+        for (unsigned i = blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += stride) {
+            const unsigned c = (i / (unsigned)d.HW) % (unsigned)d.C;
+            out[i] = x[i] * wq[c] + bq[c];
+        }
     }
 }
 
 // backward pass 1: partial sums of g and g * xhat
+template <bool VEC>
 __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(BnDims d, const float *__restrict__ x,
                                                                    const float *__restrict__ g,
                                                                    const float *__restrict__ mean,
@@ -144,13 +173,28 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(BnDims d, con
     const int b0 = (int)((long long)d.B * s / d.S), b1 = (int)((long long)d.B * (s + 1) / d.S);
     const float mu = mean[c], is = invstd[c];
     float sg = 0.f, sgx = 0.f;
-    const long long n = (long long)(b1 - b0) * d.HW;
-    for (long long i = threadIdx.x; i < n; i += BN_THREADS) {
-        const int b = b0 + (int)(i / d.HW), p = (int)(i % d.HW);
-        const size_t idx = ((size_t)b * d.C + c) * d.HW + p;
-        const float gv = g[idx];
-        sg += gv;
-        sgx = fmaf(gv, (x[idx] - mu) * is, sgx);
+    if (VEC) {
+        const unsigned q = (unsigned)d.HW >> 2, n = (unsigned)(b1 - b0) * q;
+        float sg1 = 0.f, sgx1 = 0.f;
+        for (unsigned i = threadIdx.x; i < n; i += BN_THREADS) {
+            const unsigned b = b0 + i / q, p = i % q;
+            const size_t row = ((size_t)b * d.C + c) * d.HW;
+            const float4 gv = __ldg((const float4 *)(g + row) + p);
+            const float4 xv = __ldg((const float4 *)(x + row) + p);
+            sg += gv.x + gv.y; sg1 += gv.z + gv.w;
+            sgx = fmaf(gv.x, (xv.x - mu) * is, sgx); sgx1 = fmaf(gv.y, (xv.y - mu) * is, sgx1);
+            sgx = fmaf(gv.z, (xv.z - mu) * is, sgx); sgx1 = fmaf(gv.w, (xv.w - mu) * is, sgx1);
+        }
+        sg += sg1; sgx += sgx1;
+    } else {
+        const unsigned n = (unsigned)(b1 - b0) * (unsigned)d.HW;
+        for (unsigned i = threadIdx.x; i < n; i += BN_THREADS) {
+            const unsigned b = b0 + i / (unsigned)d.HW, p = i % (unsigned)d.HW;
+            const size_t idx = ((size_t)b * d.C + c) * d.HW + p;
+            const float gv = g[idx];
+            sg += gv;
+            sgx = fmaf(gv, (x[idx] - mu) * is, sgx);
+        }
     }
     const float t0 = block_sum(sg, red);
     const float t1 = block_sum(sgx, red);
@@ -176,6 +220,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_final_kernel(BnDims d, cons
     }
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnDims d, int training, const float *__restrict__ x,
                                                                   const float *__restrict__ g,
                                                                   const float *__restrict__ mean,
@@ -183,17 +228,32 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnDims d, int 
                                                                   const float *__restrict__ weight,
                                                                   const float *__restrict__ sums,
                                                                   float *__restrict__ gx) {
-    const long long total = (long long)d.B * d.C * d.HW;
     const float inv_n = 1.0f / ((float)d.B * (float)d.HW);
-    for (long long i = (long long)blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * BN_THREADS) {
-        const int c = (int)((i / d.HW) % d.C);
+    const unsigned stride = gridDim.x * BN_THREADS;
+    const unsigned q = VEC ? (unsigned)d.HW >> 2 : (unsigned)d.HW, total = (unsigned)d.B * d.C * q;
+    for (unsigned i = blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += stride) {
+        const unsigned c = (i / q) % (unsigned)d.C;
         const float w = weight ? weight[c] : 1.0f;
         const float is = invstd[c];
-        if (training) {
-            const float xhat = (x[i] - mean[c]) * is;
-            gx[i] = w * is * (g[i] - sums[c * 2] * inv_n - xhat * sums[c * 2 + 1] * inv_n);
+        const float k = w * is;
+        // gx = w * is * (g - sum_g / N - xhat * sum_gx / N), same association per element
+        const float a = training ? sums[c * 2] * inv_n : 0.f, bb = training ? sums[c * 2 + 1] * inv_n : 0.f;
+        const float mu = mean[c];
+        if (VEC) {
+            const float4 gv = __ldg((const float4 *)g + i);
+            float4 r;
+            if (training) {
+                const float4 xv = __ldg((const float4 *)x + i);
+                r.x = k * (gv.x - a - (xv.x - mu) * is * bb);
+                r.y = k * (gv.y - a - (xv.y - mu) * is * bb);
+                r.z = k * (gv.z - a - (xv.z - mu) * is * bb);
+                r.w = k * (gv.w - a - (xv.w - mu) * is * bb);
+            } else {
+                r = make_float4(k * gv.x, k * gv.y, k * gv.z, k * gv.w);
+            }
+            ((float4 *)gx)[i] = r;
         } else {
-            gx[i] = w * is * g[i];
+            gx[i] = training ? k * (g[i] - a - (x[i] - mu) * is * bb) : k * g[i];
         }
     }
 }
@@ -242,14 +302,18 @@ int geo_sc_bn_fixed_forward(int batch, int channels, int spatial, int training, 
     float *partial = (float *)scratch;
     float *wq = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
     float *bq = wq + channels;
+    const bool vec = spatial % 4 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
     if (training) {
-        bn_reduce_kernel<0><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
+        if (vec) bn_reduce_kernel<0, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
+        else bn_reduce_kernel<0, false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
         bn_mean_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, save_mean);
-        bn_reduce_kernel<1><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
+        if (vec) bn_reduce_kernel<1, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
+        else bn_reduce_kernel<1, false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
     }
     bn_fold_kernel<<<1, BN_THREADS, 0, s>>>(d, training, eps, momentum, partial, save_mean, save_invstd, weight, bias,
                                             running_mean, running_var, wq, bq, scale_out);
-    bn_apply_kernel<<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(d, x, wq, bq, out);
+    if (vec) bn_apply_kernel<true><<<bn_grid((long long)batch * channels * spatial / 4), BN_THREADS, 0, s>>>(d, x, wq, bq, out);
+    else bn_apply_kernel<false><<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(d, x, wq, bq, out);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -266,10 +330,17 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
     BnDims d = {batch, channels, spatial, bn_slices(batch, channels)};
     float *partial = (float *)scratch;
     float *sums = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
-    bn_bwd_reduce_kernel<<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, grad_out, save_mean, save_invstd, partial);
+    if ((long long)batch * channels * spatial > (1LL << 31) - 1) return fail(GEO_SC_ERR_TOO_LARGE, "tensor too large");
+    const bool vec = spatial % 4 == 0 && (((uintptr_t)x | (uintptr_t)grad_out | (uintptr_t)grad_x) & 15) == 0;
+    if (vec) bn_bwd_reduce_kernel<true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, grad_out, save_mean, save_invstd, partial);
+    else bn_bwd_reduce_kernel<false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, grad_out, save_mean, save_invstd, partial);
     bn_bwd_final_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, sums, grad_weight, grad_bias);
-    bn_bwd_apply_kernel<<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(d, training, x, grad_out, save_mean,
-                                                                                      save_invstd, weight, sums, grad_x);
+    if (vec)
+        bn_bwd_apply_kernel<true><<<bn_grid((long long)batch * channels * spatial / 4), BN_THREADS, 0, s>>>(
+            d, training, x, grad_out, save_mean, save_invstd, weight, sums, grad_x);
+    else
+        bn_bwd_apply_kernel<false><<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(
+            d, training, x, grad_out, save_mean, save_invstd, weight, sums, grad_x);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -315,6 +386,50 @@ __global__ void __launch_bounds__(256) pool_act_bwd_kernel(int planes, int H, in
     }
 }
 
+// Vector forms for even H and W % 4 == 0: a thread owns two horizontally adjacent windows, i.e. one
+// float4 of each of the two input rows.  Rows of windows: r = plane * (H/2) + oy, input rows 2r, 2r+1.
+__global__ void __launch_bounds__(256) pool_act_fwd_vec_kernel(unsigned rows, unsigned W, const float *__restrict__ x,
+                                                               float *__restrict__ y) {
+    const unsigned q = W >> 2, total = rows * q;
+    for (unsigned i = blockIdx.x * 256 + threadIdx.x; i < total; i += gridDim.x * 256) {
+        const unsigned r = i / q, j = i % q;
+        const float4 t = __ldg((const float4 *)(x + (size_t)(2 * r) * W) + j);
+        const float4 b = __ldg((const float4 *)(x + (size_t)(2 * r + 1) * W) + j);
+        const float v0 = (t.x + t.y + b.x + b.y) / 4.0f, v1 = (t.z + t.w + b.z + b.w) / 4.0f;
+        ((float2 *)(y + (size_t)r * (W >> 1)))[j] = make_float2(fminf(fmaxf(v0, 0.0f), 1.0f), fminf(fmaxf(v1, 0.0f), 1.0f));
+    }
+}
+
+__global__ void __launch_bounds__(256) pool_act_bwd_vec_kernel(unsigned rows, unsigned W, const float *__restrict__ x,
+                                                               const float *__restrict__ gy, float *__restrict__ gx) {
+    const unsigned q = W >> 2, total = rows * q;
+    for (unsigned i = blockIdx.x * 256 + threadIdx.x; i < total; i += gridDim.x * 256) {
+        const unsigned r = i / q, j = i % q;
+        const float4 t = __ldg((const float4 *)(x + (size_t)(2 * r) * W) + j);
+        const float4 b = __ldg((const float4 *)(x + (size_t)(2 * r + 1) * W) + j);
+        const float2 g = __ldg((const float2 *)(gy + (size_t)r * (W >> 1)) + j);
+        const float v0 = (t.x + t.y + b.x + b.y) / 4.0f, v1 = (t.z + t.w + b.z + b.w) / 4.0f;
+        const float g0 = v0 > 0.0f && v0 < 1.0f ? g.x * 0.25f : 0.0f;
+        const float g1 = v1 > 0.0f && v1 < 1.0f ? g.y * 0.25f : 0.0f;
+        const float4 o = make_float4(g0, g0, g1, g1);
+        ((float4 *)(gx + (size_t)(2 * r) * W))[j] = o;
+        ((float4 *)(gx + (size_t)(2 * r + 1) * W))[j] = o;
+    }
+}
+
+__global__ void __launch_bounds__(256) quantize_vec_kernel(const float4 *x, float4 *y, unsigned n4, float levels, float inv) {
+    for (unsigned i = blockIdx.x * 256 + threadIdx.x; i < n4; i += gridDim.x * 256) {
+        const float4 v = x[i];
+        float4 r;
+        const float lo = 1.0f - levels, hi = levels - 1.0f;
+        r.x = v.x != v.x ? v.x : fminf(fmaxf(rintf(v.x * levels), lo), hi) * inv;
+        r.y = v.y != v.y ? v.y : fminf(fmaxf(rintf(v.y * levels), lo), hi) * inv;
+        r.z = v.z != v.z ? v.z : fminf(fmaxf(rintf(v.z * levels), lo), hi) * inv;
+        r.w = v.w != v.w ? v.w : fminf(fmaxf(rintf(v.w * levels), lo), hi) * inv;
+        y[i] = r;
+    }
+}
+
 }  // namespace
 }  // namespace geo
 
@@ -339,7 +454,11 @@ int geo_sc_quantize(const float *x, float *y, size_t n, int prec, void *stream) 
     if (n == 0) return GEO_SC_OK;
     if (!x || !y) return fail(GEO_SC_ERR_NULL, "x or y is NULL");
     const float levels = (float)(1 << prec);
-    quantize_kernel<<<bn_grid((long long)n), 256, 0, (cudaStream_t)stream>>>(x, y, (long long)n, levels, 1.0f / levels);
+    if (n % 4 == 0 && n / 4 < (1ULL << 32) && (((uintptr_t)x | (uintptr_t)y) & 15) == 0)
+        quantize_vec_kernel<<<bn_grid((long long)(n / 4)), 256, 0, (cudaStream_t)stream>>>((const float4 *)x, (float4 *)y,
+                                                                                       (unsigned)(n / 4), levels, 1.0f / levels);
+    else
+        quantize_kernel<<<bn_grid((long long)n), 256, 0, (cudaStream_t)stream>>>(x, y, (long long)n, levels, 1.0f / levels);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -348,7 +467,12 @@ int geo_sc_pool_act_forward(int planes, int height, int width, const float *x, f
     if (planes < 1 || height < 2 || width < 2) return fail(GEO_SC_ERR_SHAPE, "planes %d height %d width %d", planes, height, width);
     if (!x || !y) return fail(GEO_SC_ERR_NULL, "x or y is NULL");
     const long long total = (long long)planes * (height / 2) * (width / 2);
-    pool_act_fwd_kernel<<<bn_grid(total), 256, 0, (cudaStream_t)stream>>>(planes, height, width, x, y);
+    if (height % 2 == 0 && width % 4 == 0 && (long long)planes * height * width < (1LL << 32) &&
+        (((uintptr_t)x & 15) | ((uintptr_t)y & 7)) == 0)
+        pool_act_fwd_vec_kernel<<<bn_grid(total / 2), 256, 0, (cudaStream_t)stream>>>((unsigned)(planes * (height / 2)),
+                                                                                 (unsigned)width, x, y);
+    else
+        pool_act_fwd_kernel<<<bn_grid(total), 256, 0, (cudaStream_t)stream>>>(planes, height, width, x, y);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -358,7 +482,12 @@ int geo_sc_pool_act_backward(int planes, int height, int width, const float *x, 
     if (planes < 1 || height < 2 || width < 2) return fail(GEO_SC_ERR_SHAPE, "planes %d height %d width %d", planes, height, width);
     if (!x || !grad_y || !grad_x) return fail(GEO_SC_ERR_NULL, "x, grad_y or grad_x is NULL");
     const long long total = (long long)planes * height * width;
-    pool_act_bwd_kernel<<<bn_grid(total), 256, 0, (cudaStream_t)stream>>>(planes, height, width, x, grad_y, grad_x);
+    if (height % 2 == 0 && width % 4 == 0 && total < (1LL << 32) &&
+        ((((uintptr_t)x | (uintptr_t)grad_x) & 15) | ((uintptr_t)grad_y & 7)) == 0)
+        pool_act_bwd_vec_kernel<<<bn_grid(total / 8), 256, 0, (cudaStream_t)stream>>>((unsigned)(planes * (height / 2)),
+                                                                                 (unsigned)width, x, grad_y, grad_x);
+    else
+        pool_act_bwd_kernel<<<bn_grid(total), 256, 0, (cudaStream_t)stream>>>(planes, height, width, x, grad_y, grad_x);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

@@ -70,7 +70,7 @@ def test_bn_fixed_matches_reference_formulation(cuda_device, shape, training, af
     assert torch.allclose(m.running_var.cpu(), rv, rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("shape", [(8, 5, 12, 12), (3, 4, 7, 9), (256, 32, 32, 32)])
+@pytest.mark.parametrize("shape", [(8, 5, 12, 12), (3, 4, 7, 9), (2, 3, 6, 10), (256, 32, 32, 32)])
 def test_pool_hardtanh_matches_pytorch(cuda_device, shape):
     from geo_b200 import layers
 
