@@ -688,24 +688,29 @@ __global__ void __launch_bounds__(256) mma_prep_wd_kernel(MmaDims d, int Cn, con
 
 constexpr int DSTG = 3;
 
-__global__ void __launch_bounds__(128) mma_dgrad_kernel(MmaDims d, int Cn, const __nv_bfloat16 *__restrict__ Dh,
-                                                        const __nv_bfloat16 *__restrict__ wd, float *__restrict__ ga,
-                                                        const int *inexact) {
+// NWC warps along the channels: a CTA of 4 * NWC warps covers 128 pixels x 32 * NWC channels, so that one
+// staged D tile serves NWC times as many channels.
+template <int NWC>
+__global__ void __launch_bounds__(128 * NWC) mma_dgrad_kernel(MmaDims d, int Cn, const __nv_bfloat16 *__restrict__ Dh,
+                                                              const __nv_bfloat16 *__restrict__ wd,
+                                                              float *__restrict__ ga, const int *inexact) {
     if (*inexact) return;
-    constexpr int A_BYTES = 128 * 64, B_BYTES = 32 * 64, ST_BYTES = 3 * A_BYTES + B_BYTES;
+    constexpr int NTH = 128 * NWC;
+    constexpr int A_BYTES = 128 * 64, B_BYTES = 32 * NWC * 64, ST_BYTES = 3 * A_BYTES + B_BYTES;
+    constexpr int AROWS = 512 / NTH, RSTEP = NTH / 4;   // D rows a thread gathers per plane and stage
     extern __shared__ __align__(128) unsigned char dsm2[];
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int p0 = blockIdx.x * 128, c0 = blockIdx.y * 32;
+    const int t = threadIdx.x, lane = t & 31, warp = (t >> 5) & 3, wc = t >> 7;
+    const int p0 = blockIdx.x * 128, c0 = blockIdx.y * (32 * NWC) + wc * 32;
     const int HW = d.H * d.W, Min = d.B * HW;
     const int R = d.K2 * d.K3 * d.N2;
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dsm2);
     const size_t plane = (size_t)d.G * d.M * d.N2;
 
     const int gchunk = t & 3;
-    int pb[4], py[4], px[4];
+    int pb[AROWS], py[AROWS], px[AROWS];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        int pix = p0 + (t >> 2) + 32 * i;
+    for (int i = 0; i < AROWS; i++) {
+        int pix = p0 + (t >> 2) + RSTEP * i;
         const bool v = pix < Min;
         if (!v) pix = 0;
         const int b = pix / HW, rem = pix % HW;
@@ -723,8 +728,8 @@ __global__ void __launch_bounds__(128) mma_dgrad_kernel(MmaDims d, int Cn, const
             const int ky = tap / d.K3, kx = tap % d.K3;
             const int g = d.mode == GEO_SC_MODE_1D ? kx : 0;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int row = (t >> 2) + 32 * i;
+            for (int i = 0; i < AROWS; i++) {
+                const int row = (t >> 2) + RSTEP * i;
                 const int oy = py[i] - ky, ox = px[i] - kx;
                 const bool v = pb[i] >= 0 && oy >= 0 && oy < d.Ho && ox >= 0 && ox < d.Wo;
                 const size_t m = v ? (size_t)pb[i] * d.HoWo + oy * d.Wo + ox : 0;
@@ -732,9 +737,9 @@ __global__ void __launch_bounds__(128) mma_dgrad_kernel(MmaDims d, int Cn, const
 #pragma unroll
                 for (int p = 0; p < 3; p++) cp16z(a_s + p * A_BYTES + swz(row, gchunk), src + p * plane, v);
             }
-            {   // weights: 32 rows (channels) x 4 chunks = 128 copies, one per thread
+            {   // weights: 32 * NWC rows (channels) x 4 chunks, one copy per thread
                 const int row = t >> 2;
-                const __nv_bfloat16 *src = wd + (size_t)(c0 + row) * R + (size_t)ld * 32 + gchunk * 8;
+                const __nv_bfloat16 *src = wd + (size_t)(blockIdx.y * (32 * NWC) + row) * R + (size_t)ld * 32 + gchunk * 8;
                 cp16z(b_s + swz(row, gchunk), src, true);
             }
             ld++;
@@ -763,7 +768,7 @@ __global__ void __launch_bounds__(128) mma_dgrad_kernel(MmaDims d, int Cn, const
             uint32_t bf[2][4];
 #pragma unroll
             for (int np = 0; np < 2; np++) {
-                const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
+                const int row = wc * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
                 ldsm_x4(bf[np], b_s + swz(row, ks * 2 + ((lane >> 3) & 1)));
             }
 #pragma unroll
@@ -900,6 +905,19 @@ int launch_fused(const MmaDims &d, dim3 grid, const __nv_bfloat16 *apad, const _
     return GEO_SC_OK;
 }
 
+template <int NWC>
+int launch_dgrad(const MmaDims &d, int Cn, const __nv_bfloat16 *Dh, const __nv_bfloat16 *wd, float *grad_act,
+                 const int *flag, cudaStream_t s) {
+    constexpr size_t smem = (size_t)DSTG * (3 * 128 * 64 + 32 * NWC * 64);
+    static bool done[64] = {};
+    int rc = opt_in_smem(mma_dgrad_kernel<NWC>, smem, done);
+    if (rc) return rc;
+    dim3 grid((d.B * d.H * d.W + 127) / 128, Cn / (32 * NWC));
+    mma_dgrad_kernel<NWC><<<grid, 128 * NWC, smem, s>>>(d, Cn, Dh, wd, grad_act, flag);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
 // Whole backward pass on the tensor cores; every kernel returns at once if an input turned out
 // not to be bf16-exact (*flag_out != 0 after the preparation kernels), in which case the caller's
 // FFMA kernels, which test the same flag the other way round, do the work.
@@ -957,13 +975,13 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
     }
     if (grad_act) {
         mma_prep_wd_kernel<<<grid1((long long)p.Cn * d.K2 * d.K3 * d.N2), 256, 0, s>>>(d, p.Cn, weight, wd);
-        constexpr size_t smem = (size_t)DSTG * (3 * 128 * 64 + 32 * 64);
-        static bool done[64] = {};
-        int rc = opt_in_smem(mma_dgrad_kernel, smem, done);
+        // widest channel tile that still leaves four CTAs of work per SM
+        const long long ptiles = ((long long)d.B * d.H * d.W + 127) / 128;
+        int rc;
+        if (p.Cn % 128 == 0 && ptiles * (p.Cn / 128) >= 148 * 4) rc = launch_dgrad<4>(d, p.Cn, Dh, wd, grad_act, flag, s);
+        else if (p.Cn % 64 == 0 && ptiles * (p.Cn / 64) >= 148 * 4) rc = launch_dgrad<2>(d, p.Cn, Dh, wd, grad_act, flag, s);
+        else rc = launch_dgrad<1>(d, p.Cn, Dh, wd, grad_act, flag, s);
         if (rc) return rc;
-        dim3 grid((d.B * d.H * d.W + 127) / 128, p.Cn / 32);
-        mma_dgrad_kernel<<<grid, 128, smem, s>>>(d, p.Cn, Dh, wd, grad_act, flag);
-        GEO_CUDA_CHECK(cudaGetLastError());
     }
     return GEO_SC_OK;
 }

@@ -22,6 +22,7 @@ CASES = [
     ((3, 16, 4, 4), (10, 16, 4, 4), (0, 0), 16),
     ((2, 40, 6, 6), (70, 40, 3, 3), (1, 1), 16),
     ((9, 24, 1, 1), (12, 24, 1, 1), (0, 0), 8),
+    ((3, 128, 6, 6), (16, 128, 3, 3), (1, 1), 16),   # 128 input channels: widest activation-gradient tile
 ]
 
 
