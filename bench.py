@@ -218,7 +218,9 @@ def run_native(args):
                          "frac": achieved / peak_lop3 if peak_lop3 else None,
                          "peak_source": "measured live: unrolled independent LOP3 chains on all SMs",
                          "launches_timed": len(ops.STATS.records), "avg_launch_ms": acc_ms / n_acc,
-                         "traffic": None,
+                         "traffic": ACC_DRAM_BYTES_PER_LAUNCH if (args.workload == "tiny_cnn" and B == 256) else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the step's four "
+                                           "accumulate launches (profiles/accumulate_kernel_cnn_layers_dram_traffic.md)",
                          "hbm": {"achieved": nbytes / (acc_ms * 1e-3) / 1e9 if acc_ms > 0 else 0.0, "peak": hbm_peak,
                                  "unit": "GB/s", "peak_source": how + " (MEASURED_PEAKS.json)"}},
         }
@@ -228,6 +230,11 @@ def run_native(args):
         dist.barrier()
         dist.destroy_process_group()
     return out
+
+
+# DRAM bytes per accumulate launch of the default workload (4-layer CNN, 256 images), mean of the four
+# layers' launches: 16.07 + 61.72 + 24.78 + 4.80 MB read, < 0.1 MB written (one ncu capture).
+ACC_DRAM_BYTES_PER_LAUNCH = 26.85e6
 
 
 def cpu_baseline(seconds=12.0, batch=64, min_steps=2):

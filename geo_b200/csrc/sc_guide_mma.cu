@@ -686,11 +686,11 @@ __global__ void __launch_bounds__(256) mma_prep_wd_kernel(MmaDims d, int Cn, con
     }
 }
 
-constexpr int DSTG = 3;
 
 // NWC warps along the channels: a CTA of 4 * NWC warps covers 128 pixels x 32 * NWC channels, so that one
 // staged D tile serves NWC times as many channels.
-template <int NWC>
+// DSTG: stages of the cp.async ring (2 lets four CTAs share an SM; 3 when there are too few CTAs for that).
+template <int NWC, int DSTG>
 __global__ void __launch_bounds__(128 * NWC) mma_dgrad_kernel(MmaDims d, int Cn, const __nv_bfloat16 *__restrict__ Dh,
                                                               const __nv_bfloat16 *__restrict__ wd,
                                                               float *__restrict__ ga, const int *inexact) {
@@ -855,7 +855,7 @@ MmaPlan mma_plan(const MmaDims &d) {
     p.Cn = (d.C + 31) / 32 * 32;
     p.wd_bytes = align_up((size_t)p.Cn * d.K2 * d.K3 * d.N2 * 2, 256);
     const long long tiles = (long long)d.G * ((d.Kp + 63) / 64) * (d.N2 / 64);
-    long long S = (148LL * 8 + tiles - 1) / tiles;
+    long long S = 148LL * 8 / tiles;   // at most two full waves of four resident CTAs per SM, no third
     const long long maxS = (d.M + WP - 1) / WP;
     if (S > maxS) S = maxS;
     if (S < 1) S = 1;
@@ -905,17 +905,25 @@ int launch_fused(const MmaDims &d, dim3 grid, const __nv_bfloat16 *apad, const _
     return GEO_SC_OK;
 }
 
+template <int NWC, int DSTG>
+int launch_dgrad_staged(const MmaDims &d, int Cn, const __nv_bfloat16 *Dh, const __nv_bfloat16 *wd, float *grad_act,
+                        const int *flag, cudaStream_t s) {
+    constexpr size_t smem = (size_t)DSTG * (3 * 128 * 64 + 32 * NWC * 64);
+    static bool done[64] = {};
+    int rc = opt_in_smem(mma_dgrad_kernel<NWC, DSTG>, smem, done);
+    if (rc) return rc;
+    dim3 grid((d.B * d.H * d.W + 127) / 128, Cn / (32 * NWC));
+    mma_dgrad_kernel<NWC, DSTG><<<grid, 128 * NWC, smem, s>>>(d, Cn, Dh, wd, grad_act, flag);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
 template <int NWC>
 int launch_dgrad(const MmaDims &d, int Cn, const __nv_bfloat16 *Dh, const __nv_bfloat16 *wd, float *grad_act,
                  const int *flag, cudaStream_t s) {
-    constexpr size_t smem = (size_t)DSTG * (3 * 128 * 64 + 32 * NWC * 64);
-    static bool done[64] = {};
-    int rc = opt_in_smem(mma_dgrad_kernel<NWC>, smem, done);
-    if (rc) return rc;
-    dim3 grid((d.B * d.H * d.W + 127) / 128, Cn / (32 * NWC));
-    mma_dgrad_kernel<NWC><<<grid, 128 * NWC, smem, s>>>(d, Cn, Dh, wd, grad_act, flag);
-    GEO_CUDA_CHECK(cudaGetLastError());
-    return GEO_SC_OK;
+    const long long ctas = (((long long)d.B * d.H * d.W + 127) / 128) * (Cn / (32 * NWC));
+    return ctas >= 148 * 2 ? launch_dgrad_staged<NWC, 2>(d, Cn, Dh, wd, grad_act, flag, s)
+                           : launch_dgrad_staged<NWC, 3>(d, Cn, Dh, wd, grad_act, flag, s);
 }
 
 // Whole backward pass on the tensor cores; every kernel returns at once if an input turned out
