@@ -108,6 +108,9 @@ void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan) {
         else { p = 0; bit = L - t; }
         plan->mask[p][lev] |= 1u << bit;
     }
+    for (int p = 0; p < kMaxPacks; p++)
+        for (int j = 0; j < plan->nlev; j++)
+            if (plan->mask[p][j]) plan->act[p][plan->nact[p]++] = (unsigned char)j;
 }
 
 static size_t wprep_bytes(const Geometry &g) {

@@ -44,6 +44,10 @@ struct LoadPlan {
     int nlev;
     int shift[kMaxLevels];
     uint32_t mask[kMaxPacks][kMaxLevels];
+    // per pack, the levels whose mask is not empty (with progressive loading only the first pack
+    // sees more than one): the generators loop over these instead of all nlev levels
+    unsigned char nact[kMaxPacks];
+    unsigned char act[kMaxPacks][kMaxLevels];
 };
 void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan);
 

@@ -55,22 +55,33 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 
 // ---- preparation --------------------------------------------------------------------------------
 // NCHW fp32 -> padded NHWC bf16, raising *inexact if a value is not representable in bf16.
+// One thread per pixel and group of 8 channels: eight plane reads (consecutive threads = consecutive
+// channel groups, then consecutive x, so a warp reads whole 32-byte sectors) and one 16-byte store.
 __global__ void __launch_bounds__(256) mma_prep_act_kernel(MmaDims d, const float *__restrict__ act,
                                                            __nv_bfloat16 *__restrict__ out, int *inexact) {
-    const long long total = (long long)d.B * d.Hp * d.Wp * d.Cp;
+    const unsigned cg = (unsigned)d.Cp >> 3;
+    const unsigned total = (unsigned)d.B * d.Hp * d.Wp * cg;    // < 2^31: the padded tensor is indexed by int
+    const size_t hw = (size_t)d.H * d.W;
     bool bad = false;
-    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
-        const int c = (int)(i % d.Cp);
-        long long r = i / d.Cp;
-        const int x = (int)(r % d.Wp); r /= d.Wp;
-        const int y = (int)(r % d.Hp);
-        const int b = (int)(r / d.Hp);
+    for (unsigned i = blockIdx.x * 256 + threadIdx.x; i < total; i += gridDim.x * 256) {
+        const unsigned c0 = (i % cg) * 8;
+        unsigned r = i / cg;
+        const int x = (int)(r % (unsigned)d.Wp); r /= (unsigned)d.Wp;
+        const int y = (int)(r % (unsigned)d.Hp);
+        const int b = (int)(r / (unsigned)d.Hp);
         const int yi = y - d.ph, xi = x - d.pw;
-        float v = 0.0f;
-        if (c < d.C && yi >= 0 && yi < d.H && xi >= 0 && xi < d.W) v = act[(((size_t)b * d.C + c) * d.H + yi) * d.W + xi];
-        const __nv_bfloat16 h = __float2bfloat16_rn(v);
-        bad |= (__bfloat162float(h) != v);
-        out[i] = h;
+        const bool in = yi >= 0 && yi < d.H && xi >= 0 && xi < d.W;
+        const float *src = act + ((size_t)b * d.C + c0) * hw + (in ? (size_t)yi * d.W + xi : 0);
+        uint32_t pk[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float v0 = in && (int)c0 + 2 * j < d.C ? __ldg(src + (size_t)(2 * j) * hw) : 0.0f;
+            const float v1 = in && (int)c0 + 2 * j + 1 < d.C ? __ldg(src + (size_t)(2 * j + 1) * hw) : 0.0f;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+            pk[j] = *(const uint32_t *)&h;
+            bad |= (__uint_as_float(pk[j] << 16) != v0) | (__uint_as_float(pk[j] & 0xffff0000u) != v1);
+        }
+        ((uint4 *)out)[i] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
     if (bad) atomicOr(inexact, 1);
 }
@@ -942,7 +953,7 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
     float *partial = (float *)(base + p.flag_bytes + p.apad_bytes + p.wb_bytes + p.dh_bytes + p.wd_bytes);
     *flag_out = flag;
     GEO_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int), s));
-    mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * d.Cp), 256, 0, s>>>(d, act, apad, flag);
+    mma_prep_act_kernel<<<grid1((long long)d.B * d.Hp * d.Wp * (d.Cp / 8)), 256, 0, s>>>(d, act, apad, flag);
     mma_prep_weight_kernel<<<grid1((long long)d.G * d.N2 * d.Kp), 256, 0, s>>>(d, weight, wb, flag);
     GEO_CUDA_CHECK(cudaGetLastError());
     if (grad_weight && !grad_act && d.Kp <= 64) {

@@ -92,7 +92,8 @@ struct GenParams {
     int B, C, H, W, pad_h, pad_w, Hp, Wp;
     int O, K2, K3;
     int L, P, mode, z, G, K, Kp, Opad;
-    int RW;
+    int RW;    // words per pattern row in the global table
+    int RWS;   // ... in shared memory: odd, so that the rows of different values fall into different banks
 };
 
 static GenParams gen_params(const Geometry &g) {
@@ -101,13 +102,14 @@ static GenParams gen_params(const Geometry &g) {
     p.O = g.O; p.K2 = g.K2; p.K3 = g.K3;
     p.L = g.L; p.P = g.P; p.mode = g.mode; p.z = g.z; p.G = g.G; p.K = g.K; p.Kp = g.Kp; p.Opad = g.Opad;
     p.RW = row_words(g.L);
+    p.RWS = p.RW | 1;
     return p;
 }
 
 // Copies the pattern table and phase table for stream length L into shared memory.
-__device__ __forceinline__ void load_tables(uint32_t *s_pat, uint16_t *s_q0, int L, int RW) {
+__device__ __forceinline__ void load_tables(uint32_t *s_pat, uint16_t *s_q0, int L, int RW, int RWS) {
     const uint32_t *src = g_pattern + table_offset(L);
-    for (int i = threadIdx.x; i < L * RW; i += blockDim.x) s_pat[i] = src[i];
+    for (int i = threadIdx.x; i < L * RW; i += blockDim.x) s_pat[(i / RW) * RWS + i % RW] = src[i];
     const uint16_t *q = g_q0[l_index(L)];
     for (int i = threadIdx.x; i < L; i += blockDim.x) s_q0[i] = q[i];
     __syncthreads();
@@ -127,15 +129,14 @@ __host__ __device__ __forceinline__ uint32_t stream_word(const uint32_t *s_pat, 
     uint32_t word = 0;
     const int q = q0 + 32 * p;
     const int i = q >> 5, sh = q & 31;
-    for (int j = 0; j < plan.nlev; j++) {
-        const uint32_t m = plan.mask[p][j];
-        if (m) {
-            const int vj = (V >> plan.shift[j]) << plan.shift[j];
-            const uint32_t *row = s_pat + vj * RW;
-            uint32_t w32 = funnel_left(row[i + 1], row[i], sh);
-            if (L < 32) w32 >>= (32 - L);
-            word |= w32 & m;
-        }
+    const int n = plan.nact[p];
+    for (int e = 0; e < n; e++) {
+        const int j = plan.act[p][e];
+        const int vj = (V >> plan.shift[j]) << plan.shift[j];
+        const uint32_t *row = s_pat + vj * RW;
+        uint32_t w32 = funnel_left(row[i + 1], row[i], sh);
+        if (L < 32) w32 >>= (32 - L);
+        word |= w32 & plan.mask[p][j];
     }
     return word;
 }
@@ -148,8 +149,8 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
                                                               uint32_t *__restrict__ ws, int32_t *__restrict__ aoff) {
     extern __shared__ uint32_t smem[];
     uint32_t *s_pat = smem;
-    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RW);
-    load_tables(s_pat, s_q0, gp.L, gp.RW);
+    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RWS);
+    load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
 
     const long long total = (long long)gp.G * gp.Kp * gp.Opad;
     const float fL = (float)gp.L;
@@ -184,8 +185,8 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
         const int qn = s_q0[(37 + sidx) % (gp.L - 1) + 1];
         for (int p = 0; p < gp.P; p++) {
             uint2 v;
-            v.x = Vp ? stream_word(s_pat, gp.RW, gp.L, Vp, qp, p, plan) : 0u;
-            v.y = Vn ? stream_word(s_pat, gp.RW, gp.L, Vn, qn, p, plan) : 0u;
+            v.x = Vp ? stream_word(s_pat, gp.RWS, gp.L, Vp, qp, p, plan) : 0u;
+            v.y = Vn ? stream_word(s_pat, gp.RWS, gp.L, Vn, qn, p, plan) : 0u;
             *(uint2 *)(ws + ((((size_t)p * gp.G + g) * gp.Kp + k) * gp.Opad + o) * 2) = v;
         }
     }
@@ -194,22 +195,23 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
 // ---- activation streams ---------------------------------------------------------------------
 // One thread per element of the padded image; fuses zero padding and the float -> level
 // quantisation (sc_cuda.cpp:50-51).  Layout [batch][pack][c][Hp][Wp].
+// 32-bit index arithmetic: the geometry check bounds the padded tensor by 2^31 elements, and 64-bit
+// divisions would cost several times the stream generation itself.
 __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan plan, const float *__restrict__ act,
                                                           uint32_t *__restrict__ as) {
     extern __shared__ uint32_t smem[];
     uint32_t *s_pat = smem;
-    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RW);
-    load_tables(s_pat, s_q0, gp.L, gp.RW);
+    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RWS);
+    load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
 
-    const int plane = gp.Hp * gp.Wp;
-    const long long total = (long long)gp.B * gp.C * plane;
+    const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
+    const unsigned total = (unsigned)gp.B * gp.C * plane;
     const float fL = (float)gp.L;
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int yx = (int)(idx % plane);
-        const int bc = (int)(idx / plane);
-        const int c = bc % gp.C, b = bc / gp.C;
-        const int y = yx / gp.Wp, x = yx % gp.Wp;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned yx = idx % plane;
+        const unsigned bc = idx / plane;
+        const int c = (int)(bc % (unsigned)gp.C), b = (int)(bc / (unsigned)gp.C);
+        const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
         const int yi = y - gp.pad_h, xi = x - gp.pad_w;
         int V = 0;
         if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W) {
@@ -217,11 +219,11 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
             V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
         }
         const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
-        const int sidx = (cc * gp.Hp + y) * gp.Wp + x;
-        const int q0 = s_q0[sidx % (gp.L - 1) + 1];
+        const unsigned sidx = (unsigned)((cc * gp.Hp + y) * gp.Wp + x);
+        const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
         uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
         for (int p = 0; p < gp.P; p++)
-            dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RW, gp.L, V, q0, p, plan) : 0u;
+            dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
     }
 }
 
@@ -237,7 +239,7 @@ int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream,
     GenParams gp = gen_params(g);
     LoadPlan plan;
     make_load_plan(g.L, g.tw, g.lu, g.lw_w, &plan);
-    const size_t smem = (size_t)g.L * gp.RW * 4 + (size_t)g.L * 2;
+    const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     const long long total = (long long)g.G * g.Kp * g.Opad;
     prepare_weights_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, w, wstream, aoff);
     GEO_CUDA_CHECK(cudaGetLastError());
@@ -250,7 +252,7 @@ int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, c
     GenParams gp = gen_params(g);
     LoadPlan plan;
     make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
-    const size_t smem = (size_t)g.L * gp.RW * 4 + (size_t)g.L * 2;
+    const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     const long long total = (long long)g.B * g.C * g.Hp * g.Wp;
     act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
     GEO_CUDA_CHECK(cudaGetLastError());
