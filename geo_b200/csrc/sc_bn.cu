@@ -417,6 +417,21 @@ __global__ void __launch_bounds__(256) pool_act_bwd_vec_kernel(unsigned rows, un
     }
 }
 
+// SC bit counts -> the layer's value counts / bit_length (exact: bit_length is a power of two)
+template <bool VEC>
+__global__ void __launch_bounds__(256) counts_to_float_kernel(const int32_t *__restrict__ c, float *__restrict__ y, size_t n,
+                                                              float inv) {
+    const size_t stride = (size_t)gridDim.x * 256;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+        if (VEC) {
+            const int4 v = __ldg((const int4 *)c + i);
+            ((float4 *)y)[i] = make_float4((float)v.x * inv, (float)v.y * inv, (float)v.z * inv, (float)v.w * inv);
+        } else {
+            y[i] = (float)c[i] * inv;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) quantize_vec_kernel(const float4 *x, float4 *y, unsigned n4, float levels, float inv) {
     for (unsigned i = blockIdx.x * 256 + threadIdx.x; i < n4; i += gridDim.x * 256) {
         const float4 v = x[i];
@@ -459,6 +474,18 @@ int geo_sc_quantize(const float *x, float *y, size_t n, int prec, void *stream) 
                                                                                        (unsigned)(n / 4), levels, 1.0f / levels);
     else
         quantize_kernel<<<bn_grid((long long)n), 256, 0, (cudaStream_t)stream>>>(x, y, (long long)n, levels, 1.0f / levels);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int geo_sc_counts_to_float(const int32_t *counts, float *out, size_t n, int bit_length, void *stream) {
+    if (bit_length < 1 || (bit_length & (bit_length - 1))) return fail(GEO_SC_ERR_BIT_LENGTH, "bit_length %d is not a power of two", bit_length);
+    if (n == 0) return GEO_SC_OK;
+    if (!counts || !out) return fail(GEO_SC_ERR_NULL, "counts or out is NULL");
+    const float inv = 1.0f / (float)bit_length;
+    const bool vec = n % 4 == 0 && n / 4 < (1ULL << 32) && (((uintptr_t)counts | (uintptr_t)out) & 15) == 0;
+    if (vec) counts_to_float_kernel<true><<<bn_grid((long long)(n / 4)), 256, 0, (cudaStream_t)stream>>>(counts, out, n / 4, inv);
+    else counts_to_float_kernel<false><<<bn_grid((long long)n), 256, 0, (cudaStream_t)stream>>>(counts, out, n, inv);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

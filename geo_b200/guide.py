@@ -29,7 +29,7 @@ class _SCConv2dGuide(torch.autograd.Function):
             ctx.quantized = bool(quantized)
             ctx.desc = ops.desc_for(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
             ctx.save_for_backward(activation, weight)
-        return torch.mul(counts, 1.0 / bit_length)   # bit_length is a power of two: exact, one kernel
+        return ops.counts_to_float(counts, bit_length)
 
     @staticmethod
     def backward(ctx, grad_out):

@@ -261,6 +261,20 @@ def quantize(x, prec):
     return y
 
 
+def counts_to_float(counts, bit_length):
+    """SC bit counts (int32, CUDA) -> float32 counts / bit_length as one kernel."""
+    _require_cuda(counts)
+    c = counts.contiguous()
+    if c.dtype != torch.int32:
+        raise TypeError(f"counts must be int32, got {c.dtype}")
+    with torch.cuda.device(c.device):
+        y = torch.empty(c.shape, dtype=torch.float32, device=c.device)
+        check(_lib.lib().geo_sc_counts_to_float(c.data_ptr(), y.data_ptr(), c.numel(), int(bit_length),
+                                                _stream_ptr(c.device)), "geo_sc_counts_to_float")
+    STATS.launches += 1
+    return y
+
+
 def pool_act_forward(x):
     """hardtanh(avg_pool2d(x, 2), 0, 1) for x [B,C,H,W]."""
     _require_cuda(x)

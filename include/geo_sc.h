@@ -211,6 +211,11 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
  * x and y: device, n floats; y may be x.  prec 0..23. */
 int geo_sc_quantize(const float *x_device, float *y_device, size_t n, int prec, void *stream);
 
+/* The hand-off from bit counts to the layer's value (utils_functional.py:497-498, 632-634:
+ * result.float() / bit_length written over the guide's output), one kernel: out = counts / bit_length,
+ * exact because bit_length is a power of two.  counts and out: device, n elements. */
+int geo_sc_counts_to_float(const int32_t *counts_device, float *out_device, size_t n, int bit_length, void *stream);
+
 /* 2x2 average pooling (stride 2, a trailing odd row or column is dropped) followed by
  * hardtanh(0, 1): the activation the reference puts between SC layers (network.py:168-184,
  * nn.AvgPool2d(2) then nn.Hardtanh(0,1)), one pass per direction.  x is [planes][height][width]

@@ -107,3 +107,13 @@ def test_native_quantize_equals_the_elementwise_formula(cuda_device):
         assert torch.equal(torch.isnan(got), torch.isnan(want))
         assert torch.equal(sc_f.quantize(x, prec=prec).isnan(), want.isnan())
     assert ops.quantize(torch.empty(0, device=cuda_device), 7).numel() == 0
+
+
+def test_counts_to_float_is_exact(cuda_device):
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(11)
+    for shape in ((256, 32, 16, 16), (3, 5, 7), (0,)):
+        c = torch.randint(-5 * 256, 5 * 256, shape, generator=g, dtype=torch.int32).to(cuda_device)
+        for L in (8, 128, 256):
+            assert torch.equal(ops.counts_to_float(c, L), c.to(torch.float32) / L)
