@@ -1,4 +1,9 @@
-// Quantised batch normalisation ("BatchNorm*_fixed", utils_class.py:37-93) as native kernels.
+// The layers between SC convolutions as native kernels: quantised batch normalisation (below),
+// 2x2 average pooling + hardtanh, the fixed-point rounding of activations and weights
+// (utils_functional.py:33-39) and the hand-off from bit counts to the layer's float value
+// (further down, each with its own note).
+//
+// Quantised batch normalisation ("BatchNorm*_fixed", utils_class.py:37-93).
 //
 // The reference computes it with F.batch_norm (for the autograd graph), separate mean / var
 // reductions, a dozen small element-wise ops for the 7-bit folded scale and shift

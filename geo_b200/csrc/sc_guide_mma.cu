@@ -12,6 +12,11 @@
 // Tensor-core accumulation rounds toward zero; to keep that bias out of long sums, the MMA
 // accumulators are flushed into ordinary fp32 registers (round-to-nearest adds) every few steps.
 //
+// Kernels: preparation (NHWC bf16 activations, weights per group), mma_forward_kernel
+// (D = gout * exp(-y) as three bf16 terms), mma_wgrad_kernel + mma_wgrad_reduce_kernel, mma_dgrad_kernel,
+// and mma_fused_wgrad_kernel, which does forward and weight gradient in one pass without storing D
+// when no activation gradient is wanted and the groups are short (a network's first layer).
+//
 // Layouts: activations NHWC bf16 [B][Hp][Wp][Cp] (Cp = c_in rounded up to 8, zero filled), so that
 // the members of a filter tap are 16-byte chunks; weights [group][2*c_out_padded][Kp] with the
 // member index k' = tap * Cp + c contiguous.  Only the modes whose groups are whole filter taps
@@ -30,6 +35,10 @@ namespace {
 __device__ __forceinline__ void cp16z(uint32_t dst, const void *src, bool valid) {
     const int n = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp4z(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(n));
 }
 __device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -117,24 +126,18 @@ constexpr int MK = 32;        // members per stage (two k16 steps)
 constexpr int MSTAGE = 4;
 constexpr int MFLUSH = 8;     // k16 steps between flushes of the MMA accumulators
 
-// Splits v into three bf16 terms whose sum reproduces v to 24 bits.
-__device__ __forceinline__ void split3(float v, __nv_bfloat16 &h0, __nv_bfloat16 &h1, __nv_bfloat16 &h2) {
-    h0 = __float2bfloat16_rn(v);
-    const float r1 = v - __bfloat162float(h0);
-    h1 = __float2bfloat16_rn(r1);
-    h2 = __float2bfloat16_rn(r1 - __bfloat162float(h1));
-}
-
 // Output: Dh[plane][g][m][n2] bf16, plane = term of the 3-way split of D = gout * exp(-y).
 // MI = m16 tiles per warp: 2 (4 warps) or 1 (8 warps, half the accumulators per thread).
 template <int MI>
 __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const __nv_bfloat16 *__restrict__ apad,
                                                                const __nv_bfloat16 *__restrict__ wb,
                                                                const float *__restrict__ gout,
-                                                               __nv_bfloat16 *__restrict__ Dh, const int *inexact) {
+                                                               __nv_bfloat16 *__restrict__ Dh, int vec_ok,
+                                                               const int *inexact) {
     if (*inexact) return;   // the FFMA kernels handle inputs that bf16 cannot hold
     constexpr int NTH = 256 / MI, AROWS = 512 / NTH, BROWS = 256 / NTH, RSTEP = NTH / 4;
     constexpr int A_BYTES = 128 * 64, B_BYTES = 64 * 64, ST_BYTES = A_BYTES + B_BYTES;
+    constexpr int GS = 132;   // floats per staged gout row (128 positions + 4: the epilogue's reads hit 32 banks)
     extern __shared__ __align__(128) unsigned char msm[];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int m0 = blockIdx.x * 128, n0 = blockIdx.y * 64, g = blockIdx.z;
@@ -180,6 +183,31 @@ __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const 
         }
         cpa_commit();
     };
+    // gout of the tile, [column][position], rides in the first cp.async group and is read by the epilogue
+    const uint32_t g_s = sbase + MSTAGE * ST_BYTES;
+    const float *g_p = (const float *)(msm + MSTAGE * ST_BYTES);
+    if (vec_ok) {   // 16-byte copies of 4 positions (HoWo % 4 == 0, so they stay inside one image)
+        const int m4 = m0 + (t & 31) * 4;
+        const bool mv = m4 < d.M;
+        const int mm = mv ? m4 : 0;
+        const float *src = gout + (size_t)(mm / d.HoWo) * d.O * d.HoWo + mm % d.HoWo;
+#pragma unroll
+        for (int j = 0; j < 64 * 32 / NTH; j++) {
+            const int col = (t >> 5) + (NTH / 32) * j;
+            const int o = (n0 + col) % d.Opad;
+            const bool v = mv && o < d.O;
+            cp16z(g_s + (uint32_t)(col * GS + (t & 31) * 4) * 4, src + (size_t)(v ? o : 0) * d.HoWo, v);
+        }
+    } else {
+        for (int i = t; i < 64 * 128; i += NTH) {
+            const int col = i >> 7, m = m0 + (i & 127);
+            const int o = (n0 + col) % d.Opad;
+            const bool v = m < d.M && o < d.O;
+            const int mm = v ? m : 0;
+            cp4z(g_s + (uint32_t)(col * GS + (i & 127)) * 4,
+                 gout + ((size_t)(mm / d.HoWo) * d.O + (v ? o : 0)) * d.HoWo + mm % d.HoWo, v);
+        }
+    }
 #pragma unroll
     for (int s = 0; s < MSTAGE - 1; s++) issue();
 
@@ -237,28 +265,27 @@ __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const 
     for (int mi = 0; mi < MI; mi++)
 #pragma unroll
         for (int hr = 0; hr < 2; hr++) {
-            const int m = m0 + warp * (16 * MI) + mi * 16 + (lane >> 2) + hr * 8;
+            const int mrow = warp * (16 * MI) + mi * 16 + (lane >> 2) + hr * 8;
+            const int m = m0 + mrow;
             if (m >= d.M) continue;
-            const int b = m / d.HoWo, rem = m % d.HoWo;
             const size_t plane = (size_t)d.G * d.M * d.N2;
-            __nv_bfloat16 *row = Dh + ((size_t)g * d.M + m) * d.N2;
+            __nv_bfloat16 *row = Dh + ((size_t)g * d.M + m) * d.N2 + n0;
 #pragma unroll
             for (int ni = 0; ni < 8; ni++) {
-                const int n2 = n0 + ni * 8 + (lane & 3) * 2;
-                __nv_bfloat162 p0, p1, p2;
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int o = (n2 + e) % d.Opad;
-                    const float go = o < d.O ? __ldg(gout + ((size_t)b * d.O + o) * d.HoWo + rem) : 0.0f;
-                    const float v = go * expf(-sum[mi][ni][hr * 2 + e]);
-                    __nv_bfloat16 h0, h1, h2;
-                    split3(v, h0, h1, h2);
-                    if (e == 0) { p0.x = h0; p1.x = h1; p2.x = h2; }
-                    else { p0.y = h0; p1.y = h1; p2.y = h2; }
-                }
-                *(__nv_bfloat162 *)(row + n2) = p0;
-                *(__nv_bfloat162 *)(row + plane + n2) = p1;
-                *(__nv_bfloat162 *)(row + 2 * plane + n2) = p2;
+                const int col = ni * 8 + (lane & 3) * 2;
+                const float v0 = g_p[col * GS + mrow] * expf(-sum[mi][ni][hr * 2 + 0]);
+                const float v1 = g_p[(col + 1) * GS + mrow] * expf(-sum[mi][ni][hr * 2 + 1]);
+                // three-term bf16 split of both values at once (cvt.rn.bf16x2.f32)
+                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                const uint32_t p0 = *(uint32_t *)&h;
+                const float r0 = v0 - __uint_as_float(p0 << 16), r1 = v1 - __uint_as_float(p0 & 0xffff0000u);
+                h = __floats2bfloat162_rn(r0, r1);
+                const uint32_t p1 = *(uint32_t *)&h;
+                const float s0 = r0 - __uint_as_float(p1 << 16), s1 = r1 - __uint_as_float(p1 & 0xffff0000u);
+                h = __floats2bfloat162_rn(s0, s1);
+                *(uint32_t *)(row + col) = p0;
+                *(uint32_t *)(row + plane + col) = p1;
+                *(__nv_bfloat162 *)(row + 2 * plane + col) = h;
             }
         }
 }
@@ -469,11 +496,6 @@ void launch_wgrad_reduce(const MmaDims &d, int S, const float *partial, const fl
 // CTA: 8 warps on tiles of 128 positions x 64 columns; warp = 16 columns (warp & 3) x 64 positions
 // (warp >> 2); a CTA walks a contiguous range of position tiles and writes two slices of partial sums.
 constexpr int GSTRIDE = 136;   // floats per staged gout row: 128 positions + 8, so that 8 rows x 32 bytes tile the banks
-
-__device__ __forceinline__ void cp4z(uint32_t dst, const void *src, bool valid) {
-    const int n = valid ? 4 : 0;
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(n));
-}
 
 template <int KS>
 __device__ __forceinline__ uint32_t swz_rows(int row, int chunk) {
@@ -974,12 +996,13 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         return GEO_SC_OK;
     }
     {
-        constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64);
+        constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64) + 64 * 132 * 4;
         static bool done[64] = {};
         int rc = opt_in_smem(mma_forward_kernel<1>, smem, done);
         if (rc) return rc;
+        const int vec_ok = d.HoWo % 4 == 0 && ((uintptr_t)gout & 15) == 0;
         dim3 grid((d.M + 127) / 128, d.N2 / 64, d.G);
-        mma_forward_kernel<1><<<grid, 256, smem, s>>>(d, apad, wb, gout, Dh, flag);
+        mma_forward_kernel<1><<<grid, 256, smem, s>>>(d, apad, wb, gout, Dh, vec_ok, flag);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
     if (grad_weight) {
