@@ -67,6 +67,8 @@ def lib():
     L.geo_sc_bn_fixed_backward.argtypes = [i32, i32, i32, i32] + [vp] * 9 + [sz, vp]
     L.geo_sc_quantize.argtypes = [vp, vp, sz, i32, vp]
     L.geo_sc_counts_to_float.argtypes = [vp, vp, sz, i32, vp]
+    L.geo_sc_bn_pool_act_forward.argtypes = [i32, i32, i32, i32, i32, f32, f32] + [vp] * 12 + [sz, vp]
+    L.geo_sc_bn_pool_act_backward.argtypes = [i32, i32, i32, i32, i32] + [vp] * 11 + [sz, vp]
     L.geo_sc_pool_act_forward.argtypes = [i32, i32, i32, vp, vp, vp]
     L.geo_sc_pool_act_backward.argtypes = [i32, i32, i32, vp, vp, vp, vp]
     L.geo_sc_guide_backward_bytes.argtypes = [dp, szp]
@@ -76,7 +78,7 @@ def lib():
     for n in ("geo_sc_conv2d_forward", "geo_sc_linear_forward", "geo_sc_prepare_weights",
               "geo_sc_generate_act_streams", "geo_sc_accumulate", "geo_sc_group_geometry", "geo_sc_host_stream",
               "geo_sc_measure_lop3_peak", "geo_sc_guide_backward_bytes", "geo_sc_guide_backward",
-              "geo_sc_guide_backward_quantized", "geo_sc_quantize", "geo_sc_counts_to_float",
+              "geo_sc_guide_backward_quantized", "geo_sc_quantize", "geo_sc_counts_to_float", "geo_sc_bn_pool_act_forward", "geo_sc_bn_pool_act_backward",
               "geo_sc_bn_fixed_scratch_bytes",
               "geo_sc_bn_fixed_forward", "geo_sc_bn_fixed_backward", "geo_sc_pool_act_forward",
               "geo_sc_pool_act_backward"):

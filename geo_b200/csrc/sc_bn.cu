@@ -263,6 +263,109 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnDims d, int 
     }
 }
 
+// ---- batch norm + 2x2 average pool + hardtanh(0, 1) in one pass per direction -----------------------
+// out = clamp(mean over the 2x2 window of (x * w_q + b_q), 0, 1).  A thread owns two horizontally
+// adjacent windows = one float4 of each of the two input rows (even H, W % 4 == 0).  The backward pass
+// recomputes the pooled value from x to decide whether the hardtanh passes the gradient, spreads it
+// over the window (factor 1/4) and applies the batch-norm gradient to it -- the composition of the two
+// separate backward passes without ever storing the normalised tensor or its gradient.
+// Window rows: r = (b * C + c) * (H/2) + oy, input rows 2r and 2r + 1.
+struct PoolWin {
+    float4 t, b;       // the two input rows
+    float v0, v1;      // pooled values before the clamp
+};
+__device__ __forceinline__ PoolWin load_windows(const float *__restrict__ x, unsigned r, unsigned j, unsigned W, float w,
+                                                float bq) {
+    PoolWin p;
+    p.t = __ldg((const float4 *)(x + (size_t)(2 * r) * W) + j);
+    p.b = __ldg((const float4 *)(x + (size_t)(2 * r + 1) * W) + j);
+    // same expressions as bn_apply_kernel and pool_act_fwd_kernel, so the value equals their composition
+    p.v0 = ((p.t.x * w + bq) + (p.t.y * w + bq) + (p.b.x * w + bq) + (p.b.y * w + bq)) / 4.0f;
+    p.v1 = ((p.t.z * w + bq) + (p.t.w * w + bq) + (p.b.z * w + bq) + (p.b.w * w + bq)) / 4.0f;
+    return p;
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_pool_apply_kernel(unsigned rows, unsigned W, unsigned Ho, unsigned C,
+                                                                   const float *__restrict__ x,
+                                                                   const float *__restrict__ wq,
+                                                                   const float *__restrict__ bq, float *__restrict__ out) {
+    const unsigned q = W >> 2, total = rows * q;
+    for (unsigned i = blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += gridDim.x * BN_THREADS) {
+        const unsigned r = i / q, j = i % q, c = (r / Ho) % C;
+        const PoolWin p = load_windows(x, r, j, W, wq[c], bq[c]);
+        ((float2 *)(out + (size_t)r * (W >> 1)))[j] = make_float2(fminf(fmaxf(p.v0, 0.0f), 1.0f), fminf(fmaxf(p.v1, 0.0f), 1.0f));
+    }
+}
+
+// partial sums of gy and gy * xhat, gy = gradient reaching the batch-norm output
+__global__ void __launch_bounds__(BN_THREADS) bn_pool_bwd_reduce_kernel(BnDims d, unsigned W, unsigned Ho,
+                                                                        const float *__restrict__ x,
+                                                                        const float *__restrict__ g,
+                                                                        const float *__restrict__ mean,
+                                                                        const float *__restrict__ invstd,
+                                                                        const float *__restrict__ wq,
+                                                                        const float *__restrict__ bq,
+                                                                        float *__restrict__ partial) {
+    __shared__ float red[32];
+    const int c = blockIdx.x, s = blockIdx.y;
+    const int b0 = (int)((long long)d.B * s / d.S), b1 = (int)((long long)d.B * (s + 1) / d.S);
+    const float mu = mean[c], is = invstd[c], w = wq[c], bqc = bq[c];
+    const unsigned q = W >> 2, per_img = Ho * q, n = (unsigned)(b1 - b0) * per_img;
+    float sg = 0.f, sgx = 0.f;
+    for (unsigned i = threadIdx.x; i < n; i += BN_THREADS) {
+        const unsigned b = b0 + i / per_img, rem = i % per_img;
+        const unsigned r = (b * d.C + c) * Ho + rem / q, j = rem % q;
+        const PoolWin p = load_windows(x, r, j, W, w, bqc);
+        const float2 gv = __ldg((const float2 *)(g + (size_t)r * (W >> 1)) + j);
+        const float g0 = p.v0 > 0.0f && p.v0 < 1.0f ? gv.x * 0.25f : 0.0f;
+        const float g1 = p.v1 > 0.0f && p.v1 < 1.0f ? gv.y * 0.25f : 0.0f;
+        sg += 4.0f * g0 + 4.0f * g1;
+        sgx = fmaf(g0, ((p.t.x - mu) + (p.t.y - mu) + (p.b.x - mu) + (p.b.y - mu)) * is, sgx);
+        sgx = fmaf(g1, ((p.t.z - mu) + (p.t.w - mu) + (p.b.z - mu) + (p.b.w - mu)) * is, sgx);
+    }
+    const float t0 = block_sum(sg, red);
+    const float t1 = block_sum(sgx, red);
+    if (threadIdx.x == 0) {
+        partial[(c * d.S + s) * 2 + 0] = t0;
+        partial[(c * d.S + s) * 2 + 1] = t1;
+    }
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_pool_bwd_apply_kernel(BnDims d, unsigned rows, unsigned W, unsigned Ho,
+                                                                       int training, const float *__restrict__ x,
+                                                                       const float *__restrict__ g,
+                                                                       const float *__restrict__ mean,
+                                                                       const float *__restrict__ invstd,
+                                                                       const float *__restrict__ weight,
+                                                                       const float *__restrict__ sums,
+                                                                       const float *__restrict__ wq,
+                                                                       const float *__restrict__ bq,
+                                                                       float *__restrict__ gx) {
+    const float inv_n = 1.0f / ((float)d.B * (float)d.HW);
+    const unsigned q = W >> 2, total = rows * q;
+    for (unsigned i = blockIdx.x * BN_THREADS + threadIdx.x; i < total; i += gridDim.x * BN_THREADS) {
+        const unsigned r = i / q, j = i % q, c = (r / Ho) % (unsigned)d.C;
+        const PoolWin p = load_windows(x, r, j, W, wq[c], bq[c]);
+        const float2 gv = __ldg((const float2 *)(g + (size_t)r * (W >> 1)) + j);
+        const float g0 = p.v0 > 0.0f && p.v0 < 1.0f ? gv.x * 0.25f : 0.0f;
+        const float g1 = p.v1 > 0.0f && p.v1 < 1.0f ? gv.y * 0.25f : 0.0f;
+        const float is = invstd[c], k = (weight ? weight[c] : 1.0f) * is, mu = mean[c];
+        const float a = training ? sums[c * 2] * inv_n : 0.f, bb = training ? sums[c * 2 + 1] * inv_n : 0.f;
+        float4 o0, o1;
+        if (training) {
+            o0 = make_float4(k * (g0 - a - (p.t.x - mu) * is * bb), k * (g0 - a - (p.t.y - mu) * is * bb),
+                             k * (g1 - a - (p.t.z - mu) * is * bb), k * (g1 - a - (p.t.w - mu) * is * bb));
+            o1 = make_float4(k * (g0 - a - (p.b.x - mu) * is * bb), k * (g0 - a - (p.b.y - mu) * is * bb),
+                             k * (g1 - a - (p.b.z - mu) * is * bb), k * (g1 - a - (p.b.w - mu) * is * bb));
+        } else {
+            o0 = make_float4(k * g0, k * g0, k * g1, k * g1);
+            o1 = o0;
+        }
+        ((float4 *)(gx + (size_t)(2 * r) * W))[j] = o0;
+        ((float4 *)(gx + (size_t)(2 * r + 1) * W))[j] = o1;
+    }
+}
+
 int bn_slices(int B, int C) {
     int S = (148 * 4 + C - 1) / C;
     if (S > B) S = B;
@@ -346,6 +449,68 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
     else
         bn_bwd_apply_kernel<false><<<bn_grid((long long)batch * channels * spatial), BN_THREADS, 0, s>>>(
             d, training, x, grad_out, save_mean, save_invstd, weight, sums, grad_x);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+
+static int bn_pool_check(int batch, int channels, int height, int width, const void *a, const void *b, const void *c) {
+    if (batch < 1 || channels < 1 || height < 2 || width < 4 || height % 2 || width % 4)
+        return fail(GEO_SC_ERR_SHAPE, "the fused form needs an even height and a width that is a multiple of 4 (got %dx%d)", height, width);
+    if ((long long)batch * channels * height * width > (1LL << 31) - 1) return fail(GEO_SC_ERR_TOO_LARGE, "tensor too large");
+    if ((((uintptr_t)a | (uintptr_t)c) & 15) || ((uintptr_t)b & 7)) return fail(GEO_SC_ERR_SHAPE, "x / grad_x need 16-byte, pooled tensors 8-byte alignment");
+    return GEO_SC_OK;
+}
+
+int geo_sc_bn_pool_act_forward(int batch, int channels, int height, int width, int training, float eps, float momentum,
+                               const float *x, const float *weight, const float *bias, float *running_mean,
+                               float *running_var, float *out, float *save_mean, float *save_invstd, float *save_wq,
+                               float *save_bq, float *scale_out, void *scratch, size_t scratch_bytes, void *stream) {
+    if (!x || !out || !save_mean || !save_invstd || !save_wq || !save_bq || !scale_out || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
+    if (!training && (!running_mean || !running_var)) return fail(GEO_SC_ERR_NULL, "evaluation mode needs running statistics");
+    int rc = bn_pool_check(batch, channels, height, width, x, out, x);
+    if (rc) return rc;
+    size_t need = 0;
+    geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
+    if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int spatial = height * width;
+    BnDims d = {batch, channels, spatial, bn_slices(batch, channels)};
+    float *partial = (float *)scratch;
+    if (training) {
+        bn_reduce_kernel<0, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
+        bn_mean_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, save_mean);
+        bn_reduce_kernel<1, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
+    }
+    bn_fold_kernel<<<1, BN_THREADS, 0, s>>>(d, training, eps, momentum, partial, save_mean, save_invstd, weight, bias,
+                                            running_mean, running_var, save_wq, save_bq, scale_out);
+    const unsigned rows = (unsigned)batch * channels * (height / 2);
+    bn_pool_apply_kernel<<<bn_grid((long long)rows * (width / 4)), BN_THREADS, 0, s>>>(rows, (unsigned)width, (unsigned)(height / 2),
+                                                                                  (unsigned)channels, x, save_wq, save_bq, out);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int geo_sc_bn_pool_act_backward(int batch, int channels, int height, int width, int training, const float *x,
+                                const float *grad_out, const float *weight, const float *save_mean,
+                                const float *save_invstd, const float *save_wq, const float *save_bq, float *grad_x,
+                                float *grad_weight, float *grad_bias, void *scratch, size_t scratch_bytes, void *stream) {
+    if (!x || !grad_out || !save_mean || !save_invstd || !save_wq || !save_bq || !grad_x || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
+    int rc = bn_pool_check(batch, channels, height, width, x, grad_out, grad_x);
+    if (rc) return rc;
+    size_t need = 0;
+    geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
+    if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+    cudaStream_t s = (cudaStream_t)stream;
+    BnDims d = {batch, channels, height * width, bn_slices(batch, channels)};
+    float *partial = (float *)scratch;
+    float *sums = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
+    const unsigned W = (unsigned)width, Ho = (unsigned)(height / 2);
+    bn_pool_bwd_reduce_kernel<<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, W, Ho, x, grad_out, save_mean, save_invstd, save_wq, save_bq, partial);
+    bn_bwd_final_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, sums, grad_weight, grad_bias);
+    const unsigned rows = (unsigned)batch * channels * Ho;
+    bn_pool_bwd_apply_kernel<<<bn_grid((long long)rows * (width / 4)), BN_THREADS, 0, s>>>(d, rows, W, Ho, training, x, grad_out, save_mean,
+                                                                                      save_invstd, weight, sums, save_wq, save_bq, grad_x);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

@@ -53,7 +53,9 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
     ``share`` True, ``generator`` None, ``forward`` 'full_or', ``legacy`` False, ``load_unit`` 8,
     ``load_wait_w`` 1, ``load_wait_a`` 1, ``z_unit`` 1024.  One extension over the reference:
     ``quantized`` (default False) promises that both operands went through :func:`quantize` with
-    ``prec`` <= 8, which lets the backward pass run on the tensor-core kernels alone.
+    ``prec`` <= 8, which lets the backward pass run on the tensor-core kernels alone; ``weight_cache``
+    (default None) is a dict in which the packed weight streams are kept between calls -- the caller
+    empties it when the weights change.
 
     ``padding`` follows the reference's convention ``F.pad(x, (p[0], p[0], p[1], p[1]))``: the
     last dimension is padded by ``padding[0]``, dimension 2 by ``padding[1]``
@@ -92,7 +94,8 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
     return sc_conv2d_with_guide(activation, weight, int(bit_length), forward, pad_h=p1, pad_w=p0,
                                 z_unit=int(z_unit), total_width=prec_default, load_width=int(load_unit),
                                 load_wait_w=int(load_wait_w), load_wait_a=int(load_wait_a),
-                                quantized=bool(kwargs.get("quantized", False)))
+                                quantized=bool(kwargs.get("quantized", False)),
+                                weight_cache=kwargs.get("weight_cache", None))
 
 
 def linear_generic(activation, weight, **kwargs):

@@ -20,10 +20,18 @@ from . import ops
 class _SCConv2dGuide(torch.autograd.Function):
     @staticmethod
     def forward(ctx, activation, weight, bit_length, mode, pad_h, pad_w, z_unit, total_width, load_width,
-                load_wait_w, load_wait_a, quantized=False):
+                load_wait_w, load_wait_a, quantized=False, weight_cache=None):
         kw = dict(z_unit=z_unit, total_width=total_width, load_width=load_width, load_wait_w=load_wait_w,
                   load_wait_a=load_wait_a)
-        counts = ops.sc_conv2d_staged(activation, weight, bit_length, mode, (pad_h, pad_w), **kw)
+        wprep = None
+        if weight_cache is not None:
+            # weight streams depend on the weights and on everything in the descriptor but the batch
+            key = (tuple(activation.shape[1:]), tuple(weight.shape), bit_length, mode, pad_h, pad_w) + tuple(kw.values())
+            wprep = weight_cache.get(key)
+            if wprep is None:
+                wprep = ops.prepare_weights(weight, ops.desc_for(activation, weight, bit_length, mode, (pad_h, pad_w), **kw))
+                weight_cache[key] = wprep
+        counts = ops.sc_conv2d_staged(activation, weight, bit_length, mode, (pad_h, pad_w), wprep=wprep, **kw)
         need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if need_a or need_w:
             ctx.quantized = bool(quantized)
@@ -40,12 +48,14 @@ class _SCConv2dGuide(torch.autograd.Function):
             ga = ga.to(activation.dtype)
         if gw is not None:
             gw = gw.to(weight.dtype)
-        return (ga, gw) + (None,) * 10
+        return (ga, gw) + (None,) * 11
 
 
 def sc_conv2d_with_guide(activation, weight, bit_length, mode, pad_h=0, pad_w=0, z_unit=1024, total_width=7,
-                         load_width=8, load_wait_w=1, load_wait_a=1, quantized=False):
+                         load_width=8, load_wait_w=1, load_wait_a=1, quantized=False, weight_cache=None):
     """SC conv2d value with the guide's gradient; ``pad_h`` / ``pad_w`` pad dimensions 2 / 3.
-    ``quantized``: the caller's promise of :func:`geo_b200.ops.guide_backward`."""
+    ``quantized``: the caller's promise of :func:`geo_b200.ops.guide_backward`.  ``weight_cache``: a dict
+    owned by the caller in which the packed weight streams are kept between calls; the caller empties
+    it whenever the weights change."""
     return _SCConv2dGuide.apply(activation, weight, bit_length, mode, pad_h, pad_w, z_unit, total_width, load_width,
-                                load_wait_w, load_wait_a, quantized)
+                                load_wait_w, load_wait_a, quantized, weight_cache)

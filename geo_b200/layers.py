@@ -18,15 +18,29 @@ class Conv2d_Add_Partial(nn.Conv2d):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         self.register_buffer("weight_org", self.weight.data.clone())
+        # evaluation mode: quantised weights and their packed streams are kept while weight_org is unchanged
+        self._stream_cache = {}
+        self._stream_cache_tag = None
 
     def forward(self, input, prec=7, err=7, forward="1d_bin", generator="lfsr", z_unit=8, legacy=False, load_unit=8,
                 load_wait_w=2, load_wait_a=2):
         input.data = sc_f.quantize(input.data, prec=prec)
-        self.weight.data = sc_f.quantize(self.weight_org, prec=prec)
+        cache = None
+        if self.training:
+            self._stream_cache_tag = None
+            self.weight.data = sc_f.quantize(self.weight_org, prec=prec)
+        else:
+            tag = (self.weight_org.data_ptr(), self.weight_org._version, prec)
+            if tag != self._stream_cache_tag:
+                self._stream_cache.clear()
+                self._stream_cache_tag = tag
+                self.weight.data = sc_f.quantize(self.weight_org, prec=prec)
+            cache = self._stream_cache
         return sc_f.conv2d_generic(input, self.weight, bit_length=2 ** err, padding=self.padding, stride=self.stride,
                                    forward=forward, generator=generator, legacy=legacy, z_unit=z_unit,
                                    load_unit=load_unit, load_wait_w=load_wait_w, load_wait_a=load_wait_a,
-                                   quantized=prec <= 8)  # k / 2^prec with |k| < 2^8 is exact in bf16
+                                   quantized=prec <= 8,  # k / 2^prec with |k| < 2^8 is exact in bf16
+                                   weight_cache=cache)
 
 
 class _BatchNormFixed(torch.autograd.Function):
@@ -76,6 +90,39 @@ class BatchNorm1d_fixed(nn.BatchNorm1d):
 
     def forward(self, x):
         return _BatchNormFixed.apply(x, self.weight if self.affine else None, self.bias if self.affine else None, self)
+
+
+class _BatchNormPoolHardtanh(torch.autograd.Function):
+    """``hardtanh(avg_pool2d(bn(x), 2), 0, 1)`` with ``bn`` a ``BatchNorm2d_fixed``: value and gradients of the
+    composition, one native pass per direction."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, module):
+        if module.momentum is None:
+            raise NotImplementedError("cumulative moving average (momentum=None) is not provided")
+        out, mean, invstd, scale, wq, bq = ops.bn_pool_act_forward(
+            x, weight.detach() if weight is not None else None, bias.detach() if bias is not None else None,
+            module.running_mean, module.running_var, module.training, module.momentum, module.eps)
+        module.scale = scale.reshape(())
+        ctx.training = module.training
+        ctx.has_affine = weight is not None
+        ctx.save_for_backward(x, weight, mean, invstd, wq, bq)
+        return out.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, mean, invstd, wq, bq = ctx.saved_tensors
+        gx, gw, gb = ops.bn_pool_act_backward(x, grad_out, weight.detach() if weight is not None else None, mean,
+                                              invstd, wq, bq, ctx.training, ctx.has_affine)
+        return gx.to(x.dtype), gw, gb, None
+
+
+def bn_pool_hardtanh(bn, x):
+    """``nn.Hardtanh(0, 1)(nn.AvgPool2d(2)(bn(x)))`` for a ``BatchNorm2d_fixed`` module ``bn`` (network.py:168-184);
+    one pass per direction where the shape allows (even height, width a multiple of 4), else the two layers."""
+    if ops.bn_pool_act_supported(x):
+        return _BatchNormPoolHardtanh.apply(x, bn.weight if bn.affine else None, bn.bias if bn.affine else None, bn)
+    return _PoolHardtanh.apply(bn(x))
 
 
 class _PoolHardtanh(torch.autograd.Function):

@@ -65,11 +65,11 @@ class CONV_tiny_add_partial(nn.Module):
     def forward(self, x_in, target=None):
         x = x_in
         for i, (conv, bn) in enumerate(((self.conv1, self.bn1), (self.conv2, self.bn2), (self.conv3, self.bn3))):
-            x = bn(self._sc(conv, x, i))
+            x = self._sc(conv, x, i)
             if self.relu:
-                x = self.tanh(self.pool(F.relu(x)))
+                x = self.tanh(self.pool(F.relu(bn(x))))
             else:
-                x = self.pool_tanh(x)
+                x = layers.bn_pool_hardtanh(bn, x)   # tanh(pool(bn(x))), one pass where the shape allows
         x = self._sc(self.fc1, x, 3).view(-1, self.num_classes)
         return self.bn4(x)  # BN at the output stabilises training (network.py:188-189)
 
@@ -117,8 +117,8 @@ class VGG11_add_partial(nn.Module):
 
     def forward(self, x, target=None):
         for i, (conv, bn) in enumerate(zip(self.convs, self.bns)):
-            x = bn(self._sc(conv, x, i))
-            x = self.pool_tanh(x) if i in self.POOL_AFTER else self.tanh(x)
+            x = self._sc(conv, x, i)
+            x = layers.bn_pool_hardtanh(bn, x) if i in self.POOL_AFTER else self.tanh(bn(x))
         n = len(self.convs)
         x = self.tanh(self.bnf1(self._sc(self.fc1, x, n)))
         x = self.tanh(self.bnf2(self._sc(self.fc2, x, n + 1)))

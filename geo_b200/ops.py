@@ -249,6 +249,51 @@ def bn_fixed_backward(x, grad_out, weight, mean, invstd, training, need_affine=T
     return gx, gw, gb
 
 
+def bn_pool_act_supported(x):
+    """Whether the one-pass batch norm + 2x2 average pool + hardtanh applies to ``x``."""
+    return x.is_cuda and x.dim() == 4 and x.shape[2] % 2 == 0 and x.shape[3] % 4 == 0 and x.shape[2] >= 2
+
+
+def bn_pool_act_forward(x, weight, bias, running_mean, running_var, training, momentum, eps):
+    """hardtanh(avg_pool2d(bn_fixed(x), 2), 0, 1) -> (out, save_mean, save_invstd, scale, w_q, b_q)."""
+    _require_cuda(x)
+    xc = x.detach().to(torch.float32).contiguous()
+    B, C, H, W = xc.shape
+    dev = xc.device
+    with torch.cuda.device(dev):
+        out = torch.empty((B, C, H // 2, W // 2), dtype=torch.float32, device=dev)
+        stats = torch.empty((4, C), dtype=torch.float32, device=dev)     # mean, invstd, w_q, b_q
+        scale = torch.empty(1, dtype=torch.float32, device=dev)
+        scratch = _bn_scratch(B, C, dev)
+        check(_lib.lib().geo_sc_bn_pool_act_forward(
+            B, C, H, W, int(bool(training)), float(eps), float(momentum), xc.data_ptr(), _ptr(weight), _ptr(bias),
+            _ptr(running_mean), _ptr(running_var), out.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(),
+            stats[2].data_ptr(), stats[3].data_ptr(), scale.data_ptr(), scratch.data_ptr(), scratch.numel(),
+            _stream_ptr(dev)), "geo_sc_bn_pool_act_forward")
+    STATS.launches += 5 if training else 2
+    return out, stats[0], stats[1], scale, stats[2], stats[3]
+
+
+def bn_pool_act_backward(x, grad_out, weight, mean, invstd, wq, bq, training, need_affine=True):
+    """Gradient of :func:`bn_pool_act_forward` -> (grad_x, grad_weight, grad_bias)."""
+    _require_cuda(x, grad_out)
+    xc = x.detach().to(torch.float32).contiguous()
+    go = grad_out.detach().to(torch.float32).contiguous()
+    B, C, H, W = xc.shape
+    dev = xc.device
+    with torch.cuda.device(dev):
+        gx = torch.empty_like(xc)
+        gw = torch.empty(C, dtype=torch.float32, device=dev) if need_affine else None
+        gb = torch.empty(C, dtype=torch.float32, device=dev) if need_affine else None
+        scratch = _bn_scratch(B, C, dev)
+        check(_lib.lib().geo_sc_bn_pool_act_backward(
+            B, C, H, W, int(bool(training)), xc.data_ptr(), go.data_ptr(), _ptr(weight), mean.data_ptr(),
+            invstd.data_ptr(), wq.data_ptr(), bq.data_ptr(), gx.data_ptr(), _ptr(gw), _ptr(gb), scratch.data_ptr(),
+            scratch.numel(), _stream_ptr(dev)), "geo_sc_bn_pool_act_backward")
+    STATS.launches += 3
+    return gx, gw, gb
+
+
 def quantize(x, prec):
     """clamp(round(x * 2^prec), +-(2^prec - 1)) / 2^prec of a CUDA tensor as one kernel."""
     _require_cuda(x)

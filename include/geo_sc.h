@@ -205,6 +205,28 @@ int geo_sc_bn_fixed_backward(int batch, int channels, int spatial, int training,
                              const float *save_invstd_device, float *grad_x_device, float *grad_weight_device,
                              float *grad_bias_device, void *scratch_device, size_t scratch_bytes, void *stream);
 
+/* ---- batch norm + 2x2 average pool + hardtanh(0, 1) as one pass per direction ---------------------
+ * Replaces the sequence bn -> nn.AvgPool2d(2) -> nn.Hardtanh(0, 1) between the reference's SC layers
+ * (network.py:168-184 over utils_class.py:37-65).  x [batch][channels][height][width], out and
+ * grad_out [batch][channels][height/2][width/2]; even height, width a multiple of 4, x / grad_x
+ * 16-byte and the pooled tensors 8-byte aligned (GEO_SC_ERR_SHAPE otherwise: use the separate entry
+ * points).  Value and gradients equal the composition of geo_sc_bn_fixed_* and geo_sc_pool_act_*;
+ * the normalised tensor and its gradient are never stored.  save_wq / save_bq [channels] receive the
+ * folded, quantised scale and shift that the backward pass needs to recompute the pooled value.
+ * scratch as for geo_sc_bn_fixed_forward. */
+int geo_sc_bn_pool_act_forward(int batch, int channels, int height, int width, int training, float eps, float momentum,
+                               const float *x_device, const float *weight_device, const float *bias_device,
+                               float *running_mean_device, float *running_var_device, float *out_device,
+                               float *save_mean_device, float *save_invstd_device, float *save_wq_device,
+                               float *save_bq_device, float *scale_out_device, void *scratch_device,
+                               size_t scratch_bytes, void *stream);
+int geo_sc_bn_pool_act_backward(int batch, int channels, int height, int width, int training, const float *x_device,
+                                const float *grad_out_device, const float *weight_device,
+                                const float *save_mean_device, const float *save_invstd_device,
+                                const float *save_wq_device, const float *save_bq_device, float *grad_x_device,
+                                float *grad_weight_device, float *grad_bias_device, void *scratch_device,
+                                size_t scratch_bytes, void *stream);
+
 /* ---- fixed-point rounding of activations and weights ----------------------------------------------
  * Replaces quantize (utils_functional.py:33-39), which the reference evaluates as four element-wise
  * PyTorch ops: y = clamp(round_half_even(x * 2^prec), -(2^prec - 1), 2^prec - 1) / 2^prec, one kernel.

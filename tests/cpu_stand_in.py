@@ -65,6 +65,7 @@ def install(monkeypatch):
         return gx
 
     monkeypatch.setattr(ops, "counts_to_float", lambda counts, bit_length: counts.to(torch.float32) / bit_length)
+    monkeypatch.setattr(ops, "bn_pool_act_supported", lambda x: False)   # CPU: batch norm and pooling as two layers
     monkeypatch.setattr(ops, "pool_act_forward", pool_act_forward)
     monkeypatch.setattr(ops, "pool_act_backward", pool_act_backward)
     monkeypatch.setattr(ops, "bn_fixed_forward", bn_fixed_forward)

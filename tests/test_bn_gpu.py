@@ -117,3 +117,47 @@ def test_counts_to_float_is_exact(cuda_device):
         c = torch.randint(-5 * 256, 5 * 256, shape, generator=g, dtype=torch.int32).to(cuda_device)
         for L in (8, 128, 256):
             assert torch.equal(ops.counts_to_float(c, L), c.to(torch.float32) / L)
+
+
+@pytest.mark.parametrize("shape", [(16, 32, 8, 8), (256, 32, 32, 32), (3, 5, 6, 12), (8, 64, 2, 4)])
+@pytest.mark.parametrize("training", [True, False])
+def test_fused_bn_pool_hardtanh_equals_the_two_layers(cuda_device, shape, training):
+    """layers.bn_pool_hardtanh against AvgPool2Hardtanh()(BatchNorm2d_fixed(x)): same value (bit for bit),
+    same running statistics and scale buffer, gradients within fp32 summation-order tolerance."""
+    from geo_b200 import layers
+
+    g = torch.Generator().manual_seed(sum(shape))
+    C = shape[1]
+    x0 = (torch.rand(*shape, generator=g) * 1.6 - 0.3).to(cuda_device)
+    go = torch.randn(shape[0], C, shape[2] // 2, shape[3] // 2, generator=g).to(cuda_device)
+    results = []
+    for fused in (False, True):
+        torch.manual_seed(1)
+        bn = layers.BatchNorm2d_fixed(C).to(cuda_device)
+        with torch.no_grad():
+            bn.weight.fill_(1.3)
+            bn.bias.fill_(0.2)
+            bn.running_mean.fill_(0.4)
+            bn.running_var.fill_(0.3)
+        bn.train(training)
+        x = x0.clone().requires_grad_(True)
+        y = layers.bn_pool_hardtanh(bn, x) if fused else layers.AvgPool2Hardtanh()(bn(x))
+        y.backward(go)
+        results.append((y.detach(), x.grad, bn.weight.grad, bn.bias.grad, bn.running_mean.clone(), bn.running_var.clone(),
+                        bn.scale.clone()))
+    a, b = results
+    assert torch.equal(a[0], b[0])
+    assert torch.equal(a[4], b[4]) and torch.equal(a[5], b[5]) and torch.equal(a[6], b[6])
+    for i, name in ((1, "grad_x"), (2, "grad_weight"), (3, "grad_bias")):
+        scale = a[i].abs().max().item() + 1e-30
+        assert (a[i] - b[i]).abs().max().item() <= 2e-5 * scale, name
+
+
+def test_fused_bn_pool_hardtanh_falls_back_for_other_shapes(cuda_device):
+    from geo_b200 import layers, ops
+
+    x = torch.rand(2, 3, 7, 9).to(cuda_device)
+    assert not ops.bn_pool_act_supported(x)
+    bn = layers.BatchNorm2d_fixed(3).to(cuda_device)
+    y = layers.bn_pool_hardtanh(bn, x)
+    assert y.shape == (2, 3, 3, 4)

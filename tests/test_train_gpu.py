@@ -47,6 +47,42 @@ def test_graph_replay_equals_eager_steps(cuda_device):
         assert torch.equal(a, b) and torch.equal(a, c)
 
 
+def test_evaluation_keeps_weight_streams_until_the_weights_change(cuda_device):
+    """In evaluation mode a layer quantises its weights and packs their streams once; the result must
+    equal the uncached computation, fewer kernels are launched from the second call on, and an
+    in-place change of ``weight_org`` (optimiser step, checkpoint load) drops the cache."""
+    from geo_b200 import ops
+
+    net = _model(cuda_device).eval()
+    g = torch.Generator().manual_seed(9)
+    x = torch.rand(8, 3, 32, 32, generator=g).to(cuda_device)
+    with torch.no_grad():
+        ops.STATS.reset()
+        y1 = net(x.clone())
+        first = ops.STATS.launches
+        ops.STATS.reset()
+        y2 = net(x.clone())
+        second = ops.STATS.launches
+        assert torch.equal(y1, y2)
+        assert second < first                       # no weight quantisation, no weight-stream kernels
+        # same weights through the training-mode path (no cache) with frozen statistics
+        net.train()
+        for m in net.modules():
+            if hasattr(m, "running_mean"):
+                m.eval()
+        y3 = net(x.clone())
+        assert torch.equal(y1, y3)
+        net.eval()
+        # an in-place weight change must be seen
+        net.conv2.weight_org.mul_(0.5)
+        y4 = net(x.clone())
+        assert not torch.equal(y1, y4)
+        for c in (net.conv1, net.conv2, net.conv3, net.fc1):
+            c._stream_cache.clear()
+            c._stream_cache_tag = None
+        assert torch.equal(net(x.clone()), y4)
+
+
 def test_two_graph_step_with_packed_gradient_exchange(cuda_device):
     """The data-parallel hook's pack / unpack phases live inside the two graphs and only the
     collective runs between them; with a one-rank process group the result must equal the
