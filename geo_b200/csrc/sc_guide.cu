@@ -47,6 +47,7 @@ __host__ __device__ inline bool decode_member(int mode, int z, int C, int K2, in
     case GEO_SC_MODE_1D: *kx = g; *c = k / K2; *ky = k % K2; break;
     case GEO_SC_MODE_Z: *c = g; *ky = k / K3; *kx = k % K3; break;
     case GEO_SC_MODE_YZ: *kx = g % K3; *c = (g / K3) * z + k / K2; *ky = k % K2; break;
+    case GEO_SC_MODE_2D: *ky = g / K3; *kx = g % K3; *c = k; break;
     default: *c = k / (K2 * K3); *ky = (k / K3) % K2; *kx = k % K3; break;
     }
     return *c < C;
@@ -541,6 +542,7 @@ __global__ void __launch_bounds__(NTHREADS) guide_dgrad_kernel(DgradParams pr) {
             case GEO_SC_MODE_1D: g = kx; break;
             case GEO_SC_MODE_Z: g = j; break;
             case GEO_SC_MODE_YZ: g = j * pr.K3 + kx; break;
+            case GEO_SC_MODE_2D: g = kk; break;
             default: g = 0; break;
             }
             const float *plane = pr.D + (size_t)(g * pr.N2 + n2) * pr.M;

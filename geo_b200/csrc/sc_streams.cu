@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
             sidx = k;
             break;
         }
+        case GEO_SC_MODE_2D: ky = g / gp.K3; kx = g % gp.K3; c = k; sidx = k; break;   // generators indexed by channel
         default: c = k / (gp.K2 * gp.K3); ky = (k / gp.K3) % gp.K2; kx = k % gp.K3; sidx = k; break;
         }
         const bool valid = c < gp.C && k < gp.K;

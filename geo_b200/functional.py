@@ -17,7 +17,7 @@ from .guide import sc_conv2d_with_guide
 
 prec_default = 7  # 8-bit integers, one bit for the sign (utils_functional.py:28)
 
-_ACCELERATED_MODES = ("1d_bin", "z_bin", "yz_bin", "full_or")
+_ACCELERATED_MODES = ("1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin")
 
 
 def quantize(input, prec=8):
@@ -86,8 +86,9 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
         raise ValueError("stride must be 1: the reference's SC kernels ignore the stride argument "
                          "(sc_cuda_kernel.cu:1732-1834), so no other stride has a defined result")
     p0, p1 = _pair(padding)
-    if forward == "full_or":
-        # The reference's full_or kernel takes no loading arguments (sc_cuda.cpp:21-32).
+    if forward in ("full_or", "2d_bin"):
+        # The reference's full_or kernel takes no loading arguments (sc_cuda.cpp:21-32); 2d_bin exists
+        # only in its bit-serial simulation, which has no progressive loading (utils_functional.py:516-609).
         load_unit, load_wait_w, load_wait_a = 8, 1, 1
     elif forward in ("1d_bin", "z_bin"):
         load_wait_a = load_wait_w  # one load_wait for both operands (sc_cuda.cpp:47-63)

@@ -371,6 +371,8 @@ def weight_streams_canonical(buf, desc):
         z = min(desc.z_unit, C)
         zp = (C + z - 1) // z
         v = v.reshape(P, zp, K3, z, K2, O, 2).permute(6, 5, 1, 3, 4, 2, 0).reshape(2, O, zp * z, K2, K3, P)[:, :, :C]
+    elif mode == _lib.MODE_2D:      # g = ky*K3+kx, k = c
+        v = v.reshape(P, K2, K3, C, O, 2).permute(5, 4, 3, 1, 2, 0)
     else:                           # g = 0, k = (c*K2+ky)*K3+kx
         v = v.reshape(P, C, K2, K3, O, 2).permute(5, 4, 1, 2, 3, 0)
     return v.contiguous()

@@ -33,6 +33,8 @@ extern "C" {
 #define GEO_SC_MODE_Z 1       /* OR over (ky,kx), add over c: sc_cuda_kernel.cu:1141-1271                */
 #define GEO_SC_MODE_YZ 2      /* OR over (c mod z,ky), add over (c div z,kx): sc_cuda_kernel.cu:1007-1138 */
 #define GEO_SC_MODE_FULL_OR 3 /* OR over (c,ky,kx): utils_functional.py:554-609 (LFSR, deterministic)     */
+#define GEO_SC_MODE_2D 4      /* OR over c, add over (ky,kx): utils_functional.py:528-541,597-601 (only in
+                                 the reference's bit-serial simulation; weight generators indexed by c)  */
 
 typedef enum geo_sc_status {
     GEO_SC_OK = 0,

@@ -34,6 +34,14 @@ def guide_pos_neg(a_padded, weight, mode, z_unit=1024):
         groups = [(slice(c, c + 1), None) for c in range(C)]
     elif mode == "yz_bin":     # :272-296, z_unit channels x one filter column
         groups = [(slice(c, min(c + z_unit, C)), j) for c in range(0, C, z_unit) for j in range(K3)]
+    elif mode == "2d_bin":     # :212-233, one slice per filter tap
+        K2, Hp = weight.size(2), a.size(2)
+        for i in range(K2):
+            for j in range(K3):
+                a_g = a[:, :, i:Hp - K2 + i + 1, j:Wp - K3 + j + 1]
+                pos.append(_or_approx(a_g, w_pos[:, :, i:i + 1, j:j + 1]))
+                neg.append(_or_approx(a_g, w_neg[:, :, i:i + 1, j:j + 1]))
+        return torch.stack(pos, 0).sum(0), torch.stack(neg, 0).sum(0)
     else:
         raise ValueError(mode)
     for cs, j in groups:

@@ -29,6 +29,7 @@
 #define GEO_MODE_Z 1       /* OR over (ky,kx), binary add over c           */
 #define GEO_MODE_YZ 2      /* OR over (c mod z, ky), binary add over (c div z, kx) */
 #define GEO_MODE_FULL_OR 3 /* OR over (c,ky,kx)                             */
+#define GEO_MODE_2D 4      /* OR over c, binary add over (ky,kx)            */
 
 /* LFSR width for a stream length: 8->3 ... 256->8
  * (torch_c/sc-extension/sc.cpp:313-334, sc_cuda_kernel.cu:113-134). */
@@ -109,12 +110,15 @@ static int act_seed_index(int mode, int z, int c, int y, int x, int H, int W) {
  *   1d_bin : c*K2+ky            (sc_cuda_kernel.cu:146, sc.cpp:363)
  *   z_bin  : ky*K3+kx           (sc_cuda_kernel.cu:322-324)
  *   yz_bin : (c mod z)*K2+ky    (sc_cuda_kernel.cu:231)
- *   full_or: (c*K2+ky)*K3+kx    (utils_functional.py:562-563,570)          */
+ *   full_or: (c*K2+ky)*K3+kx    (utils_functional.py:562-563,570)
+ *   2d_bin : c                  (utils_functional.py:536-541,562: the filter is cut into 1x1 slices
+ *                                before the generators are laid out over its last three dims)  */
 static int w_seed_index(int mode, int z, int c, int ky, int kx, int K2, int K3) {
     switch (mode) {
     case GEO_MODE_1D: return c * K2 + ky;
     case GEO_MODE_Z: return ky * K3 + kx;
     case GEO_MODE_YZ: return (c % z) * K2 + ky;
+    case GEO_MODE_2D: return c;
     default: return (c * K2 + ky) * K3 + kx;
     }
 }
@@ -220,6 +224,17 @@ int geo_oracle_accumulate(const uint32_t *as, const uint32_t *ws, int B, int C, 
                                         }
                                     total += popc32(ap) - popc32(an);
                                 }
+                        } else if (mode == GEO_MODE_2D) {   /* utils_functional.py:597-601 */
+                            for (int ky = 0; ky < K2; ky++)
+                                for (int kx = 0; kx < K3; kx++) {
+                                    uint32_t ap = 0, an = 0;
+                                    for (int c = 0; c < C; c++) {
+                                        uint32_t a = A_AT(c, ky, kx);
+                                        ap |= a & W_AT(wp, c, ky, kx);
+                                        an |= a & W_AT(wn, c, ky, kx);
+                                    }
+                                    total += popc32(ap) - popc32(an);
+                                }
                         } else {
                             uint32_t ap = 0, an = 0;
                             for (int c = 0; c < C; c++)
@@ -245,7 +260,7 @@ int geo_oracle_accumulate(const uint32_t *as, const uint32_t *ws, int B, int C, 
 int geo_oracle_conv2d(const float *act, const float *w, int B, int C, int H, int W, int O, int K2, int K3, int L,
                       int mode, int z_unit, int tw, int lu, int lw_w, int lw_a, int32_t *out) {
     if (!lfsr_bits(L)) return -1;
-    if (mode < 0 || mode > 3) return -3;
+    if (mode < 0 || mode > 4) return -3;
     int P = (L + 31) / 32;
     uint32_t *as = (uint32_t *)malloc((size_t)B * C * H * W * P * sizeof(uint32_t));
     uint32_t *ws = (uint32_t *)malloc((size_t)2 * O * C * K2 * K3 * P * sizeof(uint32_t));

@@ -94,8 +94,26 @@ def main():
     print("wrote", sorted(os.listdir(HERE)))
 
 
-if __name__ == "__main__":
-    main()
+def make_2d_golden():
+    """``ref_legacy_2d_L128.npz``: the reference's bit-serial simulation with forward='2d_bin' (OR over the
+    channels, binary accumulation over the filter taps; utils_functional.py:528-541,597-601) at L=128."""
+    uf = ref_loader.reference_python()
+    torch.manual_seed(4242)
+    out = {}
+    cases = [((2, 3, 8, 8), (4, 3, 3, 3), (1, 1)), ((1, 5, 6, 7), (3, 5, 2, 4), (0, 0)), ((2, 8, 5, 5), (6, 8, 3, 2), (0, 1)),
+             ((3, 2, 4, 4), (5, 2, 1, 1), (0, 0))]
+    for i, (ashape, wshape, pad) in enumerate(cases):
+        a = q7(torch.rand(*ashape))
+        w = q7(torch.rand(*wshape) * 2 - 1)
+        y = uf.conv2d_generic(a.clone(), w.clone(), pad, (1, 1), bit_length=128, forward="2d_bin", generator="lfsr",
+                              legacy=True)
+        out[f"c{i}_a"] = a.numpy()
+        out[f"c{i}_w"] = w.numpy()
+        out[f"c{i}_meta"] = np.array([128, pad[0], pad[1], 4], np.int32)
+        out[f"c{i}_y"] = (y.detach() * 128).round().numpy().astype(np.int32)
+    out["n"] = np.array(len(cases))
+    np.savez_compressed(os.path.join(HERE, "ref_legacy_2d_L128.npz"), **out)
+    print("wrote ref_legacy_2d_L128.npz")
 
 
 def make_training_step_golden():
@@ -162,4 +180,11 @@ def make_training_step_golden():
 
 
 if __name__ == "__main__":
-    make_training_step_golden()
+    # python tests/golden/make_golden.py [all|forward|2d|step]: each part writes only its own fixture files
+    which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which in ("all", "forward"):
+        main()
+    if which in ("all", "2d"):
+        make_2d_golden()
+    if which in ("all", "step"):
+        make_training_step_golden()

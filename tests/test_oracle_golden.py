@@ -39,6 +39,17 @@ def test_oracle_matches_reference_bit_serial_simulation(oracle_lib):
     assert np.array_equal(y, g["lin_y"])
 
 
+def test_oracle_2d_bin_matches_reference_bit_serial_simulation(oracle_lib):
+    """2d_bin (OR over the channels, binary accumulation over the filter taps) exists only in the
+    reference's simulation; the fixture holds its outputs at L=128."""
+    g = np.load(os.path.join(GOLDEN, "ref_legacy_2d_L128.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1, mode = (int(v) for v in g[f"c{i}_meta"])
+        assert mode == 4
+        y = oracle_lib.conv2d(g[f"c{i}_a"], g[f"c{i}_w"], L, "2d_bin", pad_h=p1, pad_w=p0)
+        assert np.array_equal(y, g[f"c{i}_y"]), f"case {i}"
+
+
 @pytest.mark.parametrize("name", ["ref_cuda_modes.npz"])
 def test_oracle_matches_reference_cuda_kernels(oracle_lib, name):
     path = os.path.join(GOLDEN, name)
