@@ -20,7 +20,7 @@
 // Layouts: activations NHWC bf16 [B][Hp][Wp][Cp] (Cp = c_in rounded up to 8, zero filled), so that
 // the members of a filter tap are 16-byte chunks; weights [group][2*c_out_padded][Kp] with the
 // member index k' = tap * Cp + c contiguous.  Only the modes whose groups are whole filter taps
-// over all channels use this path (1d_bin: the taps of one filter column; full_or: all taps).
+// over all channels use this path (1d_bin: the taps of one filter column; 2d_bin: one tap; full_or: all taps).
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -54,6 +54,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Filter coordinates of tap `tap` of group g: 1d_bin groups are filter columns (taps = rows), 2d_bin
+// groups are single taps, full_or has one group with all taps.
+__device__ __forceinline__ void tap_coords(const MmaDims &d, int g, int tap, int *ky, int *kx) {
+    if (d.mode == GEO_SC_MODE_1D) { *ky = tap; *kx = g; }
+    else if (d.mode == GEO_SC_MODE_2D) { *ky = g / d.K3; *kx = g % d.K3; }
+    else { *ky = tap / d.K3; *kx = tap % d.K3; }
 }
 
 // Byte offset of 16-byte chunk `chunk` (0..3) of row `row` in a tile whose rows are 64 bytes
@@ -108,8 +116,7 @@ __global__ void __launch_bounds__(256) mma_prep_weight_kernel(MmaDims d, const f
         float v = 0.0f;
         if (tap < d.taps && c < d.C && o < d.O) {
             int ky, kx;
-            if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
-            else { ky = tap / d.K3; kx = tap % d.K3; }
+            tap_coords(d, g, tap, &ky, &kx);
             const float x = w[(((size_t)o * d.C + c) * d.K2 + ky) * d.K3 + kx];
             v = pol == 0 ? fminf(fmaxf(x, 0.0f), 100.0f) : -fminf(fmaxf(x, -100.0f), 0.0f);
         }
@@ -154,7 +161,6 @@ __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const 
         const int oy = rem / d.Wo, ox = rem % d.Wo;
         rbase[i] = (((long long)b * d.Hp + oy) * d.Wp + ox) * d.Cp;
     }
-    const int kx_g = d.mode == GEO_SC_MODE_1D ? g : 0;
     const int nchunks = d.Kp / MK;
     int ld = 0;
     auto issue = [&]() {
@@ -164,8 +170,7 @@ __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const 
             const int tap = kp / d.Cp, c = kp % d.Cp;
             const bool kv = tap < d.taps;
             int ky, kx;
-            if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = kx_g; }
-            else { ky = tap / d.K3; kx = tap % d.K3; }
+            tap_coords(d, g, tap, &ky, &kx);
             const long long koff = kv ? ((long long)ky * d.Wp + kx) * d.Cp + c : 0;
 #pragma unroll
             for (int i = 0; i < AROWS; i++) {
@@ -325,8 +330,7 @@ __global__ void __launch_bounds__(64) mma_wgrad_kernel(MmaDims d, const __nv_bfl
     const int tap = kp / d.Cp, cch = kp % d.Cp;
     const bool kvalid = tap < d.taps;
     int ky, kx;
-    if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
-    else { ky = tap / d.K3; kx = tap % d.K3; }
+    tap_coords(d, g, tap, &ky, &kx);
     const long long koff = kvalid ? ((long long)ky * d.Wp + kx) * d.Cp + cch : 0;
 
     int ld = 0;
@@ -447,8 +451,7 @@ __global__ void __launch_bounds__(256) mma_wgrad_reduce_kernel(MmaDims d, int S,
             const int c = (int)(r % d.C); r /= d.C;
             const int tap = (int)(r % d.taps), g = (int)(r / d.taps);
             int ky, kx;
-            if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
-            else { ky = tap / d.K3; kx = tap % d.K3; }
+            tap_coords(d, g, tap, &ky, &kx);
             const float *p = partial + ((size_t)g * d.Kp + tap * d.Cp + c) * d.N2 + o;
 #pragma unroll 4
             for (int s = sub; s < S; s += SW) {
@@ -542,8 +545,7 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
     const int tap = kp / d.Cp, cch = kp % d.Cp;
     const bool kvalid = tap < d.taps;
     int ky, kx;
-    if (d.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
-    else { ky = tap / d.K3; kx = tap % d.K3; }
+    tap_coords(d, g, tap, &ky, &kx);
     const long long koff = kvalid ? ((long long)ky * d.Wp + kx) * d.Cp + cch : 0;
 
     int ld = 0;
@@ -759,7 +761,7 @@ __global__ void __launch_bounds__(128 * NWC) mma_dgrad_kernel(MmaDims d, int Cn,
             const uint32_t a_s = sbase + (uint32_t)(ld % DSTG) * ST_BYTES, b_s = a_s + 3 * A_BYTES;
             const int tap = ld / spt, n2 = (ld % spt) * 32 + gchunk * 8;
             const int ky = tap / d.K3, kx = tap % d.K3;
-            const int g = d.mode == GEO_SC_MODE_1D ? kx : 0;
+            const int g = d.mode == GEO_SC_MODE_1D ? kx : (d.mode == GEO_SC_MODE_2D ? tap : 0);
 #pragma unroll
             for (int i = 0; i < AROWS; i++) {
                 const int row = (t >> 2) + RSTEP * i;
@@ -855,7 +857,8 @@ int grid1(long long total) {
 }  // namespace
 
 bool mma_eligible(const Geometry &g) {
-    return g.mode == GEO_SC_MODE_1D || g.mode == GEO_SC_MODE_FULL_OR;   // whole-tap groups only
+    // groups made of whole filter taps over all channels
+    return g.mode == GEO_SC_MODE_1D || g.mode == GEO_SC_MODE_FULL_OR || g.mode == GEO_SC_MODE_2D;
 }
 
 MmaDims mma_dims(const Geometry &g) {
@@ -865,7 +868,7 @@ MmaDims mma_dims(const Geometry &g) {
     // the guide's own channel padding: column tiles are 64 wide = 32 channels x 2 polarities
     d.mode = g.mode; d.G = g.G; d.Opad = (g.O + 31) / 32 * 32; d.N2 = 2 * d.Opad; d.M = (int)g.M;
     d.Cp = (g.C + 7) / 8 * 8;
-    d.taps = g.mode == GEO_SC_MODE_1D ? g.K2 : g.K2 * g.K3;
+    d.taps = g.mode == GEO_SC_MODE_1D ? g.K2 : (g.mode == GEO_SC_MODE_2D ? 1 : g.K2 * g.K3);
     d.Kp = (d.taps * d.Cp + MK - 1) / MK * MK;
     return d;
 }

@@ -188,7 +188,7 @@ def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True,
                                         gw.data_ptr() if need_weight else None, scratch.data_ptr(),
                                         scratch.numel(), _stream_ptr(dev)), name)
     per_family = 3 + (2 if need_weight else 0) + (2 if need_act else 0)   # prep x2, forward, wgrad+reduce, prep+dgrad
-    if desc.mode in (MODES["1d_bin"], MODES["full_or"]):
+    if desc.mode in (MODES["1d_bin"], MODES["full_or"], MODES["2d_bin"]):
         STATS.launches += per_family + (1 if quantized else per_family)
     else:
         STATS.launches += per_family

@@ -53,7 +53,7 @@ def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
     _close(ga.cpu(), ga_ref, f"{mode} grad_act")
 
 
-@pytest.mark.parametrize("mode", ["1d_bin", "full_or"])
+@pytest.mark.parametrize("mode", ["1d_bin", "full_or", "2d_bin"])
 def test_guide_gradients_for_inputs_that_bf16_cannot_hold(cuda_device, mode):
     """Unquantised inputs: the tensor-core path must stand down (its exactness argument does not
     apply) and the fp32 FFMA kernels must produce the gradients."""
@@ -79,7 +79,7 @@ def test_guide_gradients_for_inputs_that_bf16_cannot_hold(cuda_device, mode):
     _close(ga.cpu(), ga_ref, f"{mode} grad_act (one inexact value)")
 
 
-@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or"])
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin"])
 def test_guide_backward_with_quantised_inputs_promise(cuda_device, mode):
     """geo_sc_guide_backward_quantized: same gradients as the general entry point (bit for bit) for
     inputs that keep the promise; NaN gradients, not silently wrong ones, for inputs that break it
@@ -99,7 +99,7 @@ def test_guide_backward_with_quantised_inputs_promise(cuda_device, mode):
     bad = a.clone()
     bad[0, 0, 0, 0] = 0.123456
     ga3, gw3 = ops.guide_backward(bad, w, go, desc, quantized=True)
-    if mode in ("1d_bin", "full_or"):
+    if mode in ("1d_bin", "full_or", "2d_bin"):
         assert torch.isnan(ga3).all() and torch.isnan(gw3).all()
     else:
         ga4, gw4 = ops.guide_backward(bad, w, go, desc)
@@ -114,6 +114,8 @@ FIRST_LAYER_CASES = [
     ((7, 8, 6, 6), (9, 8, 2, 2), (0, 0), "full_or"),        # one group of 4 taps x 8 channels
     ((40, 3, 16, 16), (32, 3, 5, 5), (2, 2), "1d_bin"),     # more position tiles than resident CTAs per group
     ((1, 5, 3, 3), (3, 5, 3, 3), (1, 1), "1d_bin"),         # a single, partly filled position tile
+    ((4, 8, 8, 8), (16, 8, 3, 3), (1, 1), "2d_bin"),        # nine groups of one tap x 8 channels
+    ((2, 40, 6, 6), (12, 40, 2, 3), (0, 1), "2d_bin"),      # 40 channels -> 64 members
 ]
 
 
