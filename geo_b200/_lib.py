@@ -10,8 +10,9 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "lib", "libgeo_sc.so")
 
-MODE_1D, MODE_Z, MODE_YZ, MODE_FULL_OR, MODE_2D = 0, 1, 2, 3, 4
-MODES = {"1d_bin": MODE_1D, "z_bin": MODE_Z, "yz_bin": MODE_YZ, "full_or": MODE_FULL_OR, "2d_bin": MODE_2D}
+MODE_1D, MODE_Z, MODE_YZ, MODE_FULL_OR, MODE_2D, MODE_FULL_BIN = 0, 1, 2, 3, 4, 5
+MODES = {"1d_bin": MODE_1D, "z_bin": MODE_Z, "yz_bin": MODE_YZ, "full_or": MODE_FULL_OR, "2d_bin": MODE_2D,
+         "full_bin": MODE_FULL_BIN}
 
 
 class GeoScError(RuntimeError):

@@ -37,6 +37,7 @@ CONFIGS = {
     "c4_z": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "z_bin", 8, 1, 1024),
     "c4_yz16": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "yz_bin", 8, 1, 16),
     "c4_2d": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "2d_bin", 8, 1, 1024),
+    "c4_full_bin": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "full_bin", 8, 1, 1024),
 }
 
 

@@ -35,7 +35,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->nbits = lfsr_bits(d->bit_length);
     if (!g->nbits)
         return fail(GEO_SC_ERR_BIT_LENGTH, "bit_length %d is not one of 8,16,32,64,128,256", d->bit_length);
-    if (d->mode < GEO_SC_MODE_1D || d->mode > GEO_SC_MODE_2D) return fail(GEO_SC_ERR_MODE, "mode %d", d->mode);
+    if (d->mode < GEO_SC_MODE_1D || d->mode > GEO_SC_MODE_FULL_BIN) return fail(GEO_SC_ERR_MODE, "mode %d", d->mode);
     if (d->batch < 1 || d->c_in < 1 || d->h_in < 1 || d->w_in < 1 || d->c_out < 1 || d->k_h < 1 || d->k_w < 1 ||
         d->pad_h < 0 || d->pad_w < 0)
         return fail(GEO_SC_ERR_SHAPE, "non-positive dimension (batch %d c_in %d h %d w %d c_out %d k %dx%d pad %d,%d)",
@@ -54,6 +54,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->Ho = g->Hp - g->K2 + 1; g->Wo = g->Wp - g->K3 + 1;
     g->L = d->bit_length; g->P = (g->L + 31) / 32;
     g->mode = d->mode;
+    g->guide_linear = 0;
     g->tw = d->total_width; g->lu = d->load_width; g->lw_w = d->load_wait_w; g->lw_a = d->load_wait_a;
     g->z = 1;
     long long G, K;
@@ -67,6 +68,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
         K = (long long)g->z * g->K2;
         break;
     case GEO_SC_MODE_2D: G = (long long)g->K2 * g->K3; K = g->C; break;
+    case GEO_SC_MODE_FULL_BIN: G = (long long)g->C * g->K2 * g->K3; K = 1; break;
     default: G = 1; K = (long long)g->C * g->K2 * g->K3; break;
     }
     g->NT = g->O <= 16 ? 16 : (g->O <= 32 ? 32 : 64);

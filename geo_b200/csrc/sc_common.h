@@ -28,6 +28,7 @@ struct Geometry {
     int NT;                  // c_out tile of the accumulate kernel
     int Opad;                // c_out rounded up to NT
     int tw, lu, lw_w, lw_a;  // progressive loading
+    int guide_linear;        // guide without the exp(-y) factor (full_bin: the guide is the plain convolution)
     long long M;             // output positions B*Ho*Wo
     size_t act_stream_words; // B*P*C*Hp*Wp
     size_t w_stream_words;   // P*G*K*Opad*2

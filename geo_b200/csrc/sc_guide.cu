@@ -709,11 +709,29 @@ int launch_guide_dgrad(const GuideDims &d, const DgradParams &pr, cudaStream_t s
 
 using namespace geo;
 
+namespace geo {
+namespace {
+// Geometry the guide works on.  full_bin has no OR: its guide is the plain convolution
+// (utils_functional.py:617-619), i.e. the full_or guide (one group with all members) without the exp.
+int guide_geometry(const geo_sc_conv_desc *desc, Geometry *g) {
+    if (desc && desc->mode == GEO_SC_MODE_FULL_BIN) {
+        geo_sc_conv_desc d2 = *desc;
+        d2.mode = GEO_SC_MODE_FULL_OR;
+        int rc = make_geometry(&d2, g);
+        if (rc) return rc;
+        g->guide_linear = 1;
+        return GEO_SC_OK;
+    }
+    return make_geometry(desc, g);
+}
+}  // namespace
+}  // namespace geo
+
 extern "C" {
 
 int geo_sc_guide_backward_bytes(const geo_sc_conv_desc *desc, size_t *scratch_bytes) {
     Geometry g;
-    int rc = make_geometry(desc, &g);
+    int rc = guide_geometry(desc, &g);
     if (rc) return rc;
     const GuideDims d = guide_dims(g);
     if ((long long)d.G * d.N2 * d.M > (1LL << 31) - 1 || (long long)d.J * d.K2 * d.K3 * d.N2 * d.cbpad > (1LL << 31) - 1)
@@ -744,7 +762,7 @@ int guide_backward_impl(const geo_sc_conv_desc *desc, const float *act, const fl
                         float *grad_act, float *grad_weight, void *scratch, size_t scratch_bytes, void *stream,
                         bool promised_exact) {
     Geometry g;
-    int rc = make_geometry(desc, &g);
+    int rc = guide_geometry(desc, &g);
     if (rc) return rc;
     if (!act || !weight || !grad_out || !scratch) return fail(GEO_SC_ERR_NULL, "act, weight, grad_out or scratch is NULL");
     const GuideDims d = guide_dims(g);
@@ -784,7 +802,8 @@ int guide_backward_impl(const geo_sc_conv_desc *desc, const float *act, const fl
     GEO_CUDA_CHECK(cudaGetLastError());
     FwdParams fp;
     fp.apad = apad; fp.wf = wf; fp.aoff = aoff; fp.gout = grad_out; fp.D = D;
-    fp.M = d.M; fp.O = d.O; fp.Opad = d.Opad; fp.HoWo = d.HoWo; fp.Wo = d.Wo; fp.Wp = d.Wp; fp.K = d.K;
+    fp.M = d.M; fp.O = d.O; fp.Opad = d.Opad; fp.HoWo = d.HoWo; fp.Wo = d.Wo; fp.Wp = d.Wp;
+    fp.K = g.guide_linear ? 0 : d.K;   // no members: y = 0 and D = gout * exp(-0) = gout, the linear guide
     fp.img = d.C * d.Hp * d.Wp;
     fp.inexact = inexact;
     fp.vec_ok = (d.M % 4 == 0) && (d.HoWo % 4 == 0) && (((uintptr_t)grad_out & 15) == 0);

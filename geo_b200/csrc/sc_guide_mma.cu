@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const 
         const int oy = rem / d.Wo, ox = rem % d.Wo;
         rbase[i] = (((long long)b * d.Hp + oy) * d.Wp + ox) * d.Cp;
     }
-    const int nchunks = d.Kp / MK;
+    const int nchunks = d.linear ? 0 : d.Kp / MK;   // linear guide: y = 0, D = gout
     int ld = 0;
     auto issue = [&]() {
         if (ld < nchunks) {
@@ -264,6 +264,7 @@ __global__ void __launch_bounds__(256 / MI) mma_forward_kernel(MmaDims d, const 
         }
     }
     cpa_wait<0>();
+    __syncthreads();   // the staged gout tile is complete and visible even when the member loop was empty
 
     // epilogue: accumulator (mi, ni, q): row = lane/4 + 8*(q>>1), column = ni*8 + (lane%4)*2 + (q&1)
 #pragma unroll
@@ -642,7 +643,7 @@ __global__ void __launch_bounds__(256, 2) mma_fused_wgrad_kernel(MmaDims d, cons
                 for (int q = 0; q < 4; q++) acc[jj][q] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < KS; ks++) {
-                if (ks < kpairs) {
+                if (ks < kpairs && !d.linear) {
                     uint32_t bf[4];
                     const int row = wp * 64 + kk * 16 + (lane & 7) + (lane >> 4) * 8;
                     ldsm_x4(bf, a_s + swz_rows<KS>(row, ks * 2 + ((lane >> 3) & 1)));
@@ -870,6 +871,7 @@ MmaDims mma_dims(const Geometry &g) {
     d.Cp = (g.C + 7) / 8 * 8;
     d.taps = g.mode == GEO_SC_MODE_1D ? g.K2 : (g.mode == GEO_SC_MODE_2D ? 1 : g.K2 * g.K3);
     d.Kp = (d.taps * d.Cp + MK - 1) / MK * MK;
+    d.linear = g.guide_linear;
     return d;
 }
 

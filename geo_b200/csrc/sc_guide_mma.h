@@ -11,6 +11,7 @@ struct MmaDims {
     int Cp;     // channels rounded up to 8
     int taps;   // filter taps per group
     int Kp;     // members per group, taps * Cp rounded up to the stage size
+    int linear; // guide without the exp(-y) factor: the forward product is skipped and D = gout
 };
 
 bool mma_eligible(const Geometry &g);

@@ -172,6 +172,9 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
             break;
         }
         case GEO_SC_MODE_2D: ky = g / gp.K3; kx = g % gp.K3; c = k; sidx = k; break;   // generators indexed by channel
+        case GEO_SC_MODE_FULL_BIN:   // every filter element is a group of its own; generators as in full_or
+            c = g / (gp.K2 * gp.K3); ky = (g / gp.K3) % gp.K2; kx = g % gp.K3; sidx = g;
+            break;
         default: c = k / (gp.K2 * gp.K3); ky = (k / gp.K3) % gp.K2; kx = k % gp.K3; sidx = k; break;
         }
         const bool valid = c < gp.C && k < gp.K;

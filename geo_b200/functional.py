@@ -17,7 +17,7 @@ from .guide import sc_conv2d_with_guide
 
 prec_default = 7  # 8-bit integers, one bit for the sign (utils_functional.py:28)
 
-_ACCELERATED_MODES = ("1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin")
+_ACCELERATED_MODES = ("1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin", "full_bin")
 
 
 def quantize(input, prec=8):
@@ -86,9 +86,9 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
         raise ValueError("stride must be 1: the reference's SC kernels ignore the stride argument "
                          "(sc_cuda_kernel.cu:1732-1834), so no other stride has a defined result")
     p0, p1 = _pair(padding)
-    if forward in ("full_or", "2d_bin"):
-        # The reference's full_or kernel takes no loading arguments (sc_cuda.cpp:21-32); 2d_bin exists
-        # only in its bit-serial simulation, which has no progressive loading (utils_functional.py:516-609).
+    if forward in ("full_or", "2d_bin", "full_bin"):
+        # The reference's full_or kernel takes no loading arguments (sc_cuda.cpp:21-32); 2d_bin and full_bin
+        # exist only in its bit-serial simulation, which has no progressive loading (utils_functional.py:516-609).
         load_unit, load_wait_w, load_wait_a = 8, 1, 1
     elif forward in ("1d_bin", "z_bin"):
         load_wait_a = load_wait_w  # one load_wait for both operands (sc_cuda.cpp:47-63)
@@ -101,7 +101,7 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
 
 def linear_generic(activation, weight, **kwargs):
     """SC linear layer (utils_functional.py:302-404): ``bit_length`` 128, ``generator`` None,
-    ``forward`` 'full_or', ``share`` True.  One extension over the reference: ``z_unit`` (default:
+    ``forward`` 'full_or' (or 'full_bin'), ``share`` True.  One extension over the reference: ``z_unit`` (default:
     all inputs, i.e. full OR) ORs inside groups of ``z_unit`` inputs and adds across groups.
     Shared generators (``share=True``, the reference default) and the LFSR generator only.
     Unlike the reference's simulation, levels are quantised as the extension does
@@ -110,8 +110,8 @@ def linear_generic(activation, weight, **kwargs):
     generator = kwargs.get("generator", None)
     forward = kwargs.get("forward", "full_or")
     share = kwargs.get("share", True)
-    if forward != "full_or":
-        raise NotImplementedError("forward='full_bin' exists only in the reference's bit-serial simulation")
+    if forward not in ("full_or", "full_bin"):
+        raise NotImplementedError(f"forward={forward!r} is not a mode of linear_generic")
     if generator != "lfsr" or not share:
         raise NotImplementedError("only generator='lfsr' with share=True is provided")
     if activation.dim() != 2:
@@ -119,7 +119,9 @@ def linear_generic(activation, weight, **kwargs):
     z_unit = int(kwargs.get("z_unit", activation.shape[1]))
     a4 = activation.unsqueeze(-1).unsqueeze(-1)
     w4 = weight.unsqueeze(-1).unsqueeze(-1)
-    out = sc_conv2d_with_guide(a4, w4, int(bit_length), "yz_bin", pad_h=0, pad_w=0, z_unit=z_unit,
+    # full_or: OR inside groups of z_unit inputs (all of them by default); full_bin: every product bit counted
+    mode = "yz_bin" if forward == "full_or" else "full_bin"
+    out = sc_conv2d_with_guide(a4, w4, int(bit_length), mode, pad_h=0, pad_w=0, z_unit=z_unit,
                                total_width=prec_default, load_width=8, load_wait_w=1, load_wait_a=1)
     return out.flatten(1)
 

@@ -188,7 +188,7 @@ def guide_backward(act, weight, grad_out, desc, need_act=True, need_weight=True,
                                         gw.data_ptr() if need_weight else None, scratch.data_ptr(),
                                         scratch.numel(), _stream_ptr(dev)), name)
     per_family = 3 + (2 if need_weight else 0) + (2 if need_act else 0)   # prep x2, forward, wgrad+reduce, prep+dgrad
-    if desc.mode in (MODES["1d_bin"], MODES["full_or"], MODES["2d_bin"]):
+    if desc.mode in (MODES["1d_bin"], MODES["full_or"], MODES["2d_bin"], MODES["full_bin"]):
         STATS.launches += per_family + (1 if quantized else per_family)
     else:
         STATS.launches += per_family
@@ -373,6 +373,8 @@ def weight_streams_canonical(buf, desc):
         v = v.reshape(P, zp, K3, z, K2, O, 2).permute(6, 5, 1, 3, 4, 2, 0).reshape(2, O, zp * z, K2, K3, P)[:, :, :C]
     elif mode == _lib.MODE_2D:      # g = ky*K3+kx, k = c
         v = v.reshape(P, K2, K3, C, O, 2).permute(5, 4, 3, 1, 2, 0)
+    elif mode == _lib.MODE_FULL_BIN:   # g = (c*K2+ky)*K3+kx, one member
+        v = v.reshape(P, C, K2, K3, O, 2).permute(5, 4, 1, 2, 3, 0)
     else:                           # g = 0, k = (c*K2+ky)*K3+kx
         v = v.reshape(P, C, K2, K3, O, 2).permute(5, 4, 1, 2, 3, 0)
     return v.contiguous()

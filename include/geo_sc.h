@@ -35,6 +35,8 @@ extern "C" {
 #define GEO_SC_MODE_FULL_OR 3 /* OR over (c,ky,kx): utils_functional.py:554-609 (LFSR, deterministic)     */
 #define GEO_SC_MODE_2D 4      /* OR over c, add over (ky,kx): utils_functional.py:528-541,597-601 (only in
                                  the reference's bit-serial simulation; weight generators indexed by c)  */
+#define GEO_SC_MODE_FULL_BIN 5 /* no OR at all: every product bit is counted (utils_functional.py:593-595,607-609,
+                                 simulation only); the guide is the plain convolution (:617-619)        */
 
 typedef enum geo_sc_status {
     GEO_SC_OK = 0,

@@ -28,8 +28,9 @@ REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT", os.path.join(os.sep, "root
 BUILD_DIR = os.path.join(HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libsc_oracle.so")
 
-MODE_1D, MODE_Z, MODE_YZ, MODE_FULL_OR, MODE_2D = 0, 1, 2, 3, 4
-MODES = {"1d_bin": MODE_1D, "z_bin": MODE_Z, "yz_bin": MODE_YZ, "full_or": MODE_FULL_OR, "2d_bin": MODE_2D}
+MODE_1D, MODE_Z, MODE_YZ, MODE_FULL_OR, MODE_2D, MODE_FULL_BIN = 0, 1, 2, 3, 4, 5
+MODES = {"1d_bin": MODE_1D, "z_bin": MODE_Z, "yz_bin": MODE_YZ, "full_or": MODE_FULL_OR, "2d_bin": MODE_2D,
+         "full_bin": MODE_FULL_BIN}
 
 _lib = None
 

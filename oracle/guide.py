@@ -28,6 +28,8 @@ def guide_pos_neg(a_padded, weight, mode, z_unit=1024):
     pos, neg = [], []
     if mode == "full_or":      # utils_functional.py:189-210
         return _or_approx(a, w_pos), _or_approx(a, w_neg)
+    if mode == "full_bin":     # :617-619, the plain convolution
+        return F.conv2d(a, w_pos), F.conv2d(a, w_neg)
     if mode == "1d_bin":       # :235-252, one slice per filter column
         groups = [(slice(0, C), j) for j in range(K3)]
     elif mode == "z_bin":      # :254-270, one slice per input channel

@@ -30,6 +30,7 @@
 #define GEO_MODE_YZ 2      /* OR over (c mod z, ky), binary add over (c div z, kx) */
 #define GEO_MODE_FULL_OR 3 /* OR over (c,ky,kx)                             */
 #define GEO_MODE_2D 4      /* OR over c, binary add over (ky,kx)            */
+#define GEO_MODE_FULL_BIN 5 /* binary add over (c,ky,kx): no OR               */
 
 /* LFSR width for a stream length: 8->3 ... 256->8
  * (torch_c/sc-extension/sc.cpp:313-334, sc_cuda_kernel.cu:113-134). */
@@ -224,6 +225,13 @@ int geo_oracle_accumulate(const uint32_t *as, const uint32_t *ws, int B, int C, 
                                         }
                                     total += popc32(ap) - popc32(an);
                                 }
+                        } else if (mode == GEO_MODE_FULL_BIN) {   /* utils_functional.py:593-595,607-609 */
+                            for (int c = 0; c < C; c++)
+                                for (int ky = 0; ky < K2; ky++)
+                                    for (int kx = 0; kx < K3; kx++) {
+                                        uint32_t a = A_AT(c, ky, kx);
+                                        total += popc32(a & W_AT(wp, c, ky, kx)) - popc32(a & W_AT(wn, c, ky, kx));
+                                    }
                         } else if (mode == GEO_MODE_2D) {   /* utils_functional.py:597-601 */
                             for (int ky = 0; ky < K2; ky++)
                                 for (int kx = 0; kx < K3; kx++) {
@@ -260,7 +268,7 @@ int geo_oracle_accumulate(const uint32_t *as, const uint32_t *ws, int B, int C, 
 int geo_oracle_conv2d(const float *act, const float *w, int B, int C, int H, int W, int O, int K2, int K3, int L,
                       int mode, int z_unit, int tw, int lu, int lw_w, int lw_a, int32_t *out) {
     if (!lfsr_bits(L)) return -1;
-    if (mode < 0 || mode > 4) return -3;
+    if (mode < 0 || mode > 5) return -3;
     int P = (L + 31) / 32;
     uint32_t *as = (uint32_t *)malloc((size_t)B * C * H * W * P * sizeof(uint32_t));
     uint32_t *ws = (uint32_t *)malloc((size_t)2 * O * C * K2 * K3 * P * sizeof(uint32_t));

@@ -6,7 +6,7 @@ import torch
 import oracle
 from oracle import guide as oracle_guide
 
-_MODE_NAMES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or", 4: "2d_bin"}
+_MODE_NAMES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or", 4: "2d_bin", 5: "full_bin"}
 
 
 def install(monkeypatch):

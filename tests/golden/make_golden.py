@@ -116,6 +116,32 @@ def make_2d_golden():
     print("wrote ref_legacy_2d_L128.npz")
 
 
+def make_full_bin_golden():
+    """``ref_legacy_full_bin_L128.npz``: the reference's bit-serial simulation with forward='full_bin' (every
+    product bit counted, no OR; utils_functional.py:593-595,607-609 and :379-384 for the linear layer) at L=128."""
+    uf = ref_loader.reference_python()
+    torch.manual_seed(777)
+    out = {}
+    cases = [((2, 3, 8, 8), (4, 3, 3, 3), (1, 1)), ((1, 5, 6, 7), (3, 5, 2, 4), (0, 0)), ((2, 8, 5, 5), (6, 8, 3, 2), (0, 1))]
+    for i, (ashape, wshape, pad) in enumerate(cases):
+        a = q7(torch.rand(*ashape))
+        w = q7(torch.rand(*wshape) * 2 - 1)
+        y = uf.conv2d_generic(a.clone(), w.clone(), pad, (1, 1), bit_length=128, forward="full_bin", generator="lfsr",
+                              legacy=True)
+        out[f"c{i}_a"] = a.numpy()
+        out[f"c{i}_w"] = w.numpy()
+        out[f"c{i}_meta"] = np.array([128, pad[0], pad[1], 5], np.int32)
+        out[f"c{i}_y"] = (y.detach() * 128).round().numpy().astype(np.int32)
+    out["n"] = np.array(len(cases))
+    a = q7(torch.rand(5, 24))
+    w = q7(torch.rand(7, 24) * 2 - 1)
+    y = uf.linear_generic(a.clone(), w.clone(), bit_length=128, generator="lfsr", forward="full_bin")
+    out["lin_a"], out["lin_w"] = a.numpy(), w.numpy()
+    out["lin_y"] = (y.detach() * 128).round().numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(HERE, "ref_legacy_full_bin_L128.npz"), **out)
+    print("wrote ref_legacy_full_bin_L128.npz")
+
+
 def make_training_step_golden():
     """One forward/backward/SGD step of the reference's own 4-layer CNN on the CPU
     (network.CONV_tiny_add_partial + utils_class + utils_own.forward, reference files unmodified),
@@ -180,11 +206,13 @@ def make_training_step_golden():
 
 
 if __name__ == "__main__":
-    # python tests/golden/make_golden.py [all|forward|2d|step]: each part writes only its own fixture files
+    # python tests/golden/make_golden.py [all|forward|2d|full_bin|step]: each part writes only its own fixture files
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     if which in ("all", "forward"):
         main()
     if which in ("all", "2d"):
         make_2d_golden()
+    if which in ("all", "full_bin"):
+        make_full_bin_golden()
     if which in ("all", "step"):
         make_training_step_golden()

@@ -32,7 +32,7 @@ def _close(a, b, what):
     assert err <= RTOL * scale, f"{what}: max err {err:.3e} vs scale {scale:.3e} (rel {err / scale:.2e})"
 
 
-@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin"])
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin", "full_bin"])
 @pytest.mark.parametrize("case", range(len(CASES)))
 def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
     from geo_b200 import ops
@@ -53,7 +53,7 @@ def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
     _close(ga.cpu(), ga_ref, f"{mode} grad_act")
 
 
-@pytest.mark.parametrize("mode", ["1d_bin", "full_or", "2d_bin"])
+@pytest.mark.parametrize("mode", ["1d_bin", "full_or", "2d_bin", "full_bin"])
 def test_guide_gradients_for_inputs_that_bf16_cannot_hold(cuda_device, mode):
     """Unquantised inputs: the tensor-core path must stand down (its exactness argument does not
     apply) and the fp32 FFMA kernels must produce the gradients."""
@@ -116,6 +116,7 @@ FIRST_LAYER_CASES = [
     ((1, 5, 3, 3), (3, 5, 3, 3), (1, 1), "1d_bin"),         # a single, partly filled position tile
     ((4, 8, 8, 8), (16, 8, 3, 3), (1, 1), "2d_bin"),        # nine groups of one tap x 8 channels
     ((2, 40, 6, 6), (12, 40, 2, 3), (0, 1), "2d_bin"),      # 40 channels -> 64 members
+    ((3, 4, 7, 8), (9, 4, 2, 2), (0, 0), "full_bin"),       # linear guide (no exp), 4 taps x 8 channels
 ]
 
 
@@ -153,13 +154,14 @@ def test_layer_autograd_matches_reference_semantics(cuda_device, oracle_lib):
     g = torch.Generator().manual_seed(5)
     a = q7(torch.rand(4, 6, 10, 10, generator=g))
     w = q7((torch.rand(12, 6, 5, 5, generator=g) * 2 - 1) * 0.4)
-    for mode, kw in (("1d_bin", {}), ("yz_bin", {"z_unit": 2}), ("z_bin", {}), ("full_or", {}), ("2d_bin", {})):
+    for mode, kw in (("1d_bin", {}), ("yz_bin", {"z_unit": 2}), ("z_bin", {}), ("full_or", {}), ("2d_bin", {}),
+                     ("full_bin", {})):
         ad = a.to(cuda_device).requires_grad_(True)
         wd = w.to(cuda_device).requires_grad_(True)
         out = sc_f.conv2d_generic(ad, wd, (2, 2), (1, 1), bit_length=128, forward=mode, generator="lfsr", load_unit=2,
                                   load_wait_w=2, load_wait_a=2, **kw)
-        lu = 8 if mode in ("full_or", "2d_bin") else 2
-        lw = 1 if mode in ("full_or", "2d_bin") else 2
+        lu = 8 if mode in ("full_or", "2d_bin", "full_bin") else 2
+        lw = 1 if mode in ("full_or", "2d_bin", "full_bin") else 2
         ref = oracle_lib.conv2d(a, w, 128, mode, pad_h=2, pad_w=2, load_width=lu, load_wait_w=lw, load_wait_a=lw,
                                 z_unit=kw.get("z_unit", 1024))
         assert torch.equal(out.detach().cpu(), torch.from_numpy(ref).float() / 128)

@@ -69,7 +69,7 @@ def test_functional_argument_handling(monkeypatch, oracle_lib):
     with pytest.raises(NotImplementedError):
         sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="1d_bin", generator="lfsr", legacy=True)
     with pytest.raises(NotImplementedError):
-        sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="full_bin", generator="lfsr")
+        sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="bin_mult", generator="lfsr")   # simulation-only mode
     with pytest.raises(NotImplementedError):
         sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="1d_bin", generator="acc")
     with pytest.raises(ValueError):

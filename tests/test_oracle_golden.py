@@ -50,6 +50,20 @@ def test_oracle_2d_bin_matches_reference_bit_serial_simulation(oracle_lib):
         assert np.array_equal(y, g[f"c{i}_y"]), f"case {i}"
 
 
+def test_oracle_full_bin_matches_reference_bit_serial_simulation(oracle_lib):
+    """full_bin (every product bit counted, no OR) exists only in the reference's simulation; conv cases
+    and one linear layer at L=128."""
+    g = np.load(os.path.join(GOLDEN, "ref_legacy_full_bin_L128.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1, mode = (int(v) for v in g[f"c{i}_meta"])
+        assert mode == 5
+        y = oracle_lib.conv2d(g[f"c{i}_a"], g[f"c{i}_w"], L, "full_bin", pad_h=p1, pad_w=p0)
+        assert np.array_equal(y, g[f"c{i}_y"]), f"case {i}"
+    a, w = g["lin_a"], g["lin_w"]
+    y = oracle_lib.conv2d(a[:, :, None, None], w[:, :, None, None], 128, "full_bin")[:, :, 0, 0]
+    assert np.array_equal(y, g["lin_y"])
+
+
 @pytest.mark.parametrize("name", ["ref_cuda_modes.npz"])
 def test_oracle_matches_reference_cuda_kernels(oracle_lib, name):
     path = os.path.join(GOLDEN, name)

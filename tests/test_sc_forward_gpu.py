@@ -9,7 +9,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-MODE_NAMES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or", 4: "2d_bin"}
+MODE_NAMES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or", 4: "2d_bin", 5: "full_bin"}
 
 
 def q7(x):
@@ -24,7 +24,7 @@ def _rand(ashape, wshape, seed, quant=True):
 
 
 @pytest.mark.parametrize("L", [8, 16, 32, 64, 128, 256])
-@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin"])
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin", "full_bin"])
 def test_stream_words_match_oracle(cuda_device, oracle_lib, L, mode):
     from geo_b200 import ops
 
@@ -53,7 +53,7 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin"])
+@pytest.mark.parametrize("mode", ["1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin", "full_bin"])
 @pytest.mark.parametrize("case", range(len(SHAPES)))
 def test_conv_matches_oracle(cuda_device, oracle_lib, mode, case):
     from geo_b200 import ops
@@ -72,7 +72,7 @@ def test_small_stream_lengths(cuda_device, oracle_lib):
     from geo_b200 import ops
 
     for L in (8, 16):
-        for mode in ("1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin"):
+        for mode in ("1d_bin", "z_bin", "yz_bin", "full_or", "2d_bin", "full_bin"):
             a, w = _rand((2, 4, 6, 6), (6, 4, 3, 3), L)
             y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (1, 1), z_unit=2).cpu().numpy()
             assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, z_unit=2, pad_h=1, pad_w=1))
@@ -115,6 +115,23 @@ def test_golden_reference_bit_serial_2d_bin(cuda_device):
         w = torch.from_numpy(g[f"c{i}_w"]).to(cuda_device)
         y = sc_f.conv2d_generic(a, w, (p0, p1), (1, 1), bit_length=L, forward="2d_bin", generator="lfsr")
         assert np.array_equal((y * L).round().to(torch.int32).cpu().numpy(), g[f"c{i}_y"]), f"case {i}"
+
+
+def test_golden_reference_bit_serial_full_bin(cuda_device):
+    """full_bin through conv2d_generic and linear_generic (the reference's own calls) against the outputs of
+    the reference's bit-serial simulation."""
+    from geo_b200 import functional as sc_f
+
+    g = np.load(os.path.join(GOLDEN, "ref_legacy_full_bin_L128.npz"))
+    for i in range(int(g["n"])):
+        L, p0, p1, mode = (int(v) for v in g[f"c{i}_meta"])
+        a = torch.from_numpy(g[f"c{i}_a"]).to(cuda_device)
+        w = torch.from_numpy(g[f"c{i}_w"]).to(cuda_device)
+        y = sc_f.conv2d_generic(a, w, (p0, p1), (1, 1), bit_length=L, forward="full_bin", generator="lfsr")
+        assert np.array_equal((y * L).round().to(torch.int32).cpu().numpy(), g[f"c{i}_y"]), f"case {i}"
+    a, w = torch.from_numpy(g["lin_a"]).to(cuda_device), torch.from_numpy(g["lin_w"]).to(cuda_device)
+    y = sc_f.linear_generic(a, w, bit_length=128, generator="lfsr", forward="full_bin")
+    assert np.array_equal((y * 128).round().to(torch.int32).cpu().numpy(), g["lin_y"])
 
 
 def test_golden_reference_cuda_kernels(cuda_device):
