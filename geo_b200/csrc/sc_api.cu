@@ -1,9 +1,11 @@
 // extern "C" entry points of libgeo_sc.so and the host-side geometry / planning logic.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "sc_common.h"
+#include "sc_sorted.h"
 
 namespace geo {
 
@@ -116,8 +118,28 @@ void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan) {
             if (plan->mask[p][j]) plan->act[p][plan->nact[p]++] = (unsigned char)j;
 }
 
-static size_t wprep_bytes(const Geometry &g) {
+static size_t wprep_dense_bytes(const Geometry &g) {
     return align_up(g.w_stream_words * 4, 256) + align_up(g.aoff_entries * 4, 256);
+}
+// dense streams, member offsets, then (long groups only) the sign-sorted section
+static size_t wprep_bytes(const Geometry &g) { return wprep_dense_bytes(g) + sorted_plan(g).total(); }
+
+static int prepare_all(const Geometry &g, const float *weight, void *wprep, cudaStream_t s) {
+    uint32_t *ws = (uint32_t *)wprep;
+    int32_t *aoff = (int32_t *)((char *)wprep + align_up(g.w_stream_words * 4, 256));
+    int rc = launch_prepare_weights(g, weight, ws, aoff, s);
+    if (rc) return rc;
+    if (sorted_plan(g).eligible) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    return rc;
+}
+
+static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wprep, int32_t *out, cudaStream_t s) {
+    const uint32_t *ws = (const uint32_t *)wprep;
+    const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
+    static const bool use_sorted = []() { const char *e = getenv("GEO_SC_SORTED"); return !e || e[0] != '0'; }();
+    if (use_sorted && sorted_plan(g).eligible)
+        return launch_accumulate_sorted(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
+    return launch_accumulate(g, as, ws, aoff, out, s);
 }
 static size_t astream_bytes(const Geometry &g) { return align_up(g.act_stream_words * 4, 256); }
 
@@ -202,9 +224,7 @@ int geo_sc_prepare_weights(const geo_sc_conv_desc *desc, const float *weight, vo
     if (rc) return rc;
     if (!weight) return fail(GEO_SC_ERR_NULL, "weight is NULL");
     if ((rc = check_buffer(wprep, bytes, wprep_bytes(g), "prepared-weight buffer"))) return rc;
-    uint32_t *ws = (uint32_t *)wprep;
-    int32_t *aoff = (int32_t *)((char *)wprep + align_up(g.w_stream_words * 4, 256));
-    return launch_prepare_weights(g, weight, ws, aoff, (cudaStream_t)stream);
+    return prepare_all(g, weight, wprep, (cudaStream_t)stream);
 }
 
 int geo_sc_generate_act_streams(const geo_sc_conv_desc *desc, const float *act, void *astream, size_t bytes,
@@ -225,9 +245,7 @@ int geo_sc_accumulate(const geo_sc_conv_desc *desc, const void *astream, const v
     if (!astream || !wprep || !out) return fail(GEO_SC_ERR_NULL, "astream, wprep or out is NULL");
     if (((uintptr_t)astream & 15) || ((uintptr_t)wprep & 255))
         return fail(GEO_SC_ERR_WORKSPACE, "stream buffers are misaligned");
-    const uint32_t *ws = (const uint32_t *)wprep;
-    const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
-    return launch_accumulate(g, (const uint32_t *)astream, ws, aoff, out, (cudaStream_t)stream);
+    return accumulate_any(g, (const uint32_t *)astream, wprep, out, (cudaStream_t)stream);
 }
 
 int geo_sc_conv2d_forward(const geo_sc_conv_desc *desc, const float *act, const float *weight, int32_t *out,
@@ -239,12 +257,11 @@ int geo_sc_conv2d_forward(const geo_sc_conv_desc *desc, const float *act, const 
     size_t ab = astream_bytes(g), wb = wprep_bytes(g);
     if ((rc = check_buffer(workspace, workspace_bytes, ab + wb, "workspace"))) return rc;
     uint32_t *as = (uint32_t *)workspace;
-    uint32_t *ws = (uint32_t *)((char *)workspace + ab);
-    int32_t *aoff = (int32_t *)((char *)ws + align_up(g.w_stream_words * 4, 256));
+    void *wprep = (char *)workspace + ab;
     cudaStream_t s = (cudaStream_t)stream;
-    if ((rc = launch_prepare_weights(g, weight, ws, aoff, s))) return rc;
+    if ((rc = prepare_all(g, weight, wprep, s))) return rc;
     if ((rc = launch_act_streams(g, act, as, s))) return rc;
-    return launch_accumulate(g, as, ws, aoff, out, s);
+    return accumulate_any(g, as, wprep, out, s);
 }
 
 int geo_sc_linear_forward(const geo_sc_conv_desc *desc, const float *act, const float *weight, int32_t *out,

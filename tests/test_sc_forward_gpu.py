@@ -50,6 +50,8 @@ SHAPES = [
     ((2, 6, 10, 10), (70, 6, 3, 3), (0, 0)),      # two c_out tiles
     ((3, 16, 4, 4), (10, 16, 4, 4), (0, 0)),      # one position per image, 16-wide tile
     ((1, 40, 6, 6), (8, 40, 3, 3), (1, 1)),       # 120 members per group: several chunks per group
+    ((3, 16, 10, 10), (40, 16, 5, 5), (2, 2)),    # long groups, 2 c_out tiles of 32: sign-sorted kernel, ragged tiles
+    ((2, 64, 8, 8), (32, 64, 5, 5), (2, 2)),      # 320 members per group: two sorted chunks (1600 = 9 in full_or)
 ]
 
 
