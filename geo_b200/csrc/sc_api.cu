@@ -1,7 +1,6 @@
 // extern "C" entry points of libgeo_sc.so and the host-side geometry / planning logic.
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 
 #include "sc_common.h"
@@ -136,8 +135,7 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
 static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wprep, int32_t *out, cudaStream_t s) {
     const uint32_t *ws = (const uint32_t *)wprep;
     const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
-    static const bool use_sorted = []() { const char *e = getenv("GEO_SC_SORTED"); return !e || e[0] != '0'; }();
-    if (use_sorted && sorted_plan(g).eligible)
+    if (sorted_plan(g).eligible)
         return launch_accumulate_sorted(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
     return launch_accumulate(g, as, ws, aoff, out, s);
 }
@@ -188,6 +186,15 @@ int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t
     if (members_padded) *members_padded = g.Kp;
     if (cout_tile) *cout_tile = g.NT;
     if (cout_padded) *cout_padded = g.Opad;
+    return GEO_SC_OK;
+}
+
+int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!yes) return fail(GEO_SC_ERR_NULL, "yes is NULL");
+    *yes = sorted_plan(g).eligible ? 1 : 0;
     return GEO_SC_OK;
 }
 

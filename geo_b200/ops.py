@@ -42,6 +42,14 @@ def algorithmic_work(desc):
     return 2 * mac * packs, nbytes
 
 
+def executed_lop3(desc):
+    """32-bit logic ops the accumulation kernel actually issues for the OR accumulation: the definition's
+    count for the dense kernel, at most half of it for the sign-sorted kernel (one op per weight instead of
+    one per weight and polarity; members whose four weights are all zero are skipped on top of that)."""
+    lop3, _ = algorithmic_work(desc)
+    return lop3 // 2 if _lib.is_sign_sorted(desc) else lop3
+
+
 def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -98,7 +106,7 @@ def sc_conv2d_staged(act, weight, bit_length, mode="1d_bin", padding=(0, 0), wpr
         e0.record(torch.cuda.current_stream(act.device))
         out = accumulate(astreams, wprep, d)
         e1.record(torch.cuda.current_stream(act.device))
-        STATS.records.append(algorithmic_work(d) + (e0, e1))
+        STATS.records.append(algorithmic_work(d) + (e0, e1, executed_lop3(d)))
         return out
     return accumulate(astreams, wprep, d)
 
