@@ -133,14 +133,18 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
  * 1 = negative, base 37), followed by an int32 table [group][member_padded] of activation
  * offsets; members are padded (see geo_sc_group_geometry) with zero streams, c_out_padded = c_out
  * rounded up to the kernel's c_out tile
- * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.
+ * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.  For descriptors served
+ * by the sign-sorted accumulate kernel (geo_sc_accumulate_is_sign_sorted) a third section follows:
+ * per (group, chunk of <= 160 members, quad of four output channels) the members sorted by which of the
+ * four weights are negative -- one uint4 with the four non-zero stream words per member and pack, one
+ * uint16 tile offset per member and 17 pattern boundaries; geo_sc_weight_prep_bytes covers all three.
  *
  * geo_sc_generate_act_streams replaces the generation loops at
  * sc_cuda_kernel.cu:667-691,1079-1102,1218-1236 and the quantise/pad ops in sc_cuda.cpp.
  * Layout: uint32 words [batch][pack][c_in][h_in+2*pad_h][w_in+2*pad_w].
  *
  * geo_sc_accumulate replaces stream_compute_add_direct_variable (:694-1002) and
- * matmul_outer (:43-86). */
+ * matmul_outer (:43-86); it picks the dense or the sign-sorted kernel from the descriptor alone. */
 int geo_sc_weight_prep_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
 int geo_sc_prepare_weights(const geo_sc_conv_desc *desc, const float *weight_device, void *wprep_device,
                            size_t wprep_bytes, void *stream);
