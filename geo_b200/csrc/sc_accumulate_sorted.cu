@@ -3,7 +3,7 @@
 // A weight is positive or negative, so one of its two streams is all zeros and half of the dense
 // kernel's LOP3 (sc_accumulate.cu) OR zeros into an accumulator.  Here a warp owns four output
 // channels (a "quad") and 128 positions (four per lane).  At weight-preparation time the members of a
-// group (in chunks of at most SORT_CHUNK) are sorted, per quad, by which of the four weights are
+// group (in chunks of at most kSortChunkMax) are sorted, per quad, by which of the four weights are
 // negative -- 16 patterns -- and only the non-zero stream word of each weight is kept.  The kernel
 // then runs one straight-line loop per pattern, in which every activation word meets exactly one
 // LOP3 per channel, into the accumulator of the right polarity: 16 LOP3 per member and lane instead
