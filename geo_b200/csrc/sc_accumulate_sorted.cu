@@ -61,7 +61,8 @@ __device__ __forceinline__ void run_bucket(uint32_t (&accp)[4][4], uint32_t (&ac
 }
 
 // Shared memory: activation words of one chunk [KCH][128], then the sorted lists of the CTA's NQ quads
-// for the current (pack, group, chunk): stream words [NQ][SL] uint4 and tile offsets [NQ][SL] u16.
+// for the current (pack, group, chunk): stream words [NQ][SL] uint4, tile offsets [NQ][SL] u16 and
+// pattern boundaries [NQ][18] u16.
 template <int NQ>
 __global__ void __launch_bounds__(NQ * 32, 2) accumulate_sorted_kernel(SortedParams pr) {
     extern __shared__ __align__(16) uint32_t smem[];
@@ -71,9 +72,11 @@ __global__ void __launch_bounds__(NQ * 32, 2) accumulate_sorted_kernel(SortedPar
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t sw_base = smem_base + (uint32_t)pr.KCH * 128 * 4;
     const uint32_t srow_base = sw_base + (uint32_t)NQ * pr.SL * 16;
+    const uint32_t sbeg_base = srow_base + (uint32_t)NQ * pr.SL * 2;
     const uint4 *atile = (const uint4 *)smem + lane;
     const uint4 *swl = (const uint4 *)(smem + pr.KCH * 128) + warp * pr.SL;
     const uint16_t *srl = (const uint16_t *)(smem + pr.KCH * 128 + NQ * pr.SL * 4) + warp * pr.SL;
+    const uint16_t *sbl = (const uint16_t *)(smem + pr.KCH * 128 + NQ * pr.SL * 4 + NQ * pr.SL / 2) + warp * 18;
 
     // gather assignment: thread t copies position t % 128 of rows t / 128 + i * (NQ / 4)
     constexpr int RSTEP = NQ * 32 / 128;
@@ -115,12 +118,16 @@ __global__ void __launch_bounds__(NQ * 32, 2) accumulate_sorted_kernel(SortedPar
                 for (int i = t; i < NQ * pr.SL; i += NQ * 32) cp16(sw_base + (uint32_t)i * 16, wsrc + i);
                 const uint4 *rsrc = (const uint4 *)(pr.srow + gcq0 * pr.SL);
                 for (int i = t; i < NQ * pr.SL / 8; i += NQ * 32) cp16(srow_base + (uint32_t)i * 16, rsrc + i);
+                // and so are their pattern boundaries: NQ x 18 u16 = NQ * 36 bytes
+                if (t < NQ * 36 / 16) cp16(sbeg_base + (uint32_t)t * 16, (const uint4 *)(pr.sbeg + gcq0 * 18) + t);
                 cp_commit();
                 cp_wait_all();
             }
             __syncthreads();
-            const uint16_t *beg = pr.sbeg + (gcq0 + warp) * 18;
-#define GEO_BUCKET(B) run_bucket<B>(accp, accn, atile, swl, srl, beg[B], beg[B + 1]);
+            // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
+            const int mybeg = lane < 17 ? (int)sbl[lane] : 0;
+#define GEO_BUCKET(B)                                                                                \
+    run_bucket<B>(accp, accn, atile, swl, srl, __shfl_sync(0xffffffffu, mybeg, B), __shfl_sync(0xffffffffu, mybeg, B + 1));
             GEO_BUCKET(0) GEO_BUCKET(1) GEO_BUCKET(2) GEO_BUCKET(3) GEO_BUCKET(4) GEO_BUCKET(5) GEO_BUCKET(6) GEO_BUCKET(7)
             GEO_BUCKET(8) GEO_BUCKET(9) GEO_BUCKET(10) GEO_BUCKET(11) GEO_BUCKET(12) GEO_BUCKET(13) GEO_BUCKET(14) GEO_BUCKET(15)
 #undef GEO_BUCKET
@@ -243,13 +250,13 @@ int launch_accumulate_sorted(const Geometry &g, const uint32_t *astream, const i
     pr.pack_words = g.C * g.Hp * g.Wp;
     pr.img_words = g.P * pr.pack_words;
     constexpr int NQ = 8;
-    const size_t smem = (size_t)sp.KCH * 128 * 4 + (size_t)NQ * sp.SL * 18;
+    const size_t smem = (size_t)sp.KCH * 128 * 4 + (size_t)NQ * sp.SL * 18 + NQ * 36;
     static bool configured[64] = {};
     int dev = 0;
     GEO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_sorted_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            (int)((size_t)kSortChunkMax * 128 * 4 + (size_t)NQ * kSortChunkMax * 18)));
+                                            (int)((size_t)kSortChunkMax * 128 * 4 + (size_t)NQ * kSortChunkMax * 18 + NQ * 36)));
         configured[dev] = true;
     }
     dim3 grid((unsigned)((g.M + 127) / 128), (unsigned)(sp.Q / NQ), 1);
