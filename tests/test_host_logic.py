@@ -59,6 +59,13 @@ def test_group_geometry_per_mode():
     assert _lib.group_geometry(d("yz_bin", z_unit=5)) == (15, 15, 64, 64)     # ragged last channel group
     assert _lib.group_geometry(d("yz_bin", z_unit=100)) == (5, 36, 64, 64)    # z clamps to c_in
     assert _lib.group_geometry(d("full_or")) == (1, 180, 64, 64)
+    assert _lib.group_geometry(d("2d_bin")) == (15, 12, 64, 64)              # groups = filter taps, members = channels
+    assert _lib.group_geometry(d("full_bin")) == (180, 1, 64, 64)            # every filter element its own group
+    # which accumulate kernel a descriptor gets: long groups (>= 64 padded members) the sign-sorted one
+    big = lambda mode: _lib.make_desc(8, 32, 16, 16, 32, 5, 5, 128, mode, pad_h=2, pad_w=2)  # noqa: E731
+    assert _lib.is_sign_sorted(big("1d_bin")) and _lib.is_sign_sorted(big("full_or"))
+    assert not _lib.is_sign_sorted(big("z_bin")) and not _lib.is_sign_sorted(big("2d_bin"))
+    assert not _lib.is_sign_sorted(d("1d_bin"))                               # 36 members per group: dense kernel
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 10, 3, 3, 32))[2:] == (16, 16)
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 32, 3, 3, 32))[2:] == (32, 32)
 
