@@ -43,6 +43,25 @@ class Conv2d_Add_Partial(nn.Conv2d):
                                    weight_cache=cache)
 
 
+class Linear_Or(nn.Linear):
+    """SC linear layer with OR accumulation.  The reference's LeNet model asks for ``utils_class.Linear_Or``
+    (network.py:204-206) but the class is missing from utils_class.py; this one follows ``Conv2d_Add_Partial``
+    (utils_class.py:11-35): a full-precision ``weight_org`` buffer, weights and inputs quantised at every
+    forward, value and gradient from ``linear_generic`` (utils_functional.py:302-404)."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.register_buffer("weight_org", self.weight.data.clone())
+
+    def forward(self, input, prec=7, err=7, generator="lfsr", forward="full_or"):
+        input.data = sc_f.quantize(input.data, prec=prec)
+        self.weight.data = sc_f.quantize(self.weight_org, prec=prec)
+        out = sc_f.linear_generic(input, self.weight, bit_length=2 ** err, generator=generator, forward=forward)
+        if self.bias is not None:
+            out = out + self.bias
+        return out
+
+
 class _BatchNormFixed(torch.autograd.Function):
     """Value: x * w_q + b_q (folded, 7-bit quantised scale and shift).  Gradient: that of the plain
     batch normalisation, as in the reference, where F.batch_norm provides the graph and the

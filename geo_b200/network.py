@@ -1,9 +1,11 @@
 """The models the headline benchmarks are quoted on.
 
 ``CONV_tiny_add_partial`` mirrors the reference's 4-layer SC CNN (network.py:126-190; the
-training default of main_conv.py).  ``VGG11_add_partial`` is the VGG-11-style SC CNN used for the
-data-parallel configuration; the reference has no such model file, it is built from the same
-layers in the same conv -> BN -> (pool) -> hardtanh order.
+training default of main_conv.py), ``VGG16_add_partial`` its VGG-16 (network.py:12-124) and
+``CONV_minimal_add_partial`` its LeNet (network.py:192-235): same attribute names (hence the same
+state-dict keys), per-layer settings and layer order.  ``VGG11_add_partial`` is the VGG-11-style SC CNN
+used for the data-parallel configuration; the reference has no such model file, it is built from the
+same layers in the same conv -> BN -> (pool) -> hardtanh order.
 """
 from __future__ import annotations
 
@@ -124,3 +126,101 @@ class VGG11_add_partial(nn.Module):
         x = self.tanh(self.bnf2(self._sc(self.fc2, x, n + 1)))
         x = self._sc(self.fc3, x, n + 2).view(-1, self.num_classes)
         return self.bn_out(x)
+
+
+
+class VGG16_add_partial(nn.Module):
+    """VGG-16 for SC (network.py:12-124).  ``err`` / ``z_unit`` / ``load_unit`` / ``load_wait`` hold six values:
+    for conv1-2, conv3-4, conv5-7, conv8-10, conv11-13 and the classifier.  With ``half_pool`` the conv in
+    front of a pooling layer runs at half the stream length (not below 32)."""
+
+    WIDTHS = (64, 64, 128, 128, 256, 256, 256, 512, 512, 512, 512, 512, 512)
+    STAGE = (0, 0, 1, 1, 2, 2, 2, 3, 3, 3, 4, 4, 4)          # index into the per-stage settings
+    POOL_AFTER = (2, 4, 7, 10, 13)                           # 1-based conv numbers followed by pool + dropout
+
+    def __init__(self, uniform=False, sc_compute="1d_bin", generator="lfsr", legacy=False, half_pool=True):
+        super().__init__()
+        c = 3
+        for i, wd in enumerate(self.WIDTHS, start=1):
+            setattr(self, f"conv{i}", layers.Conv2d_Add_Partial(c, wd, kernel_size=3, padding=1, bias=False))
+            setattr(self, f"bn{i}", layers.BatchNorm2d_fixed(wd))
+            c = wd
+        for i in range(1, 6):
+            setattr(self, f"drop{i}", nn.Dropout2d())
+        self.fc1 = layers.Conv2d_Add_Partial(512, 10, kernel_size=1, padding=0, bias=False)
+        self.bnfc1 = layers.BatchNorm1d_fixed(10)
+        self.pool = nn.AvgPool2d(2)
+        self.tanh = nn.Hardtanh(0, 1)
+        self.err = [7] * 6
+        self.z_unit = [5] * 6
+        self.load_unit = [2] * 6
+        self.load_wait = [2] * 6
+        self.generator = generator
+        self.compute = sc_compute
+        self.legacy = legacy
+        self.half_pool = half_pool
+        if min(self.err) < 4:   # larger weights for very short streams (network.py:66-73)
+            uniform = True
+        if uniform:
+            for mod in self.modules():
+                if isinstance(mod, nn.Conv2d):
+                    mod.weight.data.uniform_()
+                    mod.weight_org.uniform_()
+
+    def _sc(self, conv, x, stage, err):
+        return conv(x, err=err, forward=self.compute, generator=self.generator, z_unit=2 ** self.z_unit[stage],
+                    legacy=self.legacy, load_unit=self.load_unit[stage], load_wait_w=self.load_wait[stage],
+                    load_wait_a=self.load_wait[stage])
+
+    def forward(self, x):
+        pool_offset = 1 if self.half_pool else 0
+        drop = 0
+        for i, stage in enumerate(self.STAGE, start=1):
+            pooled = i in self.POOL_AFTER
+            err = max(self.err[stage] - pool_offset, 5) if pooled else self.err[stage]
+            x = self._sc(getattr(self, f"conv{i}"), x, stage, err)
+            bn = getattr(self, f"bn{i}")
+            if pooled:
+                x = layers.bn_pool_hardtanh(bn, x)      # tanh(pool(bn(x)))
+                drop += 1
+                x = getattr(self, f"drop{drop}")(x)
+            else:
+                x = self.tanh(bn(x))
+        x = self._sc(self.fc1, x, 5, self.err[5]).view(-1, 10)
+        return self.bnfc1(x)  # BN at the output stabilises training
+
+
+class CONV_minimal_add_partial(nn.Module):
+    """LeNet for SC on 28x28 single-channel inputs, stream length 32 everywhere (network.py:192-235).  The
+    reference's forward ends without a return statement; this one returns the logits."""
+
+    def __init__(self, uniform=False, legacy=False, generator="lfsr", sc_compute="1d_bin"):
+        super().__init__()
+        self.bn1 = layers.BatchNorm2d_fixed(6)
+        self.bn2 = layers.BatchNorm2d_fixed(16)
+        self.conv1 = layers.Conv2d_Add_Partial(1, 6, kernel_size=5, padding=2, bias=False)
+        self.conv2 = layers.Conv2d_Add_Partial(6, 16, kernel_size=5, padding=0, bias=False)
+        self.fc1 = layers.Linear_Or(5 * 5 * 16, 120, bias=False)
+        self.fc2 = layers.Linear_Or(120, 84, bias=False)
+        self.fc3 = layers.Linear_Or(84, 10, bias=False)
+        self.bn = layers.BatchNorm1d_fixed(10, affine=False)
+        self.pool = nn.AvgPool2d(2)
+        self.tanh = nn.Hardtanh(0, 1)
+        self.generator = generator
+        self.compute = sc_compute
+        if uniform:
+            for conv in (self.conv1, self.conv2):
+                conv.weight_org *= 2
+                conv.weight.data *= 2
+        self.err = 5
+        self.legacy = legacy
+
+    def forward(self, x):
+        for conv, bn in ((self.conv1, self.bn1), (self.conv2, self.bn2)):
+            x = conv(x, err=self.err, forward=self.compute, generator=self.generator, legacy=self.legacy)
+            x = self.tanh(bn(self.pool(x)))
+        x = x.reshape(-1, 16 * 5 * 5)
+        x = self.tanh(self.fc1(x, err=self.err, generator=self.generator))
+        x = self.tanh(self.fc2(x, err=self.err, generator=self.generator))
+        x = self.fc3(x, err=self.err, generator=self.generator)
+        return self.bn(x)

@@ -60,6 +60,28 @@ def test_training_step_matches_reference_python(monkeypatch, oracle_lib):
     assert np.allclose(net2.conv1.weight_org.numpy(), g["conv1_weight_org_after"], rtol=0, atol=2e-7)
 
 
+def test_lenet_model_with_sc_linear_layers(monkeypatch, oracle_lib):
+    """CONV_minimal_add_partial (two SC convs, three Linear_Or layers): shapes, gradients on every parameter,
+    and the linear layer's value against the oracle."""
+    from geo_b200 import layers, network
+
+    cpu_stand_in.install(monkeypatch)
+    torch.manual_seed(0)
+    net = network.CONV_minimal_add_partial()
+    x = torch.rand(3, 1, 28, 28)
+    out = net(x)
+    assert out.shape == (3, 10)
+    out.sum().backward()
+    for name, p in net.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all(), name
+    lin = layers.Linear_Or(24, 7, bias=False)
+    a = torch.rand(5, 24)
+    y = lin(a.clone(), err=6)
+    ref = oracle_lib.linear(lin.weight.new_tensor(((a * 128).round().clamp(-127, 127) / 128).numpy()), lin.weight.detach(), 64,
+                            z_unit=24)
+    assert torch.equal(y.detach() * 64, torch.from_numpy(ref).float())
+
+
 def test_functional_argument_handling(monkeypatch, oracle_lib):
     from geo_b200 import functional as sc_f
 

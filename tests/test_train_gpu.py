@@ -83,6 +83,25 @@ def test_evaluation_keeps_weight_streams_until_the_weights_change(cuda_device):
         assert torch.equal(net(x.clone()), y4)
 
 
+def test_vgg16_and_lenet_models_train_one_step(cuda_device):
+    """The two other models of the reference's network.py: one eager training step each runs on the native
+    kernels and leaves finite losses, gradients and parameters."""
+    from geo_b200 import network
+    from geo_b200.train import TrainStep
+
+    g = torch.Generator().manual_seed(21)
+    for net, x in ((network.VGG16_add_partial(), torch.rand(8, 3, 32, 32, generator=g)),
+                   (network.CONV_minimal_add_partial(), torch.rand(16, 1, 28, 28, generator=g))):
+        net = net.to(cuda_device)
+        y = torch.randint(0, 10, (x.shape[0],), generator=g).to(cuda_device)
+        step = TrainStep(net)
+        before = [p.detach().clone() for p in net.parameters()]
+        loss, out = step(x.to(cuda_device), y)
+        assert out.shape == (x.shape[0], 10) and torch.isfinite(loss)
+        changed = sum(int(not torch.equal(a, b)) for a, b in zip(before, net.parameters()))
+        assert changed > 0 and all(torch.isfinite(p).all() for p in net.parameters())
+
+
 def test_two_graph_step_with_packed_gradient_exchange(cuda_device):
     """The data-parallel hook's pack / unpack phases live inside the two graphs and only the
     collective runs between them; with a one-rank process group the result must equal the
