@@ -26,7 +26,10 @@ class ConvDesc(ctypes.Structure):
 
     _fields_ = [(n, ctypes.c_int32) for n in (
         "batch", "c_in", "h_in", "w_in", "pad_h", "pad_w", "c_out", "k_h", "k_w", "bit_length", "mode", "z_unit",
-        "total_width", "load_width", "load_wait_w", "load_wait_a")]
+        "total_width", "load_width", "load_wait_w", "load_wait_a", "generator")] + [("seed", ctypes.c_uint32)]
+
+
+GENERATORS = {"lfsr": 0, "acc": 1}
 
 
 _lib = None
@@ -97,12 +100,13 @@ def check(status, what):
 
 
 def make_desc(batch, c_in, h_in, w_in, c_out, k_h, k_w, bit_length, mode="1d_bin", pad_h=0, pad_w=0, z_unit=1 << 20,
-              total_width=7, load_width=8, load_wait_w=1, load_wait_a=None):
+              total_width=7, load_width=8, load_wait_w=1, load_wait_a=None, generator="lfsr", seed=0):
     if load_wait_a is None:
         load_wait_a = load_wait_w
     m = MODES[mode] if isinstance(mode, str) else int(mode)
+    gen = GENERATORS[generator] if isinstance(generator, str) else int(generator)
     return ConvDesc(batch, c_in, h_in, w_in, pad_h, pad_w, c_out, k_h, k_w, bit_length, m, min(int(z_unit), 1 << 30),
-                    total_width, load_width, load_wait_w, load_wait_a)
+                    total_width, load_width, load_wait_w, load_wait_a, gen, int(seed) & 0xFFFFFFFF)
 
 
 def size_query(fn_name, desc):

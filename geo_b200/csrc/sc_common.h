@@ -29,6 +29,8 @@ struct Geometry {
     int Opad;                // c_out rounded up to NT
     int tw, lu, lw_w, lw_a;  // progressive loading
     int guide_linear;        // guide without the exp(-y) factor (full_bin: the guide is the plain convolution)
+    int generator;           // GEO_SC_GEN_*
+    uint32_t seed;           // GEO_SC_GEN_ACC
     long long M;             // output positions B*Ho*Wo
     size_t act_stream_words; // B*P*C*Hp*Wp
     size_t w_stream_words;   // P*G*K*Opad*2

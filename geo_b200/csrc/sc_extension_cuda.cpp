@@ -1,6 +1,8 @@
 // Python module `sc_extension_cuda`: the reference's GPU extension API (sc_cuda.cpp:78-83),
 // same function names, positional arguments and return type (int32 CUDA tensor), served by
 // libgeo_sc.so.  This file has no kernels; it is a binding over the C ABI.
+#include <atomic>
+
 #include "sc_torch_shim.h"
 
 using geo_shim::sc_conv2d;
@@ -30,15 +32,19 @@ static at::Tensor conv2d_add_yz_variable_acc(at::Tensor input, at::Tensor weight
                      load_wait_a);
 }
 
-// sc_cuda.cpp:65-76.  The reference draws bits with cuRAND from states that its blocks share
-// and race on (sc_cuda_kernel.cu:517), so its output is not reproducible even against itself.
-// Served here by the deterministic LFSR generator with the same accumulation (y-dimension).
+// sc_cuda.cpp:65-76.  y-dimension accumulation with the "accurate" generator (sampling without
+// replacement, every stream holds exactly as many ones as its level).  The reference draws from cuRAND
+// states that its thread blocks share and race on (sc_cuda_kernel.cu:517), so its output is not
+// reproducible even against itself.  Served here by the counter-based accurate generator
+// (GEO_SC_GEN_ACC); every call takes the next seed of a process-wide counter, as a random generator
+// would move on.
 static at::Tensor conv2d_add_partial_acc_acc(at::Tensor input, at::Tensor weight, int64_t bit_length,
                                              at::IntArrayRef padding, at::IntArrayRef stride, bool share, int64_t dim) {
     (void)stride;
     (void)share;
     (void)dim;
-    return sc_conv2d(input, weight, bit_length, padding, GEO_SC_MODE_1D, 1, 7, 8, 1, 1);
+    static std::atomic<uint32_t> calls{0};
+    return sc_conv2d(input, weight, bit_length, padding, GEO_SC_MODE_1D, 1, 7, 8, 1, 1, GEO_SC_GEN_ACC, ++calls);
 }
 
 // sc_cuda.cpp:21-32.  Full OR accumulation.  The reference uses cuRAND here as well (same
@@ -57,6 +63,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("conv2d_add_yz_variable_acc", &conv2d_add_yz_variable_acc,
           "SC forward conv2d partial (yz dimension) bin add variable load lfsr generator");
     m.def("conv2d_add_partial_acc_acc", &conv2d_add_partial_acc_acc,
-          "SC forward conv2d partial bin add (deterministic generator)");
+          "SC forward conv2d partial bin add, accurate generator (counter-based, reproducible)");
     m.def("conv2d_or_acc", &conv2d_or_acc, "SC forward conv2d or add (deterministic generator)");
 }

@@ -141,6 +141,27 @@ __host__ __device__ __forceinline__ uint32_t stream_word(const uint32_t *s_pat, 
     return word;
 }
 
+// Filter coordinates (c, ky, kx) and LFSR generator index of member k of group g.
+__device__ __forceinline__ void decode_weight_member(const GenParams &gp, int g, int k, int *c, int *ky, int *kx, int *sidx) {
+    switch (gp.mode) {
+    case GEO_SC_MODE_1D: *kx = g; *c = k / gp.K2; *ky = k % gp.K2; *sidx = k; break;
+    case GEO_SC_MODE_Z: *c = g; *ky = k / gp.K3; *kx = k % gp.K3; *sidx = k; break;
+    case GEO_SC_MODE_YZ: {
+        const int zp = g / gp.K3;
+        *kx = g % gp.K3;
+        *c = zp * gp.z + k / gp.K2;
+        *ky = k % gp.K2;
+        *sidx = k;
+        break;
+    }
+    case GEO_SC_MODE_2D: *ky = g / gp.K3; *kx = g % gp.K3; *c = k; *sidx = k; break;   // generators indexed by channel
+    case GEO_SC_MODE_FULL_BIN:   // every filter element is a group of its own; generators as in full_or
+        *c = g / (gp.K2 * gp.K3); *ky = (g / gp.K3) % gp.K2; *kx = g % gp.K3; *sidx = g;
+        break;
+    default: *c = k / (gp.K2 * gp.K3); *ky = (k / gp.K3) % gp.K2; *kx = k % gp.K3; *sidx = k; break;
+    }
+}
+
 // ---- weight streams -----------------------------------------------------------------------
 // One thread per (group, member, padded c_out); writes the positive and negative stream words
 // of every pack as one 8-byte store, layout [pack][group][member][c_out_padded][2], and the
@@ -160,23 +181,7 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
         const int gk = (int)(idx / gp.Opad);
         const int k = gk % gp.Kp, g = gk / gp.Kp;   // k >= K: padding member, zero streams
         int c, ky, kx, sidx;
-        switch (gp.mode) {
-        case GEO_SC_MODE_1D: kx = g; c = k / gp.K2; ky = k % gp.K2; sidx = k; break;
-        case GEO_SC_MODE_Z: c = g; ky = k / gp.K3; kx = k % gp.K3; sidx = k; break;
-        case GEO_SC_MODE_YZ: {
-            const int zp = g / gp.K3;
-            kx = g % gp.K3;
-            c = zp * gp.z + k / gp.K2;
-            ky = k % gp.K2;
-            sidx = k;
-            break;
-        }
-        case GEO_SC_MODE_2D: ky = g / gp.K3; kx = g % gp.K3; c = k; sidx = k; break;   // generators indexed by channel
-        case GEO_SC_MODE_FULL_BIN:   // every filter element is a group of its own; generators as in full_or
-            c = g / (gp.K2 * gp.K3); ky = (g / gp.K3) % gp.K2; kx = g % gp.K3; sidx = g;
-            break;
-        default: c = k / (gp.K2 * gp.K3); ky = (k / gp.K3) % gp.K2; kx = k % gp.K3; sidx = k; break;
-        }
+        decode_weight_member(gp, g, k, &c, &ky, &kx, &sidx);
         const bool valid = c < gp.C && k < gp.K;
         if (o == 0) aoff[gk] = valid ? (c * gp.Hp + ky) * gp.Wp + kx : 0;
         int Vp = 0, Vn = 0;
@@ -231,6 +236,90 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
     }
 }
 
+// ---- "accurate" generator ---------------------------------------------------------------------------
+// Sampling without replacement (utils_functional.py:157-176): with cur ones still to place and L - k bits
+// left, bit k is one when cur * L / (L - k) exceeds a uniform integer below L -- so a stream of level V
+// holds exactly V ones.  The reference draws the integers from a random generator; here they are a hash
+// of (seed, generator id, bit index), so a seed reproduces its streams.  Every activation element and
+// every weight has its own generator id.  Bits are packed like the LFSR streams (MSB first).
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7feb352dU;
+    x ^= x >> 15; x *= 0x846ca68bU;
+    x ^= x >> 16;
+    return x;
+}
+
+// Writes the packs of one stream through `put(pack, word)`.
+template <typename Put>
+__device__ __forceinline__ void acc_stream(uint32_t seed, uint32_t id, int V, int L, int P, Put put) {
+    const uint32_t base = mix32(seed ^ mix32(id + 0x9E3779B9u));
+    const int bits = L < 32 ? L : 32;
+    int cur = V;
+    for (int p = 0; p < P; p++) {
+        uint32_t word = 0;
+        for (int i = 0; i < bits; i++) {
+            const int k = p * 32 + i;
+            const uint32_t r = mix32(base + (uint32_t)k * 0x85EBCA6Bu) >> (32 - 8) & (uint32_t)(L - 1);   // L <= 256
+            const uint32_t bit = (uint32_t)(cur * L) > r * (uint32_t)(L - k) ? 1u : 0u;
+            cur -= (int)bit;
+            word = (word << 1) | bit;
+        }
+        put(p, word);
+    }
+}
+
+__global__ void __launch_bounds__(256) act_streams_acc_kernel(GenParams gp, uint32_t seed, const float *__restrict__ act,
+                                                              uint32_t *__restrict__ as) {
+    const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
+    const unsigned total = (unsigned)gp.B * gp.C * plane;
+    const float fL = (float)gp.L;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned yx = idx % plane, bc = idx / plane;
+        const int c = (int)(bc % (unsigned)gp.C), b = (int)(bc / (unsigned)gp.C);
+        const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
+        const int yi = y - gp.pad_h, xi = x - gp.pad_w;
+        int V = 0;
+        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W) {
+            const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
+            V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
+        }
+        uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
+        const size_t pstride = (size_t)gp.C * plane;
+        acc_stream(seed, idx, V, gp.L, gp.P, [&](int p, uint32_t w) { dst[(size_t)p * pstride] = w; });
+    }
+}
+
+// Weight streams of the accurate generator: same layout as prepare_weights_kernel; generator id =
+// index of (polarity, c_out, c, ky, kx), offset so that it never meets an activation's id.
+__global__ void __launch_bounds__(256) prepare_weights_acc_kernel(GenParams gp, uint32_t seed, const float *__restrict__ w,
+                                                                  uint32_t *__restrict__ ws, int32_t *__restrict__ aoff) {
+    const long long total = (long long)gp.G * gp.Kp * gp.Opad;
+    const float fL = (float)gp.L;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int o = (int)(idx % gp.Opad);
+        const int gk = (int)(idx / gp.Opad);
+        const int k = gk % gp.Kp, g = gk / gp.Kp;
+        int c, ky, kx, sidx;
+        decode_weight_member(gp, g, k, &c, &ky, &kx, &sidx);
+        const bool valid = c < gp.C && k < gp.K;
+        if (o == 0) aoff[gk] = valid ? (c * gp.Hp + ky) * gp.Wp + kx : 0;
+        int Vp = 0, Vn = 0;
+        uint32_t id = 0;
+        if (valid && o < gp.O) {
+            const uint32_t e = (uint32_t)((((size_t)o * gp.C + c) * gp.K2 + ky) * gp.K3 + kx);
+            const float x = w[e] * fL;
+            Vp = (int)ceilf(fminf(fmaxf(x, 0.0f), fL - 1.0f));
+            Vn = (int)ceilf(-fminf(fmaxf(x, 1.0f - fL), 0.0f));
+            id = 0x80000000u + 2u * e;
+        }
+        uint32_t *dst = ws + ((size_t)g * gp.Kp + k) * gp.Opad * 2 + (size_t)o * 2;
+        const size_t pstride = (size_t)gp.G * gp.Kp * gp.Opad * 2;
+        acc_stream(seed, id, Vp, gp.L, gp.P, [&](int p, uint32_t v) { dst[(size_t)p * pstride] = v; });
+        acc_stream(seed, id + 1, Vn, gp.L, gp.P, [&](int p, uint32_t v) { dst[(size_t)p * pstride + 1] = v; });
+    }
+}
+
 static int grid_for(long long total) {
     long long blocks = (total + 255) / 256;
     const long long cap = 148LL * 16;
@@ -245,7 +334,8 @@ int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream,
     make_load_plan(g.L, g.tw, g.lu, g.lw_w, &plan);
     const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     const long long total = (long long)g.G * g.Kp * g.Opad;
-    prepare_weights_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, w, wstream, aoff);
+    if (g.generator == GEO_SC_GEN_ACC) prepare_weights_acc_kernel<<<grid_for(total), 256, 0, s>>>(gp, g.seed, w, wstream, aoff);
+    else prepare_weights_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, w, wstream, aoff);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -258,7 +348,8 @@ int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, c
     make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
     const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     const long long total = (long long)g.B * g.C * g.Hp * g.Wp;
-    act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
+    if (g.generator == GEO_SC_GEN_ACC) act_streams_acc_kernel<<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
+    else act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

@@ -13,7 +13,8 @@ namespace geo_shim {
 
 inline at::Tensor sc_conv2d(const at::Tensor &input, const at::Tensor &weight, int64_t bit_length,
                             at::IntArrayRef padding, int mode, int64_t z_unit, int64_t total_width,
-                            int64_t load_width, int64_t load_wait_w, int64_t load_wait_a) {
+                            int64_t load_width, int64_t load_wait_w, int64_t load_wait_a,
+                            int generator = GEO_SC_GEN_LFSR, uint32_t seed = 0) {
     TORCH_CHECK(input.is_cuda() && weight.is_cuda(),
                 "geo_b200 SC kernels run on CUDA tensors only (there is no CPU path in this build)");
     TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "expected NCHW input and OIHW weight");
@@ -23,7 +24,9 @@ inline at::Tensor sc_conv2d(const at::Tensor &input, const at::Tensor &weight, i
     at::Tensor a = input.to(at::kFloat).contiguous();
     at::Tensor w = weight.to(input.device(), at::kFloat).contiguous();
 
-    geo_sc_conv_desc d;
+    geo_sc_conv_desc d = {};
+    d.generator = generator;
+    d.seed = seed;
     d.batch = (int32_t)a.size(0); d.c_in = (int32_t)a.size(1); d.h_in = (int32_t)a.size(2); d.w_in = (int32_t)a.size(3);
     // F::pad(input, {p0, p0, p1, p1}) pads the last dimension by p0 and dimension 2 by p1.
     d.pad_w = (int32_t)padding[0]; d.pad_h = (int32_t)padding[1];

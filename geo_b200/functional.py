@@ -40,6 +40,18 @@ def quantize_shift(tensor, scale=None, scale_only=False):
     return q * scale, scale
 
 
+_seed_counter = [0]
+
+
+def _next_seed(gen):
+    """Seed of the next call of a random generator: a process-wide counter, so that a run is reproducible and
+    successive calls draw different streams."""
+    if gen == "lfsr":
+        return 0
+    _seed_counter[0] += 1
+    return _seed_counter[0]
+
+
 def _pair(v):
     if isinstance(v, (tuple, list)):
         return int(v[0]), int(v[1])
@@ -76,11 +88,16 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
                                   "this package only provides the accelerated kernels")
     if forward not in _ACCELERATED_MODES:
         raise NotImplementedError(f"forward={forward!r} exists only in the reference's bit-serial simulation")
-    if forward != "full_or" and generator != "lfsr":
-        # generator='acc' maps to cuRAND kernels whose output the reference itself cannot
-        # reproduce (shared, racing generator states); not provided.  full_or ignores the
-        # generator argument in the reference (utils_functional.py:511-514) and does so here.
-        raise NotImplementedError(f"generator={generator!r} with forward={forward!r} is not provided; use 'lfsr'")
+    if generator == "acc":
+        # the "accurate" generator: every stream holds exactly as many ones as its level
+        # (utils_functional.py:157-176).  The reference's is random; this one is a counter-based hash whose
+        # streams are selected by ``seed`` (keyword, default: a counter that advances with every call).
+        gen = "acc"
+    elif generator == "lfsr" or forward == "full_or":
+        # full_or ignores the generator argument in the reference (utils_functional.py:511-514) and does so here
+        gen = "lfsr"
+    else:
+        raise NotImplementedError(f"generator={generator!r} with forward={forward!r} is not provided; use 'lfsr' or 'acc'")
     sh, sw = _pair(stride)
     if (sh, sw) != (1, 1):
         raise ValueError("stride must be 1: the reference's SC kernels ignore the stride argument "
@@ -96,7 +113,8 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
                                 z_unit=int(z_unit), total_width=prec_default, load_width=int(load_unit),
                                 load_wait_w=int(load_wait_w), load_wait_a=int(load_wait_a),
                                 quantized=bool(kwargs.get("quantized", False)),
-                                weight_cache=kwargs.get("weight_cache", None))
+                                weight_cache=kwargs.get("weight_cache", None) if gen == "lfsr" else None,
+                                generator=gen, seed=int(kwargs["seed"]) if "seed" in kwargs else _next_seed(gen))
 
 
 def linear_generic(activation, weight, **kwargs):

@@ -20,9 +20,9 @@ from . import ops
 class _SCConv2dGuide(torch.autograd.Function):
     @staticmethod
     def forward(ctx, activation, weight, bit_length, mode, pad_h, pad_w, z_unit, total_width, load_width,
-                load_wait_w, load_wait_a, quantized=False, weight_cache=None):
+                load_wait_w, load_wait_a, quantized=False, weight_cache=None, generator="lfsr", seed=0):
         kw = dict(z_unit=z_unit, total_width=total_width, load_width=load_width, load_wait_w=load_wait_w,
-                  load_wait_a=load_wait_a)
+                  load_wait_a=load_wait_a, generator=generator, seed=seed)
         wprep = None
         if weight_cache is not None:
             # weight streams depend on the weights and on everything in the descriptor but the batch
@@ -48,14 +48,16 @@ class _SCConv2dGuide(torch.autograd.Function):
             ga = ga.to(activation.dtype)
         if gw is not None:
             gw = gw.to(weight.dtype)
-        return (ga, gw) + (None,) * 11
+        return (ga, gw) + (None,) * 13
 
 
 def sc_conv2d_with_guide(activation, weight, bit_length, mode, pad_h=0, pad_w=0, z_unit=1024, total_width=7,
-                         load_width=8, load_wait_w=1, load_wait_a=1, quantized=False, weight_cache=None):
+                         load_width=8, load_wait_w=1, load_wait_a=1, quantized=False, weight_cache=None,
+                         generator="lfsr", seed=0):
     """SC conv2d value with the guide's gradient; ``pad_h`` / ``pad_w`` pad dimensions 2 / 3.
     ``quantized``: the caller's promise of :func:`geo_b200.ops.guide_backward`.  ``weight_cache``: a dict
     owned by the caller in which the packed weight streams are kept between calls; the caller empties
-    it whenever the weights change."""
+    it whenever the weights change.  ``generator`` 'lfsr' or 'acc' (sampling without replacement, streams
+    selected by ``seed``)."""
     return _SCConv2dGuide.apply(activation, weight, bit_length, mode, pad_h, pad_w, z_unit, total_width, load_width,
-                                load_wait_w, load_wait_a, quantized, weight_cache)
+                                load_wait_w, load_wait_a, quantized, weight_cache, generator, seed)

@@ -38,6 +38,15 @@ extern "C" {
 #define GEO_SC_MODE_FULL_BIN 5 /* no OR at all: every product bit is counted (utils_functional.py:593-595,607-609,
                                  simulation only); the guide is the plain convolution (:617-619)        */
 
+/* Stream generators.  LFSR: the reference's deterministic generator (sc_cuda_kernel.cu:18-40,156-167), the
+ * only one with bit-exact parity.  ACC: the "accurate" generator of the reference (utils_functional.py:63-73,
+ * 157-176; cuRAND in sc_cuda_kernel.cu:354-417): sampling without replacement, so that a stream of level V
+ * holds exactly V ones; every activation element and every weight has its own generator (nothing is shared),
+ * progressive loading does not apply.  Here it is counter-based (a hash of seed, element and bit index), hence
+ * reproducible; against the reference, whose generators are random, parity is statistical only. */
+#define GEO_SC_GEN_LFSR 0
+#define GEO_SC_GEN_ACC 1
+
 typedef enum geo_sc_status {
     GEO_SC_OK = 0,
     GEO_SC_ERR_NULL = -1,        /* a required pointer is NULL                                  */
@@ -75,6 +84,8 @@ typedef struct geo_sc_conv_desc {
     int32_t mode;
     int32_t z_unit;
     int32_t total_width, load_width, load_wait_w, load_wait_a;
+    int32_t generator;   /* GEO_SC_GEN_LFSR (0, the default of a zero-initialised tail) or GEO_SC_GEN_ACC */
+    uint32_t seed;       /* GEO_SC_GEN_ACC only: selects the random streams; the same seed repeats them */
 } geo_sc_conv_desc;
 
 int geo_sc_version(void);

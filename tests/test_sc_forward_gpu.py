@@ -214,3 +214,49 @@ def test_reference_module_names_and_signatures(cuda_device, oracle_lib):
         sc_extension.conv2d_add_partial_new(a, w, 32, (0, 0), (1, 1))
     with pytest.raises(RuntimeError, match="bit_length"):
         sc_extension_cuda.conv2d_or_acc(ad, wd, 100, (0, 0), (1, 1), False)
+
+
+def _popcount(x):
+    """Ones in every element of an int32/uint32 numpy array."""
+    return np.unpackbits(np.ascontiguousarray(x).view(np.uint8)).reshape(x.shape + (32,)).sum(-1)
+
+
+@pytest.mark.parametrize("L", [8, 32, 128, 256])
+def test_accurate_generator_streams_hold_exactly_their_level(cuda_device, L):
+    """GEO_SC_GEN_ACC (sampling without replacement, utils_functional.py:157-176): the stream of level V has
+    exactly V ones, whatever the seed; a seed reproduces its streams and another seed gives others."""
+    from geo_b200 import ops
+
+    a, w = _rand((2, 5, 6, 7), (9, 5, 3, 2), 50 + L)
+    for mode in ("1d_bin", "z_bin", "full_or"):
+        d = ops.desc_for(a, w, L, mode, (1, 2), generator="acc", seed=7)
+        asg = ops.act_streams_canonical(ops.generate_act_streams(a.to(cuda_device), d), d).cpu().numpy()   # [B,C,H,W,P]
+        wsg = ops.weight_streams_canonical(ops.prepare_weights(w.to(cuda_device), d), d).cpu().numpy()     # [2,O,C,K2,K3,P]
+        ap = np.pad(a.numpy(), ((0, 0), (0, 0), (1, 1), (2, 2)))
+        va = np.ceil(np.clip(ap * L, 0, L - 1)).astype(np.int64)
+        assert np.array_equal(_popcount(asg).sum(-1), va)
+        vp = np.ceil(np.clip(w.numpy() * L, 0, L - 1)).astype(np.int64)
+        vn = np.ceil(-np.clip(w.numpy() * L, 1 - L, 0)).astype(np.int64)
+        assert np.array_equal(_popcount(wsg[0]).sum(-1), vp) and np.array_equal(_popcount(wsg[1]).sum(-1), vn)
+        y1 = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (1, 2), generator="acc", seed=7)
+        y2 = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (1, 2), generator="acc", seed=7)
+        y3 = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (1, 2), generator="acc", seed=8)
+        assert torch.equal(y1, y2) and not torch.equal(y1, y3)
+
+
+def test_accurate_generator_statistics_match_reference_simulation(cuda_device):
+    """Against the reference's random 'acc' generator only distributions can agree: mean of the outputs over
+    200 seeds against the mean over 200 runs of the reference's bit-serial simulation (fixture), element by
+    element within 5 standard errors and overall within 0.25 counts (6 standard errors of the grand mean)."""
+    from geo_b200 import functional as sc_f
+
+    g = np.load(os.path.join(GOLDEN, "ref_legacy_acc_stats.npz"))
+    a, w = torch.from_numpy(g["a"]).to(cuda_device), torch.from_numpy(g["w"]).to(cuda_device)
+    n = 200
+    runs = torch.stack([sc_f.conv2d_generic(a.clone(), w, (1, 1), (1, 1), bit_length=128, forward="1d_bin",
+                                            generator="acc", seed=1000 + i) * 128 for i in range(n)])
+    mean = runs.mean(0).cpu().numpy()
+    se = np.sqrt(g["std"] ** 2 / int(g["runs"]) + runs.std(0).cpu().numpy() ** 2 / n) + 1e-6
+    assert np.all(np.abs(mean - g["mean"]) <= 5 * se + 0.5)
+    assert abs(mean.mean() - g["mean"].mean()) <= 0.25
+    assert 0.7 <= runs.std(0).mean().item() / g["std"].mean() <= 1.3
