@@ -29,7 +29,7 @@ class ConvDesc(ctypes.Structure):
         "total_width", "load_width", "load_wait_w", "load_wait_a", "generator")] + [("seed", ctypes.c_uint32)]
 
 
-GENERATORS = {"lfsr": 0, "acc": 1}
+GENERATORS = {"lfsr": 0, "acc": 1, "rand": 2}
 
 
 _lib = None

@@ -56,7 +56,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->L = d->bit_length; g->P = (g->L + 31) / 32;
     g->mode = d->mode;
     g->guide_linear = 0;
-    if (d->generator != GEO_SC_GEN_LFSR && d->generator != GEO_SC_GEN_ACC) return fail(GEO_SC_ERR_MODE, "generator %d", d->generator);
+    if (d->generator < GEO_SC_GEN_LFSR || d->generator > GEO_SC_GEN_RAND) return fail(GEO_SC_ERR_MODE, "generator %d", d->generator);
     g->generator = d->generator;
     g->seed = d->seed;
     g->tw = d->total_width; g->lu = d->load_width; g->lw_w = d->load_wait_w; g->lw_a = d->load_wait_a;

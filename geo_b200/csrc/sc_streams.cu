@@ -249,8 +249,10 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
     return x;
 }
 
-// Writes the packs of one stream through `put(pack, word)`.
-template <typename Put>
+// Writes the packs of one stream through `put(pack, word)`.  RAND: independent bits, each one when the level
+// exceeds a fresh uniform integer below L (utils_functional.py:92-102,148-150); `id` is then the shared
+// generator index, so that streams that share a generator see the same integers.
+template <bool RAND, typename Put>
 __device__ __forceinline__ void acc_stream(uint32_t seed, uint32_t id, int V, int L, int P, Put put) {
     const uint32_t base = mix32(seed ^ mix32(id + 0x9E3779B9u));
     const int bits = L < 32 ? L : 32;
@@ -260,7 +262,7 @@ __device__ __forceinline__ void acc_stream(uint32_t seed, uint32_t id, int V, in
         for (int i = 0; i < bits; i++) {
             const int k = p * 32 + i;
             const uint32_t r = mix32(base + (uint32_t)k * 0x85EBCA6Bu) >> (32 - 8) & (uint32_t)(L - 1);   // L <= 256
-            const uint32_t bit = (uint32_t)(cur * L) > r * (uint32_t)(L - k) ? 1u : 0u;
+            const uint32_t bit = RAND ? ((uint32_t)V > r ? 1u : 0u) : ((uint32_t)(cur * L) > r * (uint32_t)(L - k) ? 1u : 0u);
             cur -= (int)bit;
             word = (word << 1) | bit;
         }
@@ -268,6 +270,7 @@ __device__ __forceinline__ void acc_stream(uint32_t seed, uint32_t id, int V, in
     }
 }
 
+template <bool RAND>
 __global__ void __launch_bounds__(256) act_streams_acc_kernel(GenParams gp, uint32_t seed, const float *__restrict__ act,
                                                               uint32_t *__restrict__ as) {
     const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
@@ -285,12 +288,16 @@ __global__ void __launch_bounds__(256) act_streams_acc_kernel(GenParams gp, uint
         }
         uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
         const size_t pstride = (size_t)gp.C * plane;
-        acc_stream(seed, idx, V, gp.L, gp.P, [&](int p, uint32_t w) { dst[(size_t)p * pstride] = w; });
+        // ACC: one generator per element; RAND: one per (channel, y, x), shared over the batch like the LFSR seeds
+        const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
+        const uint32_t id = RAND ? (uint32_t)(cc * (int)plane) + yx : idx;
+        acc_stream<RAND>(seed, id, V, gp.L, gp.P, [&](int p, uint32_t w) { dst[(size_t)p * pstride] = w; });
     }
 }
 
 // Weight streams of the accurate generator: same layout as prepare_weights_kernel; generator id =
 // index of (polarity, c_out, c, ky, kx), offset so that it never meets an activation's id.
+template <bool RAND>
 __global__ void __launch_bounds__(256) prepare_weights_acc_kernel(GenParams gp, uint32_t seed, const float *__restrict__ w,
                                                                   uint32_t *__restrict__ ws, int32_t *__restrict__ aoff) {
     const long long total = (long long)gp.G * gp.Kp * gp.Opad;
@@ -311,12 +318,13 @@ __global__ void __launch_bounds__(256) prepare_weights_acc_kernel(GenParams gp, 
             const float x = w[e] * fL;
             Vp = (int)ceilf(fminf(fmaxf(x, 0.0f), fL - 1.0f));
             Vn = (int)ceilf(-fminf(fmaxf(x, 1.0f - fL), 0.0f));
-            id = 0x80000000u + 2u * e;
+            // ACC: one generator per weight and polarity; RAND: one per LFSR generator index and polarity
+            id = 0x80000000u + 2u * (RAND ? (uint32_t)sidx : e);
         }
         uint32_t *dst = ws + ((size_t)g * gp.Kp + k) * gp.Opad * 2 + (size_t)o * 2;
         const size_t pstride = (size_t)gp.G * gp.Kp * gp.Opad * 2;
-        acc_stream(seed, id, Vp, gp.L, gp.P, [&](int p, uint32_t v) { dst[(size_t)p * pstride] = v; });
-        acc_stream(seed, id + 1, Vn, gp.L, gp.P, [&](int p, uint32_t v) { dst[(size_t)p * pstride + 1] = v; });
+        acc_stream<RAND>(seed, id, Vp, gp.L, gp.P, [&](int p, uint32_t v) { dst[(size_t)p * pstride] = v; });
+        acc_stream<RAND>(seed, id + 1, Vn, gp.L, gp.P, [&](int p, uint32_t v) { dst[(size_t)p * pstride + 1] = v; });
     }
 }
 
@@ -334,7 +342,8 @@ int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream,
     make_load_plan(g.L, g.tw, g.lu, g.lw_w, &plan);
     const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     const long long total = (long long)g.G * g.Kp * g.Opad;
-    if (g.generator == GEO_SC_GEN_ACC) prepare_weights_acc_kernel<<<grid_for(total), 256, 0, s>>>(gp, g.seed, w, wstream, aoff);
+    if (g.generator == GEO_SC_GEN_ACC) prepare_weights_acc_kernel<false><<<grid_for(total), 256, 0, s>>>(gp, g.seed, w, wstream, aoff);
+    else if (g.generator == GEO_SC_GEN_RAND) prepare_weights_acc_kernel<true><<<grid_for(total), 256, 0, s>>>(gp, g.seed, w, wstream, aoff);
     else prepare_weights_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, w, wstream, aoff);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
@@ -348,7 +357,8 @@ int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, c
     make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
     const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     const long long total = (long long)g.B * g.C * g.Hp * g.Wp;
-    if (g.generator == GEO_SC_GEN_ACC) act_streams_acc_kernel<<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
+    if (g.generator == GEO_SC_GEN_ACC) act_streams_acc_kernel<false><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
+    else if (g.generator == GEO_SC_GEN_RAND) act_streams_acc_kernel<true><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
     else act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;

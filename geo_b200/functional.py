@@ -88,16 +88,16 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
                                   "this package only provides the accelerated kernels")
     if forward not in _ACCELERATED_MODES:
         raise NotImplementedError(f"forward={forward!r} exists only in the reference's bit-serial simulation")
-    if generator == "acc":
-        # the "accurate" generator: every stream holds exactly as many ones as its level
-        # (utils_functional.py:157-176).  The reference's is random; this one is a counter-based hash whose
+    if generator in ("acc", "rand"):
+        # 'acc': every stream holds exactly as many ones as its level (utils_functional.py:157-176); 'rand':
+        # independent bits (:92-102).  The reference's are random; these are counter-based hashes whose
         # streams are selected by ``seed`` (keyword, default: a counter that advances with every call).
-        gen = "acc"
+        gen = generator
     elif generator == "lfsr" or forward == "full_or":
         # full_or ignores the generator argument in the reference (utils_functional.py:511-514) and does so here
         gen = "lfsr"
     else:
-        raise NotImplementedError(f"generator={generator!r} with forward={forward!r} is not provided; use 'lfsr' or 'acc'")
+        raise NotImplementedError(f"generator={generator!r} with forward={forward!r} is not provided; use 'lfsr', 'acc' or 'rand'")
     sh, sw = _pair(stride)
     if (sh, sw) != (1, 1):
         raise ValueError("stride must be 1: the reference's SC kernels ignore the stride argument "

@@ -46,6 +46,12 @@ extern "C" {
  * reproducible; against the reference, whose generators are random, parity is statistical only. */
 #define GEO_SC_GEN_LFSR 0
 #define GEO_SC_GEN_ACC 1
+/* RAND: the "true random" generator of the reference's simulation (utils_functional.py:92-102,148-150): every
+ * bit compares the level with a fresh uniform integer below bit_length, so the bits of a stream are independent
+ * with probability level / bit_length; the integers are shared the way the LFSR generators are (weights over
+ * c_out and the binary-accumulated axis, activations over the batch).  Counter-based like ACC, statistical
+ * parity only. */
+#define GEO_SC_GEN_RAND 2
 
 typedef enum geo_sc_status {
     GEO_SC_OK = 0,
@@ -84,8 +90,8 @@ typedef struct geo_sc_conv_desc {
     int32_t mode;
     int32_t z_unit;
     int32_t total_width, load_width, load_wait_w, load_wait_a;
-    int32_t generator;   /* GEO_SC_GEN_LFSR (0, the default of a zero-initialised tail) or GEO_SC_GEN_ACC */
-    uint32_t seed;       /* GEO_SC_GEN_ACC only: selects the random streams; the same seed repeats them */
+    int32_t generator;   /* GEO_SC_GEN_LFSR (0, the default of a zero-initialised tail), _ACC or _RAND */
+    uint32_t seed;       /* _ACC and _RAND: selects the random streams; the same seed repeats them */
 } geo_sc_conv_desc;
 
 int geo_sc_version(void);

@@ -142,24 +142,25 @@ def make_full_bin_golden():
     print("wrote ref_legacy_full_bin_L128.npz")
 
 
-def make_acc_golden():
-    """``ref_legacy_acc_stats.npz``: mean and standard deviation, over 200 runs, of the outputs of the
-    reference's bit-serial simulation with generator='acc' (random sampling without replacement,
-    utils_functional.py:157-176) for one small 1d_bin conv at L=128 -- the target of a statistical check."""
+def make_acc_golden(generator="acc"):
+    """``ref_legacy_acc_stats.npz`` / ``ref_legacy_rand_stats.npz``: mean and standard deviation, over 200 runs,
+    of the outputs of the reference's bit-serial simulation with generator='acc' (random sampling without
+    replacement, utils_functional.py:157-176) or 'rand' (independent bits, :92-102) for one small 1d_bin conv
+    at L=128 -- the target of a statistical check."""
     uf = ref_loader.reference_python()
     torch.manual_seed(99)
     a = q7(torch.rand(2, 4, 6, 6))
     w = q7((torch.rand(5, 4, 3, 3) * 2 - 1) * 0.6)
     runs = []
     for _ in range(200):
-        y = uf.conv2d_generic(a.clone(), w.clone(), (1, 1), (1, 1), bit_length=128, forward="1d_bin", generator="acc",
-                              legacy=True)
+        y = uf.conv2d_generic(a.clone(), w.clone(), (1, 1), (1, 1), bit_length=128, forward="1d_bin",
+                              generator=generator, legacy=True)
         runs.append((y.detach() * 128).round())
     r = torch.stack(runs)
-    np.savez_compressed(os.path.join(HERE, "ref_legacy_acc_stats.npz"), a=a.numpy(), w=w.numpy(),
+    np.savez_compressed(os.path.join(HERE, f"ref_legacy_{generator}_stats.npz"), a=a.numpy(), w=w.numpy(),
                         mean=r.mean(0).numpy().astype(np.float32), std=r.std(0).numpy().astype(np.float32),
                         runs=np.array(200))
-    print("wrote ref_legacy_acc_stats.npz")
+    print(f"wrote ref_legacy_{generator}_stats.npz")
 
 
 def make_training_step_golden():
@@ -226,7 +227,7 @@ def make_training_step_golden():
 
 
 if __name__ == "__main__":
-    # python tests/golden/make_golden.py [all|forward|2d|full_bin|acc|step]: each part writes only its own fixture files
+    # python tests/golden/make_golden.py [all|forward|2d|full_bin|acc|rand|step]: each part writes only its own fixture files
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     if which in ("all", "forward"):
         main()
@@ -235,6 +236,8 @@ if __name__ == "__main__":
     if which in ("all", "full_bin"):
         make_full_bin_golden()
     if which in ("all", "acc"):
-        make_acc_golden()
+        make_acc_golden("acc")
+    if which in ("all", "rand"):
+        make_acc_golden("rand")
     if which in ("all", "step"):
         make_training_step_golden()

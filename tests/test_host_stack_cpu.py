@@ -93,7 +93,7 @@ def test_functional_argument_handling(monkeypatch, oracle_lib):
     with pytest.raises(NotImplementedError):
         sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="bin_mult", generator="lfsr")   # simulation-only mode
     with pytest.raises(NotImplementedError):
-        sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="1d_bin", generator="rand")
+        sc_f.conv2d_generic(a, w, (1, 1), (1, 1), forward="1d_bin", generator="sobol")   # no such generator
     with pytest.raises(ValueError):
         sc_f.conv2d_generic(a, w, (1, 1), (2, 2), forward="1d_bin", generator="lfsr")
     # padding[0] pads the last dimension, padding[1] dimension 2 (utils_functional.py:492)
