@@ -70,6 +70,36 @@ def test_conv_matches_oracle(cuda_device, oracle_lib, mode, case):
         assert np.array_equal(y, ref), f"{mode} case {case} L={L}: {np.abs(y - ref).max()} max diff"
 
 
+def test_random_shapes_modes_and_plans(cuda_device, oracle_lib):
+    """Forty seeded random configurations (shape, mode, stream length, loading plan, a third of the weights
+    zero) against the oracle; both accumulate kernels are hit (long and short groups)."""
+    import random
+
+    from geo_b200 import _lib, ops
+
+    rng = random.Random(5)
+    kernels = set()
+    for it in range(40):
+        mode = rng.choice(["1d_bin", "full_or", "yz_bin", "2d_bin", "z_bin"])
+        C, O = rng.choice([8, 16, 24, 40, 64, 100]), rng.choice([17, 32, 33, 48, 64, 70, 96])
+        K2, K3 = rng.choice([(3, 3), (5, 5), (1, 1), (2, 4), (3, 1)])
+        H, W, B = rng.choice([6, 8, 9, 12]), rng.choice([6, 8, 10, 12]), rng.choice([2, 3, 5, 9])
+        ph, pw = rng.choice([(0, 0), (1, 1), (2, 1)])
+        L, z = rng.choice([32, 64, 128, 256]), rng.choice([4, 8, 16])
+        lu, lw = rng.choice([(8, 1), (2, 2), (1, 3)])
+        if H + 2 * ph < K2 or W + 2 * pw < K3:
+            continue
+        g = torch.Generator().manual_seed(it)
+        a = q7(torch.rand(B, C, H, W, generator=g))
+        w = q7(torch.rand(O, C, K2, K3, generator=g) * 2 - 1)
+        w.view(-1)[::3] = 0
+        kw = dict(z_unit=z, total_width=7, load_width=lu, load_wait_w=lw, load_wait_a=lw)
+        kernels.add(_lib.is_sign_sorted(ops.desc_for(a, w, L, mode, (ph, pw), **kw)))
+        y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (ph, pw), **kw).cpu().numpy()
+        assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, pad_h=ph, pad_w=pw, **kw)), (it, mode, L)
+    assert kernels == {True, False}
+
+
 def test_small_stream_lengths(cuda_device, oracle_lib):
     from geo_b200 import ops
 
