@@ -218,19 +218,18 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
 template <int NT, int NTHREADS, int KC = 16, int NSTAGE = 4, int MINB = 384 / NTHREADS>
 static int launch_tile(const Geometry &g, AccParams pr, cudaStream_t s) {
     using T = Tile<NT, NTHREADS, KC, NSTAGE>;
-    static bool configured[64] = {};
-    int dev = 0;
-    GEO_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    static PerDeviceOnce once;
+    int rc = per_device_once(once, []() -> int {
         GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_kernel<NT, NTHREADS, KC, NSTAGE, MINB>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
-        configured[dev] = true;
-    }
+        return GEO_SC_OK;
+    });
+    if (rc) return rc;
     dim3 grid((unsigned)((g.M + T::MT - 1) / T::MT), (unsigned)(g.Opad / NT), 1);
     // CTAs along grid.z share an output tile and split its (pack, group) pairs.  The split count is
     // the one that minimises (waves of resident CTAs) x (work of the longest CTA), where a CTA's
     // fixed cost (pipeline fill, epilogue) is put at 12 members' worth of work.
-    const long long tiles = (long long)grid.x * grid.y, slots = 148LL * MINB;
+    const long long tiles = (long long)grid.x * grid.y, slots = (long long)sm_count() * MINB;
     const long long pairs = (long long)g.P * g.G;
     long long splits = 1, best = -1;
     for (long long c = 1; c <= pairs && c <= 32; c++) {

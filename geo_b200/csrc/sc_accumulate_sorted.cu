@@ -214,7 +214,8 @@ __global__ void __launch_bounds__(128) sort_members_kernel(const uint32_t *__res
 
 SortedPlan sorted_plan(const Geometry &g) {
     SortedPlan sp;
-    sp.eligible = g.Kp >= 64 && g.Opad % 32 == 0 && g.M >= 128;
+    sp.layout = g.Kp >= 64 && g.Opad % 32 == 0;
+    sp.eligible = sp.layout && g.M >= 128;
     sp.NCH = (g.Kp + kSortChunkMax - 1) / kSortChunkMax;
     sp.KCH = ((g.Kp + sp.NCH - 1) / sp.NCH + 7) / 8 * 8;   // multiple of 8: the u16 lists are copied 16 bytes at a time
     sp.SL = sp.KCH;
@@ -251,16 +252,15 @@ int launch_accumulate_sorted(const Geometry &g, const uint32_t *astream, const i
     pr.img_words = g.P * pr.pack_words;
     constexpr int NQ = 8;
     const size_t smem = (size_t)sp.KCH * 128 * 4 + (size_t)NQ * sp.SL * 18 + NQ * 36;
-    static bool configured[64] = {};
-    int dev = 0;
-    GEO_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    static PerDeviceOnce once;
+    int rc = per_device_once(once, []() -> int {
         GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_sorted_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)((size_t)kSortChunkMax * 128 * 4 + (size_t)NQ * kSortChunkMax * 18 + NQ * 36)));
-        configured[dev] = true;
-    }
+        return GEO_SC_OK;
+    });
+    if (rc) return rc;
     dim3 grid((unsigned)((g.M + 127) / 128), (unsigned)(sp.Q / NQ), 1);
-    const long long tiles = (long long)grid.x * grid.y, slots = 148LL * 2, pairs = (long long)g.P * g.G;
+    const long long tiles = (long long)grid.x * grid.y, slots = (long long)sm_count() * 2, pairs = (long long)g.P * g.G;
     long long splits = 1, best = -1;
     for (long long c = 1; c <= pairs && c <= 32; c++) {
         const long long waves = (tiles * c + slots - 1) / slots;

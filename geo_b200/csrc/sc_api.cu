@@ -18,6 +18,20 @@ int fail(int status, const char *fmt, ...) {
     return status;
 }
 
+int sm_count() {
+    static std::mutex m;
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(m);
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 static int lfsr_bits(int L) {
     switch (L) {
     case 8: return 3;
@@ -131,7 +145,7 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
     int32_t *aoff = (int32_t *)((char *)wprep + align_up(g.w_stream_words * 4, 256));
     int rc = launch_prepare_weights(g, weight, ws, aoff, s);
     if (rc) return rc;
-    if (sorted_plan(g).eligible) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    if (sorted_plan(g).layout) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     return rc;
 }
 

@@ -367,7 +367,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_pool_bwd_apply_kernel(BnDims d,
 }
 
 int bn_slices(int B, int C) {
-    int S = (148 * 4 + C - 1) / C;
+    int S = (sm_count() * 4 + C - 1) / C;
     if (S > B) S = B;
     if (S < 1) S = 1;
     if (S > 64) S = 64;
@@ -376,7 +376,7 @@ int bn_slices(int B, int C) {
 
 int bn_grid(long long total) {
     long long b = (total + BN_THREADS - 1) / BN_THREADS;
-    return (int)(b < 148 * 8 ? (b > 0 ? b : 1) : 148 * 8);
+    return (int)(b < sm_count() * 8 ? (b > 0 ? b : 1) : sm_count() * 8);
 }
 
 }  // namespace

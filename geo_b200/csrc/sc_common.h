@@ -5,6 +5,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/geo_sc.h"
 
 namespace geo {
@@ -64,6 +66,28 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
                       int32_t *out, cudaStream_t s);
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Streaming multiprocessors of the current device (queried once per device, then cached): the unit
+// in which grids and split counts are sized.
+int sm_count();
+
+// Runs `f` (a callable returning a geo_sc_status) once per device and caller-owned state, under a
+// lock: per-device launch configuration (shared-memory opt-ins) from any number of host threads.
+struct PerDeviceOnce {
+    std::mutex m;
+    bool done[64] = {};
+};
+template <typename F>
+int per_device_once(PerDeviceOnce &st, F f) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(GEO_SC_ERR_CUDA, "cudaGetDevice failed");
+    if (dev < 0 || dev >= 64) return f();   // beyond the table: configure every time
+    std::lock_guard<std::mutex> lock(st.m);
+    if (st.done[dev]) return GEO_SC_OK;
+    int rc = f();
+    if (rc == GEO_SC_OK) st.done[dev] = true;
+    return rc;
+}
 
 #define GEO_CUDA_CHECK(expr)                                                                       \
     do {                                                                                           \

@@ -610,7 +610,7 @@ __global__ void __launch_bounds__(NTHREADS) guide_dgrad_kernel(DgradParams pr) {
 
 int grid1d(long long total) {
     long long blocks = (total + 255) / 256;
-    return (int)(blocks < 148 * 16 ? (blocks > 0 ? blocks : 1) : 148 * 16);
+    return (int)(blocks < sm_count() * 16 ? (blocks > 0 ? blocks : 1) : sm_count() * 16);
 }
 
 // ---- buffer plan -------------------------------------------------------------------------------------
@@ -640,7 +640,7 @@ GuidePlan guide_plan(const GuideDims &d, const Geometry &g) {
         }
     }
     const long long tiles = (long long)d.G * ((d.K + p.KT - 1) / p.KT) * ((d.N2 + WNT - 1) / WNT);
-    long long S = (148LL * 6 + tiles - 1) / tiles;
+    long long S = ((long long)sm_count() * 6 + tiles - 1) / tiles;
     const long long maxS = (d.M + WMC - 1) / WMC;
     if (S > maxS) S = maxS;
     if (S < 1) S = 1;
@@ -656,6 +656,8 @@ GuidePlan guide_plan(const GuideDims &d, const Geometry &g) {
 // that steady-state calls contain nothing but launches and can be captured into a CUDA graph).
 template <typename Kern>
 int set_smem(Kern kern, size_t bytes, bool *done) {   // `done`: one 64-entry array per kernel
+    static std::mutex m;   // host threads may launch concurrently: the flags are read and written under it
+    std::lock_guard<std::mutex> lock(m);
     int dev = 0;
     GEO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !done[dev]) {
@@ -792,7 +794,7 @@ int guide_backward_impl(const geo_sc_conv_desc *desc, const float *act, const fl
         if (promised_exact) {
             const long long na = grad_act ? (long long)d.B * d.C * d.H * d.W : 0;
             const long long nw = grad_weight ? (long long)d.O * d.C * d.K2 * d.K3 : 0;
-            guide_poison_kernel<<<148, 256, 0, s>>>(grad_act, na, grad_weight, nw, inexact);
+            guide_poison_kernel<<<sm_count(), 256, 0, s>>>(grad_act, na, grad_weight, nw, inexact);
             GEO_CUDA_CHECK(cudaGetLastError());
             return GEO_SC_OK;
         }

@@ -482,7 +482,7 @@ void launch_wgrad_reduce(const MmaDims &d, int S, const float *partial, const fl
                          cudaStream_t s) {
     const long long sets = ((long long)d.G * d.taps * d.C * d.O + 31) / 32;
     const int sw = S <= 4 ? 1 : (S <= 16 ? 2 : (S <= 64 ? 4 : 8));
-    const int blocks = (int)std::min<long long>((sets * sw + 7) / 8, 148 * 16);
+    const int blocks = (int)std::min<long long>((sets * sw + 7) / 8, sm_count() * 16);
     switch (sw) {
     case 1: mma_wgrad_reduce_kernel<1><<<blocks, 256, 0, s>>>(d, S, partial, w, gw, flag); break;
     case 2: mma_wgrad_reduce_kernel<2><<<blocks, 256, 0, s>>>(d, S, partial, w, gw, flag); break;
@@ -852,7 +852,7 @@ __global__ void __launch_bounds__(128 * NWC) mma_dgrad_kernel(MmaDims d, int Cn,
 
 int grid1(long long total) {
     long long b = (total + 255) / 256;
-    return (int)(b < 148 * 16 ? (b > 0 ? b : 1) : 148 * 16);
+    return (int)(b < sm_count() * 16 ? (b > 0 ? b : 1) : sm_count() * 16);
 }
 
 }  // namespace
@@ -893,7 +893,7 @@ MmaPlan mma_plan(const MmaDims &d) {
     p.Cn = (d.C + 31) / 32 * 32;
     p.wd_bytes = align_up((size_t)p.Cn * d.K2 * d.K3 * d.N2 * 2, 256);
     const long long tiles = (long long)d.G * ((d.Kp + 63) / 64) * (d.N2 / 64);
-    long long S = 148LL * 8 / tiles;   // at most two full waves of four resident CTAs per SM, no third
+    long long S = (long long)sm_count() * 8 / tiles;   // at most two full waves of four resident CTAs per SM, no third
     const long long maxS = (d.M + WP - 1) / WP;
     if (S > maxS) S = maxS;
     if (S < 1) S = 1;
@@ -903,7 +903,7 @@ MmaPlan mma_plan(const MmaDims &d) {
     p.S = (int)((d.M + len - 1) / len);
     // the fused kernel: two resident CTAs per SM, each writing two slices
     const long long mt = (d.M + 127) / 128;
-    long long X = 148LL * 2 / ((long long)d.G * (d.N2 / 64));
+    long long X = (long long)sm_count() * 2 / ((long long)d.G * (d.N2 / 64));
     if (X < 1) X = 1;
     if (X > mt) X = mt;
     p.fused_tiles = (int)((mt + X - 1) / X);
@@ -915,6 +915,8 @@ MmaPlan mma_plan(const MmaDims &d) {
 
 template <typename Kern>
 int opt_in_smem(Kern kern, size_t bytes, bool *done) {
+    static std::mutex m;   // host threads may launch concurrently: the flags are read and written under it
+    std::lock_guard<std::mutex> lock(m);
     int dev = 0;
     GEO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !done[dev]) {
@@ -960,7 +962,7 @@ template <int NWC>
 int launch_dgrad(const MmaDims &d, int Cn, const __nv_bfloat16 *Dh, const __nv_bfloat16 *wd, float *grad_act,
                  const int *flag, cudaStream_t s) {
     const long long ctas = (((long long)d.B * d.H * d.W + 127) / 128) * (Cn / (32 * NWC));
-    return ctas >= 148 * 2 ? launch_dgrad_staged<NWC, 2>(d, Cn, Dh, wd, grad_act, flag, s)
+    return ctas >= sm_count() * 2 ? launch_dgrad_staged<NWC, 2>(d, Cn, Dh, wd, grad_act, flag, s)
                            : launch_dgrad_staged<NWC, 3>(d, Cn, Dh, wd, grad_act, flag, s);
 }
 
@@ -1025,8 +1027,8 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         // widest channel tile that still leaves four CTAs of work per SM
         const long long ptiles = ((long long)d.B * d.H * d.W + 127) / 128;
         int rc;
-        if (p.Cn % 128 == 0 && ptiles * (p.Cn / 128) >= 148 * 4) rc = launch_dgrad<4>(d, p.Cn, Dh, wd, grad_act, flag, s);
-        else if (p.Cn % 64 == 0 && ptiles * (p.Cn / 64) >= 148 * 4) rc = launch_dgrad<2>(d, p.Cn, Dh, wd, grad_act, flag, s);
+        if (p.Cn % 128 == 0 && ptiles * (p.Cn / 128) >= sm_count() * 4) rc = launch_dgrad<4>(d, p.Cn, Dh, wd, grad_act, flag, s);
+        else if (p.Cn % 64 == 0 && ptiles * (p.Cn / 64) >= sm_count() * 4) rc = launch_dgrad<2>(d, p.Cn, Dh, wd, grad_act, flag, s);
         else rc = launch_dgrad<1>(d, p.Cn, Dh, wd, grad_act, flag, s);
         if (rc) return rc;
     }

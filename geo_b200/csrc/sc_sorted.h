@@ -9,10 +9,13 @@ namespace geo {
 constexpr int kSortChunkMax = 160;   // members of a chunk: 80 KB of activation words + 23 KB of sorted lists, two CTAs per SM
 
 struct SortedPlan {
-    bool eligible;
+    // `layout`: the prepared-weight buffer carries the sorted section.  Decided from the group length and the
+    // padded c_out alone, never from the batch, so that weights prepared once serve every batch size.
+    // `eligible`: this launch runs on the sorted kernel (layout present and at least one full position tile).
+    bool layout, eligible;
     int NCH, KCH, SL, Q;   // chunks per group, members per chunk, slots per (group, chunk, quad), quads
     size_t sw_bytes, srow_bytes, sbeg_bytes;
-    size_t total() const { return eligible ? sw_bytes + srow_bytes + sbeg_bytes : 0; }
+    size_t total() const { return layout ? sw_bytes + srow_bytes + sbeg_bytes : 0; }
 };
 
 SortedPlan sorted_plan(const Geometry &g);

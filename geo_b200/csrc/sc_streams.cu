@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(256) prepare_weights_acc_kernel(GenParams gp, 
 
 static int grid_for(long long total) {
     long long blocks = (total + 255) / 256;
-    const long long cap = 148LL * 16;
+    const long long cap = (long long)sm_count() * 16;
     return (int)(blocks < cap ? blocks : cap);
 }
 

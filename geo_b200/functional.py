@@ -4,9 +4,10 @@ Same public names, keyword arguments, defaults and error behaviour for the accel
 ``quantize`` (utils_functional.py:33-39), ``quantize_shift`` (:41-57), ``conv2d_generic``
 (:406-634) and ``linear_generic`` (:302-404).  The stochastic-computing result comes from the
 CUDA library through the C ABI; the float "guide" whose autograd is the training backward
-(:611-634) comes from the native guide kernels.  What the reference computes only through its
-bit-serial PyTorch simulation (``legacy=True``, ``2d_bin``, ``full_bin``, the ``rand``
-generator, CPU tensors) is outside this package and raises ``NotImplementedError``.
+(:611-634) comes from the native guide kernels.  All six accumulation modes (``1d_bin``, ``z_bin``,
+``yz_bin``, ``full_or``, and ``2d_bin`` / ``full_bin``, which the reference only simulates bit by bit)
+and the ``lfsr``, ``acc`` and ``rand`` generators run natively.  The bit-serial simulation itself
+(``legacy=True``) and CPU tensors are outside this package: ``NotImplementedError`` / ``RuntimeError``.
 """
 from __future__ import annotations
 

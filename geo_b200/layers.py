@@ -13,13 +13,25 @@ class Conv2d_Add_Partial(nn.Conv2d):
     """SC conv2d with partial binary accumulation (utils_class.py:11-35).
 
     Keeps a full-precision copy of the weights in the buffer ``weight_org``; every forward
-    re-quantises ``weight`` from it and quantises the input in place (straight-through)."""
+    re-quantises ``weight`` from it and quantises the input in place (straight-through).
+
+    In evaluation mode the quantised weights and their packed streams are kept between calls and
+    rebuilt when ``weight_org`` changes.  The change is noticed through the tensor's version counter,
+    which in-place operations on ``weight_org`` advance but writes through ``weight_org.data`` (some
+    optimisers and checkpoint loaders) do not: after such a write call :meth:`invalidate_stream_cache`.
+    ``load_state_dict`` does so by itself."""
 
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         self.register_buffer("weight_org", self.weight.data.clone())
         # evaluation mode: quantised weights and their packed streams are kept while weight_org is unchanged
         self._stream_cache = {}
+        self._stream_cache_tag = None
+        self.register_load_state_dict_post_hook(lambda module, incompatible: module.invalidate_stream_cache())
+
+    def invalidate_stream_cache(self):
+        """Forget the quantised weights and packed weight streams kept for evaluation mode."""
+        self._stream_cache.clear()
         self._stream_cache_tag = None
 
     def forward(self, input, prec=7, err=7, forward="1d_bin", generator="lfsr", z_unit=8, legacy=False, load_unit=8,

@@ -3,10 +3,15 @@
  * forward hot path of nanocad-lab/geo, written for NVIDIA B200 (sm_100a).
  *
  * Plain pointers and sizes only.  Every pointer named "device" must be device
- * memory of the current CUDA device; the library never allocates device memory
- * (the caller owns workspaces), never throws and never traps: every entry point
- * returns GEO_SC_OK (0) or a negative geo_sc_status, and geo_sc_last_error()
- * gives a thread-local human-readable detail.  All work is enqueued on the
+ * memory of the current CUDA device.  The library allocates no device memory at
+ * run time: the caller owns every workspace.  (Two stated exceptions: the fixed
+ * LFSR tables and the 64 MiB stream scratch of geo_sc_conv2d_forward_static are
+ * file-scope device arrays that come with the library image, and
+ * geo_sc_measure_lop3_peak allocates and frees a few bytes.)  It never throws and
+ * never traps: every entry point returns GEO_SC_OK (0) or a negative
+ * geo_sc_status, and geo_sc_last_error() gives a thread-local human-readable
+ * detail.  Entry points may be called from several host threads at once; work
+ * given to different streams is independent unless an entry point says otherwise.  All work is enqueued on the
  * stream passed in (a cudaStream_t passed as void*; NULL = default stream) and
  * the call returns without synchronising.  The one exception is the first call
  * on each device, which uploads the LFSR pattern tables with a synchronous copy;
@@ -129,7 +134,10 @@ int geo_sc_conv2d_forward(const geo_sc_conv_desc *desc, const float *act_device,
  *     rewrites every word it later reads, so that is harmless for calls that run one after
  *     another, but two calls that may overlap on the GPU (other streams, other threads) race.
  *   - The first call on each device looks up the array's device address (and, like every entry
- *     point, may upload the LFSR tables): make it before starting any stream capture. */
+ *     point, may upload the LFSR tables): make it before starting any stream capture.
+ *   - It always runs the dense accumulation kernel, because the sign-sorted weight section would
+ *     take scratch of its own: layers with long groups (64 or more members per group) give the
+ *     same result through it but run about a quarter slower than through geo_sc_conv2d_forward. */
 size_t geo_sc_static_scratch_bytes(void);
 int geo_sc_conv2d_forward_static(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
                                  int32_t *out_device, void *stream);
@@ -150,11 +158,15 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
  * 1 = negative, base 37), followed by an int32 table [group][member_padded] of activation
  * offsets; members are padded (see geo_sc_group_geometry) with zero streams, c_out_padded = c_out
  * rounded up to the kernel's c_out tile
- * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.  For descriptors served
- * by the sign-sorted accumulate kernel (geo_sc_accumulate_is_sign_sorted) a third section follows:
+ * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.  For descriptors with long
+ * groups (64 or more padded members, c_out padded to a multiple of 32) a third section follows for the
+ * sign-sorted accumulate kernel:
  * per (group, chunk of <= 160 members, quad of four output channels) the members sorted by which of the
  * four weights are negative -- one uint4 with the four non-zero stream words per member and pack, one
  * uint16 tile offset per member and 17 pattern boundaries; geo_sc_weight_prep_bytes covers all three.
+ * Neither the size nor the contents of the prepared buffer depend on `batch`: a buffer prepared once
+ * serves geo_sc_accumulate calls of any batch size whose descriptor agrees in every other field
+ * (geo_sc_accumulate picks the dense or the sign-sorted kernel per call; both sections are there).
  *
  * geo_sc_generate_act_streams replaces the generation loops at
  * sc_cuda_kernel.cu:667-691,1079-1102,1218-1236 and the quantise/pad ops in sc_cuda.cpp.

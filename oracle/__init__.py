@@ -24,7 +24,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 # where the reference's source tree is mounted, when it is (build of oracle/_ref, fixture generation)
-REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# GEO_REFERENCE_ROOT, else a checkout named "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 BUILD_DIR = os.path.join(HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libsc_oracle.so")
 

@@ -28,7 +28,9 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# GEO_REFERENCE_ROOT, else a checkout named "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("GEO_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _torch_flags():

@@ -30,14 +30,15 @@ def test_graph_replay_equals_eager_steps(cuda_device):
         net = _model(cuda_device)
         step = TrainStep(net, graph=graph, grad_hook=hook)
         losses = []
-        # graph capture warms up with three extra steps on the first batch; give the eager run the same
-        if not graph:
-            for _ in range(3):
-                step(xs[0].clone(), ys[0])
-        for x, y in zip(xs, ys):
+        # the warm-up runs of the capture are undone, so the graph's first call is one step like eager's;
+        # the learning rate changes after the second step, as a scheduler would change it
+        for i, (x, y) in enumerate(zip(xs, ys)):
+            if i == 2:
+                step.optimizer.param_groups[0]["lr"] = 5e-4
             loss, _ = step(x.clone(), y)
             losses.append(float(loss))
-        return losses, [p.detach().clone() for p in net.parameters()]
+        stats = [b.detach().clone() for n, b in net.named_buffers() if "running" in n]
+        return losses, [p.detach().clone() for p in net.parameters()] + stats
 
     l_eager, p_eager = run(False, None)
     l_graph, p_graph = run(True, None)
@@ -45,6 +46,43 @@ def test_graph_replay_equals_eager_steps(cuda_device):
     assert l_eager == l_graph == l_two              # every kernel is deterministic: bit-identical
     for a, b, c in zip(p_eager, p_graph, p_two):
         assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_graph_step_with_adam_is_capturable(cuda_device):
+    """Adam under graph replay (capturable form, tensor learning rate) follows the eager Adam step."""
+    from geo_b200.train import TrainStep
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.rand(16, 3, 32, 32, generator=g).to(cuda_device)
+    y = torch.randint(0, 10, (16,), generator=g).to(cuda_device)
+    out = []
+    for graph in (False, True):
+        net = _model(cuda_device, seed=2)
+        step = TrainStep(net, lr=1e-3, optim="Adam", graph=graph)
+        for _ in range(3):
+            loss, _ = step(x.clone(), y)
+        out.append((float(loss), [p.detach().clone() for p in net.parameters()]))
+    assert abs(out[0][0] - out[1][0]) <= 1e-4 * abs(out[0][0])
+    for a, b in zip(out[0][1], out[1][1]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-5)
+
+
+def test_evaluation_cache_survives_a_change_of_batch_size(cuda_device):
+    """Weight streams prepared at one batch size serve any other: the prepared layout (dense streams plus the
+    sign-sorted section of long-group layers) does not depend on the batch.  conv3 of the 4-layer CNN at batch 1
+    has 64 output positions (dense kernel), at batch 8 it has 512 (sign-sorted kernel)."""
+    g = torch.Generator().manual_seed(10)
+    x = torch.rand(8, 3, 32, 32, generator=g).to(cuda_device)
+    for order in ((1, 8), (8, 1)):
+        net = _model(cuda_device).eval()
+        with torch.no_grad():
+            got = [net(x[:n].clone()) for n in order]          # second call hits the cache of the first
+            for c in (net.conv1, net.conv2, net.conv3, net.fc1):
+                c.invalidate_stream_cache()
+            fresh = net(x[:order[1]].clone())                  # uncached
+            assert torch.equal(got[1], fresh)
+            big, small = (got[1], got[0]) if order == (1, 8) else (got[0], got[1])
+            assert torch.equal(big[:1], small)                 # and the result does not depend on the batch split
 
 
 def test_evaluation_keeps_weight_streams_until_the_weights_change(cuda_device):
@@ -78,9 +116,12 @@ def test_evaluation_keeps_weight_streams_until_the_weights_change(cuda_device):
         y4 = net(x.clone())
         assert not torch.equal(y1, y4)
         for c in (net.conv1, net.conv2, net.conv3, net.fc1):
-            c._stream_cache.clear()
-            c._stream_cache_tag = None
+            c.invalidate_stream_cache()
         assert torch.equal(net(x.clone()), y4)
+        # a write through .data bypasses the version counter: the cache has to be dropped by hand
+        net.conv2.weight_org.data.mul_(2.0)
+        net.conv2.invalidate_stream_cache()
+        assert torch.equal(net(x.clone()), y1)
 
 
 def test_vgg16_and_lenet_models_train_one_step(cuda_device):

@@ -18,10 +18,11 @@ def q7(x):
     return (x * 128).round().clamp(-127, 127) / 128
 
 
-def _static_forward(a, w, desc):
+def _static_forward(a, w, desc, out=None):
     from geo_b200 import _lib, ops
 
-    out = torch.full(ops.out_shape(desc), -12345, dtype=torch.int32, device=a.device)
+    if out is None:
+        out = torch.full(ops.out_shape(desc), -12345, dtype=torch.int32, device=a.device)
     stream = ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)
     _lib.check(_lib.lib().geo_sc_conv2d_forward_static(ctypes.byref(desc), a.data_ptr(), w.data_ptr(), out.data_ptr(),
                                                        stream), "geo_sc_conv2d_forward_static")
@@ -38,6 +39,11 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda_device):
         ((24, 16, 14, 14), (40, 16, 3, 3), (1, 1), 128, "1d_bin", dict(total_width=7, load_width=2, load_wait_w=2)),
         # ... then a smaller one with another mode and stream length, over the leftovers
         ((3, 6, 9, 7), (5, 6, 3, 2), (0, 1), 64, "yz_bin", dict(z_unit=2)),
+        # long groups (160 members): the ordinary entry point takes its sign-sorted kernel here, this one stays
+        # on the dense kernel; 8 x 12 x 12 positions leave a ragged last position tile
+        ((8, 32, 12, 12), (64, 32, 5, 5), (2, 2), 128, "1d_bin", dict(total_width=7, load_width=2, load_wait_w=2)),
+        # the counter-based "accurate" generator with a fixed seed
+        ((4, 8, 10, 10), (12, 8, 3, 3), (1, 1), 64, "1d_bin", dict(generator="acc", seed=11)),
     ]
     for ashape, wshape, pad, L, mode, kw in calls:
         a = q7(torch.rand(*ashape, generator=g)).to(cuda_device)
@@ -47,6 +53,27 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda_device):
         got = _static_forward(a, w, desc)
         torch.cuda.synchronize()
         assert torch.equal(got, expect), f"{mode} L={L}: static-scratch result differs"
+
+
+def test_static_scratch_call_leaves_device_memory_untouched(cuda_device):
+    """A warm call neither takes nor returns device memory: the free-memory figure of the driver is the same
+    before and after (inputs and output are allocated beforehand)."""
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(7)
+    a = q7(torch.rand(16, 8, 12, 12, generator=g)).to(cuda_device)
+    w = q7(torch.rand(16, 8, 3, 3, generator=g) * 2 - 1).to(cuda_device)
+    desc = ops.desc_for(a, w, 128, "1d_bin", (1, 1))
+    out = torch.empty(ops.out_shape(desc), dtype=torch.int32, device=cuda_device)
+    _static_forward(a, w, desc, out)          # first call on the device: address look-up, table upload
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(cuda_device)
+    for _ in range(3):
+        _static_forward(a, w, desc, out)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free_after == free_before
+    assert torch.equal(out, ops.sc_conv2d(a, w, 128, "1d_bin", (1, 1)))
 
 
 def test_static_scratch_rejects_oversized_problems(cuda_device):
