@@ -226,8 +226,58 @@ def make_training_step_golden():
     print("wrote ref_tiny_cnn_step.npz")
 
 
+def make_guide_golden():
+    """Gradients of the reference's own float guide functions (utils_functional.py:189-296), called with the weight
+    split of conv2d_generic (:611-613) and differentiated by autograd on the CPU in fp32, for every accumulation
+    mode and three small shapes each.  A fifth of the weights are exactly zero (both clamps have a kink there)
+    and the upstream gradient is random.  Inputs are stored as levels (uint8 / int8, k/128)."""
+    uf = ref_loader.reference_python()
+    g = torch.Generator().manual_seed(77)
+    shapes = [((2, 3, 7, 6), (4, 3, 3, 2), (1, 1), 2), ((1, 8, 6, 6), (5, 8, 3, 3), (0, 1), 4),
+              ((3, 6, 5, 8), (9, 6, 2, 4), (2, 0), 3)]
+    out, n = {}, 0
+    for mode in ("full_or", "1d_bin", "z_bin", "yz_bin", "2d_bin", "full_bin"):
+        for ashape, wshape, (pad_h, pad_w), z in shapes:
+            a_lv = torch.randint(0, 128, ashape, generator=g, dtype=torch.int32)
+            w_lv = torch.randint(-127, 128, wshape, generator=g, dtype=torch.int32)
+            w_lv[torch.rand(wshape, generator=g) < 0.2] = 0
+            a = (a_lv.float() / 128).requires_grad_(True)
+            w = (w_lv.float() / 128 * 0.5).requires_grad_(True)          # multiples of 1/256: still exact in bf16
+            ap = torch.nn.functional.pad(a, (pad_w, pad_w, pad_h, pad_h))
+            w_pos, w_neg = w.clamp(0, 100), -(w.clamp(-100, 0))          # utils_functional.py:611-612
+            if mode == "full_or":
+                pos, neg = uf.conv2d_or_approx(ap, w_pos, (0, 0), (1, 1)), uf.conv2d_or_approx(ap, w_neg, (0, 0), (1, 1))
+            elif mode == "full_bin":
+                pos = torch.nn.functional.conv2d(ap, w_pos, padding=(0, 0), stride=(1, 1))
+                neg = torch.nn.functional.conv2d(ap, w_neg, padding=(0, 0), stride=(1, 1))
+            elif mode == "2d_bin":
+                pos, neg = uf.conv2d_or_bin_2d(ap, w_pos, w_neg, (0, 0), (1, 1))
+            elif mode == "1d_bin":
+                pos, neg = uf.conv2d_or_bin_1d(ap, w_pos, w_neg, (0, 0), (1, 1))
+            elif mode == "z_bin":
+                pos, neg = uf.conv2d_or_bin_z(ap, w_pos, w_neg, (0, 0), (1, 1))
+            else:
+                pos, neg = uf.conv2d_or_bin_yz(ap, w_pos, w_neg, (0, 0), (1, 1), z)
+            y = pos - neg
+            go = torch.randn(y.shape, generator=g)
+            ga, gw = torch.autograd.grad(y, (a, w), go)
+            out[f"g{n}_meta"] = np.array([MODE_IDS[mode], pad_h, pad_w, z], np.int32)
+            out[f"g{n}_a"] = a_lv.to(torch.uint8).numpy()
+            out[f"g{n}_w2"] = w_lv.to(torch.int8).numpy()               # weight = level / 256
+            out[f"g{n}_go"] = go.numpy()
+            out[f"g{n}_ga"] = ga.numpy()
+            out[f"g{n}_gw"] = gw.numpy()
+            n += 1
+    out["n"] = np.array(n)
+    np.savez_compressed(os.path.join(HERE, "ref_guide_grads.npz"), **out)
+    print(f"wrote ref_guide_grads.npz ({n} cases)")
+
+
+MODE_IDS = {"1d_bin": 0, "z_bin": 1, "yz_bin": 2, "full_or": 3, "2d_bin": 4, "full_bin": 5}
+
+
 if __name__ == "__main__":
-    # python tests/golden/make_golden.py [all|forward|2d|full_bin|acc|rand|step]: each part writes only its own fixture files
+    # python tests/golden/make_golden.py [all|forward|2d|full_bin|acc|rand|step|guide]: each part writes only its own fixture files
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     if which in ("all", "forward"):
         main()
@@ -241,3 +291,5 @@ if __name__ == "__main__":
         make_acc_golden("rand")
     if which in ("all", "step"):
         make_training_step_golden()
+    if which in ("all", "guide"):
+        make_guide_golden()

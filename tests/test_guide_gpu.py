@@ -1,8 +1,13 @@
 """fp32 parity of the native guide kernels (forward exp(-y), weight and activation gradients) with
 the PyTorch restatement of the reference's guide functions, run on the CPU in fp32.
 Tolerance: 1e-5 relative to the largest magnitude of each gradient tensor."""
+import os
+import sys
+
 import pytest
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 pytestmark = pytest.mark.gpu
 RTOL = 1e-5
@@ -51,6 +56,26 @@ def test_guide_gradients_match_reference_guide(cuda_device, mode, case):
     ga, gw = ops.guide_backward(ad, wd, go.to(cuda_device), desc)
     _close(gw.cpu(), gw_ref, f"{mode} grad_weight")
     _close(ga.cpu(), ga_ref, f"{mode} grad_act")
+
+
+def test_guide_gradients_match_recorded_reference_functions(cuda_device):
+    """The CUDA guide against gradients recorded from the reference's own guide functions
+    (utils_functional.py:189-296, fixture tests/golden/ref_guide_grads.npz), every mode, through both entry
+    points: the general one and the one for quantised inputs (tensor-core kernels alone)."""
+    from test_oracle_golden import guide_fixture_cases
+
+    from geo_b200 import ops
+
+    n = 0
+    for mode, pad_h, pad_w, z, a, w, go, ga_ref, gw_ref in guide_fixture_cases():
+        desc = ops.desc_for(a, w, 128, mode, (pad_h, pad_w), z_unit=z)
+        for quantized in (False, True):
+            ga, gw = ops.guide_backward(a.to(cuda_device), w.to(cuda_device), go.to(cuda_device), desc,
+                                        quantized=quantized)
+            _close(gw.cpu(), gw_ref, f"{mode} grad_weight case {n} quantized={quantized}")
+            _close(ga.cpu(), ga_ref, f"{mode} grad_act case {n} quantized={quantized}")
+        n += 1
+    assert n == 18
 
 
 @pytest.mark.parametrize("mode", ["1d_bin", "full_or", "2d_bin", "full_bin"])

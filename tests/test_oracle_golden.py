@@ -95,3 +95,35 @@ def test_mode_identities(oracle_lib):
     # zero weights or zero activations give zero counts
     assert not oracle_lib.conv2d(a * 0, w, 64).any()
     assert not oracle_lib.conv2d(a, w * 0, 64).any()
+
+
+_GUIDE_MODES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or", 4: "2d_bin", 5: "full_bin"}
+
+
+def guide_fixture_cases():
+    """(mode, pad_h, pad_w, z_unit, act, weight, grad_out, grad_act, grad_weight) of every recorded case: gradients of
+    the reference's own guide functions (utils_functional.py:189-296) under autograd, fp32 on the CPU."""
+    import torch
+
+    g = np.load(os.path.join(GOLDEN, "ref_guide_grads.npz"))
+    for i in range(int(g["n"])):
+        mode, pad_h, pad_w, z = (int(v) for v in g[f"g{i}_meta"])
+        a = torch.from_numpy(g[f"g{i}_a"].astype(np.float32)) / 128
+        w = torch.from_numpy(g[f"g{i}_w2"].astype(np.float32)) / 256
+        yield (_GUIDE_MODES[mode], pad_h, pad_w, z, a, w, torch.from_numpy(g[f"g{i}_go"]),
+               torch.from_numpy(g[f"g{i}_ga"]), torch.from_numpy(g[f"g{i}_gw"]))
+
+
+def test_guide_oracle_matches_reference_guide_functions():
+    """The guide restatement against the recorded gradients of the reference's functions, all six modes:
+    1e-5 of the largest gradient magnitude (both run fp32 convolutions on the CPU; only summation order differs)."""
+    from oracle import guide as oracle_guide
+
+    n = 0
+    for mode, pad_h, pad_w, z, a, w, go, ga_ref, gw_ref in guide_fixture_cases():
+        ga, gw = oracle_guide.guide_grads(a, w, go, mode, pad_h, pad_w, z_unit=z)
+        for mine, ref, what in ((ga, ga_ref, "grad_act"), (gw, gw_ref, "grad_weight")):
+            scale = ref.abs().max().item() + 1e-30
+            assert (mine - ref).abs().max().item() <= 1e-5 * scale, f"{mode} {what} case {n}"
+        n += 1
+    assert n == 18
