@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "sc_common.h"
+#include "sc_rows.h"
 #include "sc_sorted.h"
 
 namespace geo {
@@ -137,22 +138,29 @@ void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan) {
 static size_t wprep_dense_bytes(const Geometry &g) {
     return align_up(g.w_stream_words * 4, 256) + align_up(g.aoff_entries * 4, 256);
 }
-// dense streams, member offsets, then (long groups only) the sign-sorted section
-static size_t wprep_bytes(const Geometry &g) { return wprep_dense_bytes(g) + sorted_plan(g).total(); }
+// dense streams, member offsets, then (long groups only) one sign-sorted section: the row-tile form where the
+// layer's geometry allows it, else the im2col form
+static size_t wprep_bytes(const Geometry &g) {
+    const RowsPlan rp = rows_plan(g);
+    return wprep_dense_bytes(g) + (rp.layout ? rp.total() : sorted_plan(g).total());
+}
 
 static int prepare_all(const Geometry &g, const float *weight, void *wprep, cudaStream_t s) {
     uint32_t *ws = (uint32_t *)wprep;
     int32_t *aoff = (int32_t *)((char *)wprep + align_up(g.w_stream_words * 4, 256));
     int rc = launch_prepare_weights(g, weight, ws, aoff, s);
     if (rc) return rc;
-    if (sorted_plan(g).layout) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    if (rows_plan(g).layout) rc = launch_sort_rows(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    else if (sorted_plan(g).layout) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     return rc;
 }
 
 static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wprep, int32_t *out, cudaStream_t s) {
     const uint32_t *ws = (const uint32_t *)wprep;
     const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
-    if (sorted_plan(g).eligible)
+    const RowsPlan rp = rows_plan(g);
+    if (rp.eligible) return launch_accumulate_rows(g, as, (const char *)wprep + wprep_dense_bytes(g), out, s);
+    if (!rp.layout && sorted_plan(g).eligible)
         return launch_accumulate_sorted(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
     return launch_accumulate(g, as, ws, aoff, out, s);
 }
@@ -211,7 +219,8 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes) {
     int rc = make_geometry(desc, &g);
     if (rc) return rc;
     if (!yes) return fail(GEO_SC_ERR_NULL, "yes is NULL");
-    *yes = sorted_plan(g).eligible ? 1 : 0;
+    const RowsPlan rp = rows_plan(g);
+    *yes = rp.eligible || (!rp.layout && sorted_plan(g).eligible) ? 1 : 0;
     return GEO_SC_OK;
 }
 
