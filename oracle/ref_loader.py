@@ -27,9 +27,17 @@ def _cpu_flags():
 def _load(path, name):
     import torch  # noqa: F401  (libtorch must be loaded before the extension)
 
+    # Creating an extension module also files it in sys.modules under its own name, where it would shadow
+    # this repository's modules of the same names (the torch shims sc_extension / sc_extension_cuda): put back
+    # whatever was there.
+    saved = sys.modules.get(name)
     spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
+    if saved is not None:
+        sys.modules[name] = saved
+    elif sys.modules.get(name) is mod:
+        del sys.modules[name]
     return mod
 
 

@@ -218,11 +218,16 @@ def test_reference_module_names_and_signatures(cuda_device, oracle_lib):
     """The pybind11 shims keep the reference's module and function names (sc_cuda.cpp:78-83)."""
     ext_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "geo_b200", "ext")
     sys.path.insert(0, ext_dir)
+    saved = {n: sys.modules.pop(n, None) for n in ("sc_extension", "sc_extension_cuda")}
     try:
         import sc_extension
         import sc_extension_cuda
     finally:
         sys.path.remove(ext_dir)
+        for n, m in saved.items():
+            if m is not None:
+                sys.modules[n] = m
+    assert os.path.dirname(sc_extension.__file__) == ext_dir and os.path.dirname(sc_extension_cuda.__file__) == ext_dir
     a, w = _rand((2, 4, 8, 8), (6, 4, 3, 3), 9)
     ad, wd = a.to(cuda_device), w.to(cuda_device)
     ap = torch.nn.functional.pad(ad, (1, 1, 1, 1))
