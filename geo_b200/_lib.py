@@ -74,6 +74,10 @@ def lib():
     L.geo_sc_counts_to_float.argtypes = [vp, vp, sz, i32, vp]
     L.geo_sc_bn_pool_act_forward.argtypes = [i32, i32, i32, i32, i32, f32, f32] + [vp] * 12 + [sz, vp]
     L.geo_sc_bn_pool_act_backward.argtypes = [i32, i32, i32, i32, i32] + [vp] * 11 + [sz, vp]
+    L.geo_sc_epilogue_forward.argtypes = [dp, i32, i32, i32, f32, f32] + [vp] * 12 + [sz, vp, sz, vp]
+    L.geo_sc_epilogue_backward.argtypes = [i32] * 6 + [vp] * 10 + [vp, sz, vp]
+    L.geo_sc_epilogue_forward.restype = i32
+    L.geo_sc_epilogue_backward.restype = i32
     L.geo_sc_pool_act_forward.argtypes = [i32, i32, i32, vp, vp, vp]
     L.geo_sc_pool_act_backward.argtypes = [i32, i32, i32, vp, vp, vp, vp]
     L.geo_sc_guide_backward_bytes.argtypes = [dp, szp]

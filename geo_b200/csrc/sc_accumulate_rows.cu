@@ -53,17 +53,33 @@ struct RowsParams {
     long long n_items;
 };
 
-// One pattern's members: PAT bit j set = the weight of channel j is negative.
+// Shared-memory loads with explicit 32-bit shared-space addresses: the inner loop is all address arithmetic and
+// loads around the LOP3s, and generic 64-bit pointers would triple the integer instructions per member.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// One pattern's members: PAT bit j set = the weight of channel j is negative.  a_lo / a_hi: shared address of the
+// lane's two runs of four positions in plane 0, row 0; sw / so: shared address of the quad's stream-word and
+// offset lists; members [i0, i1) of the lists.
 template <int PAT>
-__device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], const unsigned char *a_lo,
-                                           const unsigned char *a_hi, const uint4 *__restrict__ sw,
-                                           const uint32_t *__restrict__ so, int i0, int i1) {
+__device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo, uint32_t a_hi,
+                                           uint32_t sw, uint32_t so, int i0, int i1) {
+    uint32_t wa = sw + (uint32_t)i0 * 16, oa = so + (uint32_t)i0 * 4;
+    const uint32_t wend = sw + (uint32_t)i1 * 16;
 #pragma unroll 2
-    for (int i = i0; i < i1; i++) {
-        const uint4 w = sw[i];
-        const uint32_t off = so[i];
-        const uint4 x = *(const uint4 *)(a_lo + off);
-        const uint4 y = *(const uint4 *)(a_hi + off);
+    for (; wa < wend; wa += 16, oa += 4) {
+        const uint4 w = lds128(wa);
+        const uint32_t off = lds32(oa);
+        const uint4 x = lds128(a_lo + off);
+        const uint4 y = lds128(a_hi + off);
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -220,11 +236,11 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
                 for (int j = 0; j < 4; j++) { accp[i][j] = 0; accn[i][j] = 0; }
         }
         {
-            const unsigned char *stage = smem + (size_t)(s & 1) * pr.stage_bytes;
-            const unsigned char *a_lo = stage + lane_off[0], *a_hi = stage + lane_off[1];
-            const uint4 *swl = (const uint4 *)(stage + sw_off) + ql * pr.SL;
-            const uint32_t *sol = (const uint32_t *)(stage + so_off) + ql * pr.SL;
-            const uint16_t *sbl = (const uint16_t *)(stage + sb_off) + ql * 24;
+            const uint32_t stage = smem_base + (uint32_t)(s & 1) * pr.stage_bytes;
+            const uint32_t a_lo = stage + lane_off[0], a_hi = stage + lane_off[1];
+            const uint32_t swl = stage + sw_off + (uint32_t)ql * pr.SL * 16;
+            const uint32_t sol = stage + so_off + (uint32_t)ql * pr.SL * 4;
+            const uint16_t *sbl = (const uint16_t *)(smem + (size_t)(s & 1) * pr.stage_bytes + sb_off) + ql * 24;
             // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
             const int mybeg = lane < 17 ? (int)sbl[lane] : 0;
 #define GEO_BUCKET(B) \

@@ -15,6 +15,7 @@
 //     dgamma = sum g * xhat,  dbeta = sum g,  dx = gamma * invstd * (g - dbeta/N - xhat * dgamma/N)
 // (in evaluation mode dx = gamma * invstd * g).  Layout: x [B][C][HW] (HW = 1 for the 1d variant).
 #include "sc_common.h"
+#include "sc_pool.h"
 
 namespace geo {
 
@@ -45,9 +46,10 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 // mode 0: sum(x)   mode 1: sum((x - mean)^2)   -> partial[c][s]
 // VEC: rows of HW floats are read as float4 (HW % 4 == 0, 16-byte aligned base).
 template <int MODE, bool VEC>
-__global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnDims d, const float *__restrict__ x,
+__global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnDims d, XSource xs,
                                                                const float *__restrict__ mean,
                                                                float *__restrict__ partial) {
+    const float *x = (const float *)xs.p;   // scalar path: fp32 only
     __shared__ float red[32];
     const int c = blockIdx.x, s = blockIdx.y;
     const int b0 = (int)((long long)d.B * s / d.S), b1 = (int)((long long)d.B * (s + 1) / d.S);
@@ -58,7 +60,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnDims d, const f
         float a1 = 0.f, a2 = 0.f, a3 = 0.f;
         for (unsigned i = threadIdx.x; i < n; i += BN_THREADS) {
             const unsigned b = b0 + i / q, p = i % q;
-            const float4 v = __ldg((const float4 *)(x + ((size_t)b * d.C + c) * d.HW) + p);
+            const float4 v = load_x4(xs, (((size_t)b * d.C + c) * d.HW >> 2) + p);
             if (MODE == 0) { acc += v.x; a1 += v.y; a2 += v.z; a3 += v.w; }
             else {
                 acc = fmaf(v.x - mu, v.x - mu, acc); a1 = fmaf(v.y - mu, v.y - mu, a1);
@@ -274,19 +276,18 @@ struct PoolWin {
     float4 t, b;       // the two input rows
     float v0, v1;      // pooled values before the clamp
 };
-__device__ __forceinline__ PoolWin load_windows(const float *__restrict__ x, unsigned r, unsigned j, unsigned W, float w,
-                                                float bq) {
+__device__ __forceinline__ PoolWin load_windows(const XSource &xs, unsigned r, unsigned j, unsigned W, float w, float bq) {
     PoolWin p;
-    p.t = __ldg((const float4 *)(x + (size_t)(2 * r) * W) + j);
-    p.b = __ldg((const float4 *)(x + (size_t)(2 * r + 1) * W) + j);
+    p.t = load_x4(xs, ((size_t)(2 * r) * W >> 2) + j);
+    p.b = load_x4(xs, ((size_t)(2 * r + 1) * W >> 2) + j);
     // same expressions as bn_apply_kernel and pool_act_fwd_kernel, so the value equals their composition
-    p.v0 = ((p.t.x * w + bq) + (p.t.y * w + bq) + (p.b.x * w + bq) + (p.b.y * w + bq)) / 4.0f;
-    p.v1 = ((p.t.z * w + bq) + (p.t.w * w + bq) + (p.b.z * w + bq) + (p.b.w * w + bq)) / 4.0f;
+    p.v0 = pooled_value(p.t.x, p.t.y, p.b.x, p.b.y, w, bq);
+    p.v1 = pooled_value(p.t.z, p.t.w, p.b.z, p.b.w, w, bq);
     return p;
 }
 
 __global__ void __launch_bounds__(BN_THREADS) bn_pool_apply_kernel(unsigned rows, unsigned W, unsigned Ho, unsigned C,
-                                                                   const float *__restrict__ x,
+                                                                   XSource x,
                                                                    const float *__restrict__ wq,
                                                                    const float *__restrict__ bq, float *__restrict__ out) {
     const unsigned q = W >> 2, total = rows * q;
@@ -299,7 +300,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_pool_apply_kernel(unsigned rows
 
 // partial sums of gy and gy * xhat, gy = gradient reaching the batch-norm output
 __global__ void __launch_bounds__(BN_THREADS) bn_pool_bwd_reduce_kernel(BnDims d, unsigned W, unsigned Ho,
-                                                                        const float *__restrict__ x,
+                                                                        XSource x,
                                                                         const float *__restrict__ g,
                                                                         const float *__restrict__ mean,
                                                                         const float *__restrict__ invstd,
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_pool_bwd_reduce_kernel(BnDims d
 }
 
 __global__ void __launch_bounds__(BN_THREADS) bn_pool_bwd_apply_kernel(BnDims d, unsigned rows, unsigned W, unsigned Ho,
-                                                                       int training, const float *__restrict__ x,
+                                                                       int training, XSource x,
                                                                        const float *__restrict__ g,
                                                                        const float *__restrict__ mean,
                                                                        const float *__restrict__ invstd,
@@ -412,11 +413,12 @@ int geo_sc_bn_fixed_forward(int batch, int channels, int spatial, int training, 
     float *bq = wq + channels;
     const bool vec = spatial % 4 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
     if (training) {
-        if (vec) bn_reduce_kernel<0, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
-        else bn_reduce_kernel<0, false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
+        const XSource xs = {x, 1.0f, 0};
+        if (vec) bn_reduce_kernel<0, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, xs, nullptr, partial);
+        else bn_reduce_kernel<0, false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, xs, nullptr, partial);
         bn_mean_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, save_mean);
-        if (vec) bn_reduce_kernel<1, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
-        else bn_reduce_kernel<1, false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
+        if (vec) bn_reduce_kernel<1, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, xs, save_mean, partial);
+        else bn_reduce_kernel<1, false><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, xs, save_mean, partial);
     }
     bn_fold_kernel<<<1, BN_THREADS, 0, s>>>(d, training, eps, momentum, partial, save_mean, save_invstd, weight, bias,
                                             running_mean, running_var, wq, bq, scale_out);
@@ -462,31 +464,67 @@ static int bn_pool_check(int batch, int channels, int height, int width, const v
     return GEO_SC_OK;
 }
 
-int geo_sc_bn_pool_act_forward(int batch, int channels, int height, int width, int training, float eps, float momentum,
-                               const float *x, const float *weight, const float *bias, float *running_mean,
-                               float *running_var, float *out, float *save_mean, float *save_invstd, float *save_wq,
-                               float *save_bq, float *scale_out, void *scratch, size_t scratch_bytes, void *stream) {
-    if (!x || !out || !save_mean || !save_invstd || !save_wq || !save_bq || !scale_out || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
+// Statistics and folded scale / shift of the pooled forms; x as fp32 or as bit counts.
+static int bn_pool_stats(int batch, int channels, int height, int width, int training, float eps, float momentum, XSource xs,
+                         const float *weight, const float *bias, float *running_mean, float *running_var, float *save_mean,
+                         float *save_invstd, float *save_wq, float *save_bq, float *scale_out, void *scratch,
+                         size_t scratch_bytes, cudaStream_t s) {
+    if (!xs.p || !save_mean || !save_invstd || !save_wq || !save_bq || !scale_out || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
     if (!training && (!running_mean || !running_var)) return fail(GEO_SC_ERR_NULL, "evaluation mode needs running statistics");
-    int rc = bn_pool_check(batch, channels, height, width, x, out, x);
+    size_t need = 0;
+    geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
+    if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+    BnDims d = {batch, channels, height * width, bn_slices(batch, channels)};
+    float *partial = (float *)scratch;
+    if (training) {
+        bn_reduce_kernel<0, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, xs, nullptr, partial);
+        bn_mean_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, save_mean);
+        bn_reduce_kernel<1, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, xs, save_mean, partial);
+    }
+    bn_fold_kernel<<<1, BN_THREADS, 0, s>>>(d, training, eps, momentum, partial, save_mean, save_invstd, weight, bias,
+                                            running_mean, running_var, save_wq, save_bq, scale_out);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+static int bn_pool_backward(int batch, int channels, int height, int width, int training, XSource xs, const float *grad_out,
+                            const float *weight, const float *save_mean, const float *save_invstd, const float *save_wq,
+                            const float *save_bq, float *grad_x, float *grad_weight, float *grad_bias, void *scratch,
+                            size_t scratch_bytes, cudaStream_t s) {
+    if (!xs.p || !grad_out || !save_mean || !save_invstd || !save_wq || !save_bq || !grad_x || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
+    int rc = bn_pool_check(batch, channels, height, width, xs.p, grad_out, grad_x);
     if (rc) return rc;
     size_t need = 0;
     geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
     if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
-    cudaStream_t s = (cudaStream_t)stream;
-    const int spatial = height * width;
-    BnDims d = {batch, channels, spatial, bn_slices(batch, channels)};
+    BnDims d = {batch, channels, height * width, bn_slices(batch, channels)};
     float *partial = (float *)scratch;
-    if (training) {
-        bn_reduce_kernel<0, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, nullptr, partial);
-        bn_mean_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, save_mean);
-        bn_reduce_kernel<1, true><<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, x, save_mean, partial);
-    }
-    bn_fold_kernel<<<1, BN_THREADS, 0, s>>>(d, training, eps, momentum, partial, save_mean, save_invstd, weight, bias,
-                                            running_mean, running_var, save_wq, save_bq, scale_out);
+    float *sums = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
+    const unsigned W = (unsigned)width, Ho = (unsigned)(height / 2);
+    bn_pool_bwd_reduce_kernel<<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, W, Ho, xs, grad_out, save_mean, save_invstd, save_wq, save_bq, partial);
+    bn_bwd_final_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, sums, grad_weight, grad_bias);
+    const unsigned rows = (unsigned)batch * channels * Ho;
+    bn_pool_bwd_apply_kernel<<<bn_grid((long long)rows * (width / 4)), BN_THREADS, 0, s>>>(d, rows, W, Ho, training, xs, grad_out, save_mean,
+                                                                                      save_invstd, weight, sums, save_wq, save_bq, grad_x);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int geo_sc_bn_pool_act_forward(int batch, int channels, int height, int width, int training, float eps, float momentum,
+                               const float *x, const float *weight, const float *bias, float *running_mean,
+                               float *running_var, float *out, float *save_mean, float *save_invstd, float *save_wq,
+                               float *save_bq, float *scale_out, void *scratch, size_t scratch_bytes, void *stream) {
+    if (!out) return fail(GEO_SC_ERR_NULL, "out is NULL");
+    int rc = bn_pool_check(batch, channels, height, width, x, out, x);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const XSource xs = {x, 1.0f, 0};
+    rc = bn_pool_stats(batch, channels, height, width, training, eps, momentum, xs, weight, bias, running_mean, running_var,
+                       save_mean, save_invstd, save_wq, save_bq, scale_out, scratch, scratch_bytes, s);
+    if (rc) return rc;
     const unsigned rows = (unsigned)batch * channels * (height / 2);
     bn_pool_apply_kernel<<<bn_grid((long long)rows * (width / 4)), BN_THREADS, 0, s>>>(rows, (unsigned)width, (unsigned)(height / 2),
-                                                                                  (unsigned)channels, x, save_wq, save_bq, out);
+                                                                                  (unsigned)channels, xs, save_wq, save_bq, out);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -495,24 +533,43 @@ int geo_sc_bn_pool_act_backward(int batch, int channels, int height, int width, 
                                 const float *grad_out, const float *weight, const float *save_mean,
                                 const float *save_invstd, const float *save_wq, const float *save_bq, float *grad_x,
                                 float *grad_weight, float *grad_bias, void *scratch, size_t scratch_bytes, void *stream) {
-    if (!x || !grad_out || !save_mean || !save_invstd || !save_wq || !save_bq || !grad_x || !scratch) return fail(GEO_SC_ERR_NULL, "a required pointer is NULL");
-    int rc = bn_pool_check(batch, channels, height, width, x, grad_out, grad_x);
+    const XSource xs = {x, 1.0f, 0};
+    return bn_pool_backward(batch, channels, height, width, training, xs, grad_out, weight, save_mean, save_invstd, save_wq,
+                            save_bq, grad_x, grad_weight, grad_bias, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+int geo_sc_epilogue_forward(const geo_sc_conv_desc *next_desc, int in_bit_length, int prec, int training, float eps,
+                            float momentum, const int32_t *counts, const float *weight, const float *bias,
+                            float *running_mean, float *running_var, float *act_out, float *save_mean, float *save_invstd,
+                            float *save_wq, float *save_bq, float *scale_out, void *astream, size_t astream_bytes,
+                            void *scratch, size_t scratch_bytes, void *stream) {
+    Geometry g;
+    int rc = make_geometry(next_desc, &g);
     if (rc) return rc;
-    size_t need = 0;
-    geo_sc_bn_fixed_scratch_bytes(batch, channels, &need);
-    if (scratch_bytes < need || ((uintptr_t)scratch & 255)) return fail(GEO_SC_ERR_WORKSPACE, "bn scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+    if (in_bit_length < 1 || (in_bit_length & (in_bit_length - 1))) return fail(GEO_SC_ERR_BIT_LENGTH, "bit length %d of the counts is not a power of two", in_bit_length);
+    if (prec < 0 || prec > 23) return fail(GEO_SC_ERR_SHAPE, "prec %d outside 0..23", prec);
+    if (g.generator != GEO_SC_GEN_LFSR) return fail(GEO_SC_ERR_UNSUPPORTED, "the fused epilogue generates LFSR streams only");
+    if (!act_out || !astream) return fail(GEO_SC_ERR_NULL, "act_out or astream is NULL");
+    const int height = 2 * g.H, width = 2 * g.W;
+    if ((rc = bn_pool_check(g.B, g.C, height, width, counts, act_out, counts))) return rc;
+    const size_t need = align_up(g.act_stream_words * 4, 256);
+    if (astream_bytes < need || ((uintptr_t)astream & 255)) return fail(GEO_SC_ERR_WORKSPACE, "activation-stream buffer holds %zu bytes, %zu needed (256-byte aligned)", astream_bytes, need);
     cudaStream_t s = (cudaStream_t)stream;
-    BnDims d = {batch, channels, height * width, bn_slices(batch, channels)};
-    float *partial = (float *)scratch;
-    float *sums = (float *)((char *)scratch + align_up((size_t)channels * 64 * 2 * sizeof(float), 256));
-    const unsigned W = (unsigned)width, Ho = (unsigned)(height / 2);
-    bn_pool_bwd_reduce_kernel<<<dim3(channels, d.S), BN_THREADS, 0, s>>>(d, W, Ho, x, grad_out, save_mean, save_invstd, save_wq, save_bq, partial);
-    bn_bwd_final_kernel<<<(channels + BN_THREADS - 1) / BN_THREADS, BN_THREADS, 0, s>>>(d, partial, sums, grad_weight, grad_bias);
-    const unsigned rows = (unsigned)batch * channels * Ho;
-    bn_pool_bwd_apply_kernel<<<bn_grid((long long)rows * (width / 4)), BN_THREADS, 0, s>>>(d, rows, W, Ho, training, x, grad_out, save_mean,
-                                                                                      save_invstd, weight, sums, save_wq, save_bq, grad_x);
-    GEO_CUDA_CHECK(cudaGetLastError());
-    return GEO_SC_OK;
+    const XSource xs = {counts, 1.0f / (float)in_bit_length, 1};
+    rc = bn_pool_stats(g.B, g.C, height, width, training, eps, momentum, xs, weight, bias, running_mean, running_var, save_mean,
+                       save_invstd, save_wq, save_bq, scale_out, scratch, scratch_bytes, s);
+    if (rc) return rc;
+    return launch_epilogue_streams(g, xs, save_wq, save_bq, prec, act_out, (uint32_t *)astream, s);
+}
+
+int geo_sc_epilogue_backward(int batch, int channels, int height, int width, int in_bit_length, int training,
+                             const int32_t *counts, const float *grad_out, const float *weight, const float *save_mean,
+                             const float *save_invstd, const float *save_wq, const float *save_bq, float *grad_x,
+                             float *grad_weight, float *grad_bias, void *scratch, size_t scratch_bytes, void *stream) {
+    if (in_bit_length < 1 || (in_bit_length & (in_bit_length - 1))) return fail(GEO_SC_ERR_BIT_LENGTH, "bit length %d of the counts is not a power of two", in_bit_length);
+    const XSource xs = {counts, 1.0f / (float)in_bit_length, 1};
+    return bn_pool_backward(batch, channels, height, width, training, xs, grad_out, weight, save_mean, save_invstd, save_wq,
+                            save_bq, grad_x, grad_weight, grad_bias, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -61,6 +61,12 @@ int ensure_tables();
 int launch_prepare_weights(const Geometry &g, const float *w, uint32_t *wstream, int32_t *aoff, cudaStream_t s);
 int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, cudaStream_t s);
 
+// Fused layer epilogue (sc_streams.cu): bit counts of one layer -> batch norm (folded scale / shift) -> 2x2 average
+// pool -> hardtanh(0, 1) -> fixed-point rounding -> packed activation streams of the next layer `g`.
+struct XSource;
+int launch_epilogue_streams(const Geometry &g, const XSource &xs, const float *wq, const float *bq, int prec, float *act_out,
+                            uint32_t *astream, cudaStream_t s);
+
 // Accumulation (sc_accumulate.cu)
 int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t *wstream, const int32_t *aoff,
                       int32_t *out, cudaStream_t s);

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "sc_common.h"
+#include "sc_pool.h"
 
 namespace geo {
 
@@ -236,6 +237,54 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
     }
 }
 
+// ---- fused layer epilogue ---------------------------------------------------------------------
+// What lies between two SC layers of the reference (network.py:165-184, utils_class.py:32-33,37-65), from the
+// bit counts of one layer to the packed streams of the next in one pass: x = counts / L, batch norm with the
+// folded 7-bit scale and shift, 2x2 average pool, hardtanh(0, 1), fixed-point rounding of the activation
+// (utils_functional.py:33-39), float -> level (sc_cuda.cpp:50-51) and the stream words of every pack, written
+// into the next layer's padded stream image [batch][pack][c][Hp][Wp] (whose border the launcher has zeroed).
+// The rounded activation is also written as fp32: the backward pass of the next layer reads it.
+// A thread owns two horizontally adjacent pooled values = one 16-byte load from each of two input rows.
+// `gp` describes the NEXT layer: C, H, W are the pooled tensor's dimensions.
+__global__ void __launch_bounds__(256) epilogue_streams_kernel(GenParams gp, LoadPlan plan, XSource xs,
+                                                               const float *__restrict__ wq, const float *__restrict__ bq,
+                                                               float qlevels, float qinv, float *__restrict__ act_out,
+                                                               uint32_t *__restrict__ as) {
+    extern __shared__ uint32_t smem[];
+    uint32_t *s_pat = smem;
+    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RWS);
+    load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
+
+    const unsigned Wx = 2u * (unsigned)gp.W;                 // width of the counts
+    const unsigned q = Wx >> 2, rows = (unsigned)gp.B * gp.C * gp.H, total = rows * q;
+    const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
+    const float fL = (float)gp.L;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned r = i / q, j = i % q;                 // r = (b * C + c) * H + oy
+        const unsigned oy = r % (unsigned)gp.H, bc = r / (unsigned)gp.H;
+        const unsigned c = bc % (unsigned)gp.C, b = bc / (unsigned)gp.C;
+        const float w = wq[c], sh = bq[c];
+        const float4 t = load_x4(xs, ((size_t)(2 * r) * Wx >> 2) + j);
+        const float4 u = load_x4(xs, ((size_t)(2 * r + 1) * Wx >> 2) + j);
+        float v[2] = {pooled_value(t.x, t.y, u.x, u.y, w, sh), pooled_value(t.z, t.w, u.z, u.w, w, sh)};
+#pragma unroll
+        for (int e = 0; e < 2; e++) v[e] = quantize_value(fminf(fmaxf(v[e], 0.0f), 1.0f), qlevels, qinv);
+        ((float2 *)(act_out + (size_t)r * gp.W))[j] = make_float2(v[0], v[1]);
+        const int cc = gp.mode == GEO_SC_MODE_YZ ? (int)c % gp.z : (int)c;
+        const unsigned y = oy + (unsigned)gp.pad_h;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const unsigned x = 2 * j + e + (unsigned)gp.pad_w;
+            const int V = (int)ceilf(fminf(fmaxf(v[e] * fL, 0.0f), fL - 1.0f));
+            const unsigned sidx = (unsigned)((cc * gp.Hp + (int)y) * gp.Wp + (int)x);
+            const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
+            uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + y * (unsigned)gp.Wp + x;
+            for (int p = 0; p < gp.P; p++)
+                dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+        }
+    }
+}
+
 // ---- "accurate" generator ---------------------------------------------------------------------------
 // Sampling without replacement (utils_functional.py:157-176): with cur ones still to place and L - k bits
 // left, bit k is one when cur * L / (L - k) exceeds a uniform integer below L -- so a stream of level V
@@ -360,6 +409,23 @@ int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, c
     if (g.generator == GEO_SC_GEN_ACC) act_streams_acc_kernel<false><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
     else if (g.generator == GEO_SC_GEN_RAND) act_streams_acc_kernel<true><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
     else act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+int launch_epilogue_streams(const Geometry &g, const XSource &xs, const float *wq, const float *bq, int prec, float *act_out,
+                            uint32_t *astream, cudaStream_t s) {
+    int rc = ensure_tables();
+    if (rc) return rc;
+    GenParams gp = gen_params(g);
+    LoadPlan plan;
+    make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
+    const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
+    // the kernel writes the interior of every padded image; the border holds the all-zero streams of level 0
+    if (g.pad_h || g.pad_w) GEO_CUDA_CHECK(cudaMemsetAsync(astream, 0, g.act_stream_words * 4, s));
+    const long long total = (long long)g.B * g.C * g.H * (g.W / 2);
+    const float levels = (float)(1 << prec);
+    epilogue_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, xs, wq, bq, levels, 1.0f / levels, act_out, astream);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

@@ -59,22 +59,10 @@ def _pair(v):
     return int(v), int(v)
 
 
-def conv2d_generic(activation, weight, padding, stride, **kwargs):
-    """SC conv2d with a float guide for back-propagation (utils_functional.py:406-634).
-
-    Keyword arguments (defaults as in the reference): ``bit_length`` 128, ``prec`` 128,
-    ``share`` True, ``generator`` None, ``forward`` 'full_or', ``legacy`` False, ``load_unit`` 8,
-    ``load_wait_w`` 1, ``load_wait_a`` 1, ``z_unit`` 1024.  One extension over the reference:
-    ``quantized`` (default False) promises that both operands went through :func:`quantize` with
-    ``prec`` <= 8, which lets the backward pass run on the tensor-core kernels alone; ``weight_cache``
-    (default None) is a dict in which the packed weight streams are kept between calls -- the caller
-    empties it when the weights change.
-
-    ``padding`` follows the reference's convention ``F.pad(x, (p[0], p[0], p[1], p[1]))``: the
-    last dimension is padded by ``padding[0]``, dimension 2 by ``padding[1]``
-    (utils_functional.py:492-516).  The value returned is the SC bit count divided by
-    ``bit_length``; its gradient is the gradient of the guide.
-    """
+def resolve_sc_arguments(padding, stride, kwargs):
+    """The keyword arguments of :func:`conv2d_generic` turned into the native descriptor's fields, with the
+    reference's defaults and the rules of utils_functional.py:489-516 (padding order, which modes take loading
+    arguments, full_or ignoring the generator); raises for what only the bit-serial simulation provides."""
     bit_length = kwargs.get("bit_length", 128)
     generator = kwargs.get("generator", None)
     forward = kwargs.get("forward", "full_or")
@@ -110,12 +98,37 @@ def conv2d_generic(activation, weight, padding, stride, **kwargs):
         load_unit, load_wait_w, load_wait_a = 8, 1, 1
     elif forward in ("1d_bin", "z_bin"):
         load_wait_a = load_wait_w  # one load_wait for both operands (sc_cuda.cpp:47-63)
-    return sc_conv2d_with_guide(activation, weight, int(bit_length), forward, pad_h=p1, pad_w=p0,
-                                z_unit=int(z_unit), total_width=prec_default, load_width=int(load_unit),
-                                load_wait_w=int(load_wait_w), load_wait_a=int(load_wait_a),
+    return dict(bit_length=int(bit_length), mode=forward, pad_h=p1, pad_w=p0, z_unit=int(z_unit),
+                total_width=prec_default, load_width=int(load_unit), load_wait_w=int(load_wait_w),
+                load_wait_a=int(load_wait_a), generator=gen)
+
+
+def conv2d_generic(activation, weight, padding, stride, **kwargs):
+    """SC conv2d with a float guide for back-propagation (utils_functional.py:406-634).
+
+    Keyword arguments (defaults as in the reference): ``bit_length`` 128, ``prec`` 128,
+    ``share`` True, ``generator`` None, ``forward`` 'full_or', ``legacy`` False, ``load_unit`` 8,
+    ``load_wait_w`` 1, ``load_wait_a`` 1, ``z_unit`` 1024.  One extension over the reference:
+    ``quantized`` (default False) promises that both operands went through :func:`quantize` with
+    ``prec`` <= 8, which lets the backward pass run on the tensor-core kernels alone; ``weight_cache``
+    (default None) is a dict in which the packed weight streams are kept between calls -- the caller
+    empties it when the weights change; ``astreams`` (default None) are the packed activation streams of
+    ``activation`` for this very call, when the fused epilogue of the previous layer has made them.
+
+    ``padding`` follows the reference's convention ``F.pad(x, (p[0], p[0], p[1], p[1]))``: the
+    last dimension is padded by ``padding[0]``, dimension 2 by ``padding[1]``
+    (utils_functional.py:492-516).  The value returned is the SC bit count divided by
+    ``bit_length``; its gradient is the gradient of the guide.
+    """
+    r = resolve_sc_arguments(padding, stride, kwargs)
+    gen = r["generator"]
+    return sc_conv2d_with_guide(activation, weight, r["bit_length"], r["mode"], pad_h=r["pad_h"], pad_w=r["pad_w"],
+                                z_unit=r["z_unit"], total_width=r["total_width"], load_width=r["load_width"],
+                                load_wait_w=r["load_wait_w"], load_wait_a=r["load_wait_a"],
                                 quantized=bool(kwargs.get("quantized", False)),
                                 weight_cache=kwargs.get("weight_cache", None) if gen == "lfsr" else None,
-                                generator=gen, seed=int(kwargs["seed"]) if "seed" in kwargs else _next_seed(gen))
+                                generator=gen, seed=int(kwargs["seed"]) if "seed" in kwargs else _next_seed(gen),
+                                astreams=kwargs.get("astreams", None) if gen == "lfsr" else None)
 
 
 def linear_generic(activation, weight, **kwargs):

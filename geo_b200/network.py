@@ -56,23 +56,29 @@ class CONV_tiny_add_partial(nn.Module):
                 conv.weight_org *= 2
                 conv.weight.data *= 2
 
-    def _sc(self, conv, x, i):
+    def _sc_kwargs(self, i):
         # The last layer takes its weight load_wait from entry 2 and its activation load_wait from
         # entry 3 (network.py:186); kept so that per-layer settings mean the same thing.
         wait_w = self.load_wait[2] if i == 3 else self.load_wait[i]
-        return conv(x, err=self.err[i], forward=self.compute, generator=self.generator, z_unit=2 ** self.z_unit[i],
-                    legacy=self.legacy, load_unit=self.load_unit[i], load_wait_w=wait_w,
-                    load_wait_a=self.load_wait[i])
+        return dict(err=self.err[i], forward=self.compute, generator=self.generator, z_unit=2 ** self.z_unit[i],
+                    legacy=self.legacy, load_unit=self.load_unit[i], load_wait_w=wait_w, load_wait_a=self.load_wait[i])
+
+    def _sc(self, conv, x, i, astreams=None):
+        return conv(x, astreams=astreams, **self._sc_kwargs(i))
 
     def forward(self, x_in, target=None):
-        x = x_in
+        x, streams = x_in, None
+        convs = (self.conv1, self.conv2, self.conv3, self.fc1)
         for i, (conv, bn) in enumerate(((self.conv1, self.bn1), (self.conv2, self.bn2), (self.conv3, self.bn3))):
-            x = self._sc(conv, x, i)
             if self.relu:
-                x = self.tanh(self.pool(F.relu(bn(x))))
+                x = self.tanh(self.pool(F.relu(bn(self._sc(conv, x, i, streams)))))
+                streams = None
             else:
-                x = layers.bn_pool_hardtanh(bn, x)   # tanh(pool(bn(x))), one pass where the shape allows
-        x = self._sc(self.fc1, x, 3).view(-1, self.num_classes)
+                # tanh(pool(bn(conv(x)))) and the next layer's input rounding and stream generation, one pass
+                # from bit counts to streams where the shapes allow
+                x, streams = layers.sc_block(conv, bn, x, self._sc_kwargs(i), convs[i + 1], self._sc_kwargs(i + 1),
+                                             astreams=streams)
+        x = self._sc(self.fc1, x, 3, streams).view(-1, self.num_classes)
         return self.bn4(x)  # BN at the output stabilises training (network.py:188-189)
 
 
@@ -111,18 +117,27 @@ class VGG11_add_partial(nn.Module):
         self.compute = sc_compute
         self.legacy = legacy
 
-    def _sc(self, conv, x, i):
+    def _sc_kwargs(self, i):
         err, zu = _per_layer(self.err, i + 1)[i], _per_layer(self.z_unit, i + 1)[i]
         lu, lw = _per_layer(self.load_unit, i + 1)[i], _per_layer(self.load_wait, i + 1)[i]
-        return conv(x, err=err, forward=self.compute, generator=self.generator, z_unit=2 ** zu, legacy=self.legacy,
+        return dict(err=err, forward=self.compute, generator=self.generator, z_unit=2 ** zu, legacy=self.legacy,
                     load_unit=lu, load_wait_w=lw, load_wait_a=lw)
 
+    def _sc(self, conv, x, i, astreams=None):
+        return conv(x, astreams=astreams, **self._sc_kwargs(i))
+
     def forward(self, x, target=None):
+        streams = None
+        sc_layers = list(self.convs) + [self.fc1]
         for i, (conv, bn) in enumerate(zip(self.convs, self.bns)):
-            x = self._sc(conv, x, i)
-            x = layers.bn_pool_hardtanh(bn, x) if i in self.POOL_AFTER else self.tanh(bn(x))
+            if i in self.POOL_AFTER:
+                x, streams = layers.sc_block(conv, bn, x, self._sc_kwargs(i), sc_layers[i + 1], self._sc_kwargs(i + 1),
+                                             astreams=streams)
+            else:
+                x = self.tanh(bn(self._sc(conv, x, i, streams)))
+                streams = None
         n = len(self.convs)
-        x = self.tanh(self.bnf1(self._sc(self.fc1, x, n)))
+        x = self.tanh(self.bnf1(self._sc(self.fc1, x, n, streams)))
         x = self.tanh(self.bnf2(self._sc(self.fc2, x, n + 1)))
         x = self._sc(self.fc3, x, n + 2).view(-1, self.num_classes)
         return self.bn_out(x)

@@ -93,14 +93,17 @@ def sc_conv2d(act, weight, bit_length, mode="1d_bin", padding=(0, 0), workspace=
     return out
 
 
-def sc_conv2d_staged(act, weight, bit_length, mode="1d_bin", padding=(0, 0), wprep=None, **kw):
+def sc_conv2d_staged(act, weight, bit_length, mode="1d_bin", padding=(0, 0), wprep=None, astreams=None, **kw):
     """Same result as :func:`sc_conv2d` through the three stage entry points; ``wprep`` may hold
-    weight streams prepared earlier for the same weights and descriptor geometry."""
+    weight streams prepared earlier for the same weights and descriptor geometry, ``astreams`` the
+    activation streams of ``act`` for this descriptor (the fused layer epilogue of the previous layer
+    produces them)."""
     _require_cuda(act, weight)
     d = desc_for(act, weight, bit_length, mode, padding, **kw)
     if wprep is None:
         wprep = prepare_weights(weight, d)
-    astreams = generate_act_streams(act, d)
+    if astreams is None:
+        astreams = generate_act_streams(act, d)
     if STATS.profile:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(torch.cuda.current_stream(act.device))
@@ -393,3 +396,55 @@ def measure_lop3_peak():
     rate, ms = ctypes.c_double(0), ctypes.c_double(0)
     check(_lib.lib().geo_sc_measure_lop3_peak(ctypes.byref(rate), ctypes.byref(ms)), "geo_sc_measure_lop3_peak")
     return rate.value, ms.value
+
+
+def epilogue_forward(counts, in_bit_length, next_desc, weight, bias, running_mean, running_var, training, momentum, eps,
+                     prec=7):
+    """Bit counts of one SC layer -> the next layer's rounded activation and packed streams in one pass (batch norm
+    with folded 7-bit scale / shift, 2x2 average pool, hardtanh(0, 1), rounding, stream generation).
+    ``next_desc`` describes the next layer (its input is the pooled tensor).
+    Returns (activation, streams, save_mean, save_invstd, scale, w_q, b_q)."""
+    _require_cuda(counts)
+    c = counts.contiguous()
+    if c.dtype != torch.int32:
+        raise TypeError(f"counts must be int32, got {c.dtype}")
+    B, C, H, W = c.shape
+    if (B, C, H, W) != (next_desc.batch, next_desc.c_in, 2 * next_desc.h_in, 2 * next_desc.w_in):
+        raise ValueError(f"counts {tuple(c.shape)} do not pool to the next layer's input "
+                         f"({next_desc.batch}, {next_desc.c_in}, {next_desc.h_in}, {next_desc.w_in})")
+    dev = c.device
+    nbytes = _lib.size_query("geo_sc_act_stream_bytes", next_desc)
+    with torch.cuda.device(dev):
+        act = torch.empty((B, C, H // 2, W // 2), dtype=torch.float32, device=dev)
+        streams = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        stats = torch.empty((4, C), dtype=torch.float32, device=dev)     # mean, invstd, w_q, b_q
+        scale = torch.empty(1, dtype=torch.float32, device=dev)
+        scratch = _bn_scratch(B, C, dev)
+        check(_lib.lib().geo_sc_epilogue_forward(
+            ctypes.byref(next_desc), int(in_bit_length), int(prec), int(bool(training)), float(eps), float(momentum),
+            c.data_ptr(), _ptr(weight), _ptr(bias), _ptr(running_mean), _ptr(running_var), act.data_ptr(),
+            stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(), stats[3].data_ptr(), scale.data_ptr(),
+            streams.data_ptr(), nbytes, scratch.data_ptr(), scratch.numel(), _stream_ptr(dev)), "geo_sc_epilogue_forward")
+    STATS.launches += (6 if training else 3)
+    return act, streams, stats[0], stats[1], scale, stats[2], stats[3]
+
+
+def epilogue_backward(counts, in_bit_length, grad_out, weight, mean, invstd, wq, bq, training, need_affine=True):
+    """Gradient of :func:`epilogue_forward` with respect to the layer's value counts / bit_length and the batch-norm
+    affine parameters -> (grad_x, grad_weight, grad_bias)."""
+    _require_cuda(counts, grad_out)
+    c = counts.contiguous()
+    go = grad_out.detach().to(torch.float32).contiguous()
+    B, C, H, W = c.shape
+    dev = c.device
+    with torch.cuda.device(dev):
+        gx = torch.empty((B, C, H, W), dtype=torch.float32, device=dev)
+        gw = torch.empty(C, dtype=torch.float32, device=dev) if need_affine else None
+        gb = torch.empty(C, dtype=torch.float32, device=dev) if need_affine else None
+        scratch = _bn_scratch(B, C, dev)
+        check(_lib.lib().geo_sc_epilogue_backward(
+            B, C, H, W, int(in_bit_length), int(bool(training)), c.data_ptr(), go.data_ptr(), _ptr(weight), mean.data_ptr(),
+            invstd.data_ptr(), wq.data_ptr(), bq.data_ptr(), gx.data_ptr(), _ptr(gw), _ptr(gb), scratch.data_ptr(),
+            scratch.numel(), _stream_ptr(dev)), "geo_sc_epilogue_backward")
+    STATS.launches += 3
+    return gx, gw, gb

@@ -271,6 +271,33 @@ int geo_sc_bn_pool_act_backward(int batch, int channels, int height, int width, 
                                 float *grad_weight_device, float *grad_bias_device, void *scratch_device,
                                 size_t scratch_bytes, void *stream);
 
+/* ---- from the bit counts of one SC layer to the packed streams of the next, one pass ---------------------
+ * Replaces the whole chain the reference runs between two SC layers (network.py:165-184): result / bit_length
+ * (utils_functional.py:632-634) -> BatchNorm2d_fixed (utils_class.py:37-65) -> nn.AvgPool2d(2) -> nn.Hardtanh(0, 1)
+ * -> quantize of the next layer's input (utils_class.py:32, utils_functional.py:33-39) -> float -> level and stream
+ * generation of the next layer (sc_cuda.cpp:50-51, sc_cuda_kernel.cu:667-691).  next_desc describes the NEXT layer:
+ * its batch, c_in, h_in, w_in are the pooled tensor, counts is int32 [batch][c_in][2*h_in][2*w_in] (w_in even,
+ * counts 16-byte aligned); in_bit_length is the stream length the counts were produced with; prec the fractional
+ * bits of the rounding (the reference uses 7).  The batch-norm statistics are taken over counts / in_bit_length
+ * exactly as geo_sc_bn_pool_act_forward takes them over x, so every output equals what the separate entry points
+ * (geo_sc_counts_to_float, geo_sc_bn_pool_act_forward, geo_sc_quantize, geo_sc_generate_act_streams) give, bit
+ * for bit: act_out [batch][c_in][h_in][w_in] is the rounded activation (the next layer's backward pass reads
+ * it), astream the next layer's activation streams (geo_sc_act_stream_bytes(next_desc)), save_* / scale_out /
+ * scratch as for geo_sc_bn_pool_act_forward.  LFSR generator only.
+ * The backward pass of the chain is geo_sc_epilogue_backward: geo_sc_bn_pool_act_backward reading the counts
+ * in place of x (counts [batch][channels][height][width], the layer's own output size). */
+int geo_sc_epilogue_forward(const geo_sc_conv_desc *next_desc, int in_bit_length, int prec, int training, float eps,
+                            float momentum, const int32_t *counts_device, const float *weight_device,
+                            const float *bias_device, float *running_mean_device, float *running_var_device,
+                            float *act_out_device, float *save_mean_device, float *save_invstd_device,
+                            float *save_wq_device, float *save_bq_device, float *scale_out_device, void *astream_device,
+                            size_t astream_bytes, void *scratch_device, size_t scratch_bytes, void *stream);
+int geo_sc_epilogue_backward(int batch, int channels, int height, int width, int in_bit_length, int training,
+                             const int32_t *counts_device, const float *grad_out_device, const float *weight_device,
+                             const float *save_mean_device, const float *save_invstd_device, const float *save_wq_device,
+                             const float *save_bq_device, float *grad_x_device, float *grad_weight_device,
+                             float *grad_bias_device, void *scratch_device, size_t scratch_bytes, void *stream);
+
 /* ---- fixed-point rounding of activations and weights ----------------------------------------------
  * Replaces quantize (utils_functional.py:33-39), which the reference evaluates as four element-wise
  * PyTorch ops: y = clamp(round_half_even(x * 2^prec), -(2^prec - 1), 2^prec - 1) / 2^prec, one kernel.

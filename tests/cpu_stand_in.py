@@ -12,8 +12,8 @@ _MODE_NAMES = {0: "1d_bin", 1: "z_bin", 2: "yz_bin", 3: "full_or", 4: "2d_bin", 
 def install(monkeypatch):
     from geo_b200 import ops
 
-    def sc_conv2d_staged(act, weight, bit_length, mode="1d_bin", padding=(0, 0), wprep=None, generator="lfsr", seed=0,
-                         **kw):
+    def sc_conv2d_staged(act, weight, bit_length, mode="1d_bin", padding=(0, 0), wprep=None, astreams=None,
+                         generator="lfsr", seed=0, **kw):
         assert generator == "lfsr", "the CPU oracle only has the LFSR generator"
         y = oracle.conv2d(act.detach(), weight.detach(), bit_length, mode, pad_h=padding[0], pad_w=padding[1], **kw)
         return torch.from_numpy(y)

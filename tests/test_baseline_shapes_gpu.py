@@ -33,18 +33,48 @@ def _check_slices(oracle_lib, y, a, w, L, mode, pad, slices, **kw):
         assert np.array_equal(got, ref), f"{mode} L={L} images {b} channels {o}: max diff {np.abs(got - ref).max()}"
 
 
-def test_c1_single_conv_whole_layer(cuda_device, oracle_lib):
+_REF_CPU_SCRIPT = """
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+from oracle import ref_loader
+ext = ref_loader.ref_sc_extension()
+if ext is None:
+    sys.exit(3)
+d = np.load(sys.argv[2])
+y = ext.conv2d_add_partial_new(torch.from_numpy(d["a"]), torch.from_numpy(d["w"]), int(d["L"]), (int(d["pad"]),) * 2, (1, 1))
+np.save(sys.argv[3], y.numpy())
+"""
+
+
+def _reference_cpu_kernel(a, w, L, pad, tmp_path):
+    """Output of the reference's own CPU kernel (sc.cpp built unmodified), or None where that build is absent.  Run
+    in a process of its own: its module is called sc_extension like one of this repository's torch shims, and one
+    process cannot hold both."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    inp, out = str(tmp_path / "in.npz"), str(tmp_path / "out.npy")
+    np.savez(inp, a=a.numpy(), w=w.numpy(), L=L, pad=pad)
+    r = subprocess.run([sys.executable, "-c", _REF_CPU_SCRIPT, root, inp, out], capture_output=True, text=True, timeout=600)
+    if r.returncode == 3:
+        return None
+    assert r.returncode == 0, r.stderr[-2000:]
+    return np.load(out)
+
+
+def test_c1_single_conv_whole_layer(cuda_device, oracle_lib, tmp_path):
     """32x3x32x32 . 32x3x5x5, pad 2, L=64, activations on 1/64 levels, 1d_bin, no progressive loading: the whole
     output against the oracle and, where it is built, against the reference's CPU kernel itself."""
     from geo_b200 import ops
-    from oracle import ref_loader
 
     a, w = _inputs((32, 3, 32, 32), (32, 3, 5, 5), 0, levels=64)
     y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), 64, "1d_bin", (2, 2)).cpu()
     assert np.array_equal(y.numpy(), oracle_lib.conv2d(a, w, 64, "1d_bin", pad_h=2, pad_w=2))
-    ext = ref_loader.ref_sc_extension()
-    if ext is not None:
-        assert torch.equal(y, ext.conv2d_add_partial_new(a, w, 64, (2, 2), (1, 1)))
+    ref = _reference_cpu_kernel(a, w, 64, 2, tmp_path)
+    if ref is not None:
+        assert np.array_equal(y.numpy(), ref)
     # the mode the configuration's prose describes (OR inside a channel, binary across channels) is z_bin
     yz = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), 64, "z_bin", (2, 2)).cpu().numpy()
     assert np.array_equal(yz, oracle_lib.conv2d(a, w, 64, "z_bin", pad_h=2, pad_w=2))

@@ -161,3 +161,84 @@ def test_fused_bn_pool_hardtanh_falls_back_for_other_shapes(cuda_device):
     bn = layers.BatchNorm2d_fixed(3).to(cuda_device)
     y = layers.bn_pool_hardtanh(bn, x)
     assert y.shape == (2, 3, 3, 4)
+
+
+@pytest.mark.parametrize("training", [True, False])
+def test_fused_epilogue_equals_the_separate_kernels(cuda_device, training):
+    """Bit counts -> batch norm -> pool -> hardtanh -> rounding -> next layer's streams in one pass
+    (geo_sc_epilogue_forward) against the chain of separate entry points, bit for bit: the rounded activation, the
+    stream image including its zero border, the saved statistics and the running statistics; and the backward
+    pass reading counts against the one reading the float value."""
+    from geo_b200 import ops
+
+    g = torch.Generator().manual_seed(12)
+    cases = [
+        # counts shape, L of the counts, next layer: (c_out, k, pad, L, mode, z_unit, load_unit, load_wait)
+        ((6, 8, 12, 16), 128, (5, 3, 1, 128, "1d_bin", 4, 2, 2)),
+        ((3, 5, 8, 8), 64, (7, 5, 2, 256, "yz_bin", 2, 8, 1)),
+        ((4, 16, 4, 8), 256, (9, 2, 0, 32, "z_bin", 4, 3, 4)),
+        ((2, 3, 6, 4), 32, (4, 1, 0, 16, "full_or", 4, 8, 1)),
+    ]
+    for shape, L_in, (O2, k, pad, L2, mode, z, lu, lw) in cases:
+        B, C, H, W = shape
+        counts = torch.randint(-L_in * 3, L_in * 3, shape, generator=g, dtype=torch.int32).to(cuda_device)
+        bw = (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+        bb = (torch.rand(C, generator=g) - 0.5).to(cuda_device)
+        rm = [torch.rand(C, generator=g).to(cuda_device) for _ in range(1)] * 1
+        rm1, rv1 = rm[0].clone(), (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+        rm2, rv2 = rm1.clone(), rv1.clone()
+        nd = ops.make_desc(B, C, H // 2, W // 2, O2, k, k, L2, mode, pad_h=pad, pad_w=pad, z_unit=z, total_width=7,
+                           load_width=lu, load_wait_w=lw, load_wait_a=lw)
+        act, streams, mean, invstd, scale, wq, bq = ops.epilogue_forward(counts, L_in, nd, bw, bb, rm1, rv1, training, 0.1, 1e-5)
+        x = ops.counts_to_float(counts, L_in)
+        y, mean2, invstd2, scale2, wq2, bq2 = ops.bn_pool_act_forward(x, bw, bb, rm2, rv2, training, 0.1, 1e-5)
+        yq = ops.quantize(y, 7)
+        streams2 = ops.generate_act_streams(yq, nd)
+        assert torch.equal(act, yq)
+        n = streams2.numel()
+        assert torch.equal(streams[:n], streams2[:n])
+        for a, b in ((mean, mean2), (invstd, invstd2), (scale, scale2), (wq, wq2), (bq, bq2), (rm1, rm2), (rv1, rv2)):
+            assert torch.equal(a, b)
+        go = torch.randn(act.shape, generator=g).to(cuda_device)
+        gx, gw, gb = ops.epilogue_backward(counts, L_in, go, bw, mean, invstd, wq, bq, training)
+        gx2, gw2, gb2 = ops.bn_pool_act_backward(x, go, bw, mean2, invstd2, wq2, bq2, training)
+        assert torch.equal(gx, gx2) and torch.equal(gw, gw2) and torch.equal(gb, gb2)
+
+
+def test_network_with_fused_blocks_equals_network_of_separate_layers(cuda_device):
+    """The 4-layer CNN and the VGG-11-style network, forward and backward, with the SC blocks fused (one pass from
+    bit counts to the next layer's streams) and as separate layers: logits, running statistics and every gradient
+    are identical."""
+    from geo_b200 import layers, network
+
+    g = torch.Generator().manual_seed(31)
+    for make, batch in ((network.CONV_tiny_add_partial, 16), (network.VGG11_add_partial, 8)):
+        x = torch.rand(batch, 3, 32, 32, generator=g).to(cuda_device)
+        y = torch.randint(0, 10, (batch,), generator=g).to(cuda_device)
+        results = []
+        for fuse in (True, False):
+            layers.FUSE_EPILOGUE = fuse
+            try:
+                torch.manual_seed(5)
+                net = make().to(cuda_device).train()
+                out = net(x.clone())
+                torch.nn.functional.cross_entropy(out, y).backward()
+                stats = [b.detach().clone() for n, b in net.named_buffers() if "running" in n]
+                results.append((out.detach().clone(), [p.grad.detach().clone() for p in net.parameters()], stats))
+            finally:
+                layers.FUSE_EPILOGUE = True
+        assert torch.equal(results[0][0], results[1][0])
+        for a, b in zip(results[0][1] + results[0][2], results[1][1] + results[1][2]):
+            assert torch.equal(a, b)
+        # evaluation mode: weight-stream cache and running statistics
+        outs = []
+        for fuse in (True, False):
+            layers.FUSE_EPILOGUE = fuse
+            try:
+                net.eval()
+                with torch.no_grad():
+                    outs.append(net(x.clone()))
+                    outs.append(net(x.clone()))      # second call: cached weight streams
+            finally:
+                layers.FUSE_EPILOGUE = True
+        assert all(torch.equal(outs[0], o) for o in outs[1:])
