@@ -60,26 +60,24 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-    return v;
-}
 
 // One pattern's members: PAT bit j set = the weight of channel j is negative.  a_lo / a_hi: shared address of the
-// lane's two runs of four positions in plane 0, row 0; sw / so: shared address of the quad's stream-word and
-// offset lists; members [i0, i1) of the lists.
+// lane's two runs of four positions in plane 0, row 0; sw / so: the quad's stream-word and offset lists; members
+// [i0, i1) of the lists.  The stream words and the offset of member i + 1 are fetched while member i is computed,
+// so that the activation loads of a member never wait for its offset (slot i1 exists: the lists are padded).
 template <int PAT>
 __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo, uint32_t a_hi,
-                                           uint32_t sw, uint32_t so, int i0, int i1) {
-    uint32_t wa = sw + (uint32_t)i0 * 16, oa = so + (uint32_t)i0 * 4;
-    const uint32_t wend = sw + (uint32_t)i1 * 16;
+                                           const uint4 *__restrict__ sw, const uint32_t *__restrict__ so, int i0, int i1) {
+    if (i0 >= i1) return;
+    uint4 wn = sw[i0];
+    uint32_t on = so[i0];
 #pragma unroll 2
-    for (; wa < wend; wa += 16, oa += 4) {
-        const uint4 w = lds128(wa);
-        const uint32_t off = lds32(oa);
-        const uint4 x = lds128(a_lo + off);
-        const uint4 y = lds128(a_hi + off);
+    for (int i = i0; i < i1; i++) {
+        const uint4 w = wn;
+        const uint4 x = lds128(a_lo + on);
+        const uint4 y = lds128(a_hi + on);
+        wn = sw[i + 1];
+        on = so[i + 1];
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -107,7 +105,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
     const int sw_off = pr.a_bytes, so_off = sw_off + NQ * pr.SL * 16, sb_off = so_off + NQ * pr.SL * 4;
 
     // ---- producer side: the words of a plane that this thread copies, for the producer's position tile ----
-    int prod_ptile = -1;
+    int prod_ptile = -1, nslots = 0;   // nslots: how many of this thread's slots hold a word of the tile
     int goff[kRowsGatherSlots];     // word offset in the stream image of one pack (image, row, column), -1: none
     auto set_gather_slots = [&](int ptile) {
         prod_ptile = ptile;
@@ -134,6 +132,9 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
                 }
             }
         }
+        nslots = 0;
+#pragma unroll
+        for (int s = 0; s < kRowsGatherSlots; s++) nslots += goff[s] >= 0;
     };
 
     auto produce = [&](int s) {
@@ -148,12 +149,12 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
         const int npl = min(pr.UCH, pr.units - chunk * pr.UCH) * pr.PU;
         const uint32_t *src = pr.as + (size_t)p * pr.pack_words;
         const int32_t *pg = pr.pgoff + (size_t)gc * pr.NPL;
-        for (int pl = 0; pl < npl; pl++) {
+        uint32_t dp = dst + (uint32_t)t * 4;
+        for (int pl = 0; pl < npl; pl++, dp += (uint32_t)pr.PL * 4) {
             const uint32_t *sp = src + __ldg(pg + pl);
-            const uint32_t dp = dst + (uint32_t)(pl * pr.PL + t) * 4;
 #pragma unroll
-            for (int k = 0; k < kRowsGatherSlots; k++)
-                if (goff[k] >= 0) cp4(dp + k * kRowsThreads * 4, sp + goff[k]);
+            for (int k = 0; k < kRowsGatherSlots; k++)   // slots past the tile's words (goff < 0) are the last ones
+                if (k < nslots) cp4(dp + k * kRowsThreads * 4, sp + goff[k]);
         }
         // the NQ quads' lists are contiguous
         const size_t gcq = (size_t)gc * pr.Q + ctile * NQ;
@@ -238,8 +239,9 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
         {
             const uint32_t stage = smem_base + (uint32_t)(s & 1) * pr.stage_bytes;
             const uint32_t a_lo = stage + lane_off[0], a_hi = stage + lane_off[1];
-            const uint32_t swl = stage + sw_off + (uint32_t)ql * pr.SL * 16;
-            const uint32_t sol = stage + so_off + (uint32_t)ql * pr.SL * 4;
+            const unsigned char *stage_ptr = smem + (size_t)(s & 1) * pr.stage_bytes;
+            const uint4 *swl = (const uint4 *)(stage_ptr + sw_off) + ql * pr.SL;
+            const uint32_t *sol = (const uint32_t *)(stage_ptr + so_off) + ql * pr.SL;
             const uint16_t *sbl = (const uint16_t *)(smem + (size_t)(s & 1) * pr.stage_bytes + sb_off) + ql * 24;
             // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
             const int mybeg = lane < 17 ? (int)sbl[lane] : 0;

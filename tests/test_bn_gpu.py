@@ -195,8 +195,8 @@ def test_fused_epilogue_equals_the_separate_kernels(cuda_device, training):
         yq = ops.quantize(y, 7)
         streams2 = ops.generate_act_streams(yq, nd)
         assert torch.equal(act, yq)
-        n = streams2.numel()
-        assert torch.equal(streams[:n], streams2[:n])
+        # the buffers are rounded up to 256 bytes: compare the stream words, not the slack behind them
+        assert torch.equal(ops.act_streams_canonical(streams, nd), ops.act_streams_canonical(streams2, nd))
         for a, b in ((mean, mean2), (invstd, invstd2), (scale, scale2), (wq, wq2), (bq, bq2), (rm1, rm2), (rv1, rv2)):
             assert torch.equal(a, b)
         go = torch.randn(act.shape, generator=g).to(cuda_device)
