@@ -50,6 +50,7 @@ struct RowsParams {
     int img_words, pack_words;
     int stage_bytes, a_bytes;
     int pairs;
+    uint32_t one;   // 1, as a run-time value (see add_on_fma_pipe)
     long long n_items;
 };
 
@@ -61,21 +62,30 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
+// base + off computed as a multiply-add by a run-time one: the integer multiply-add issues on the FMA pipe, which
+// this kernel leaves idle, instead of the ALU pipe that the LOP3s saturate.
+__device__ __forceinline__ uint32_t add_on_fma_pipe(uint32_t off, uint32_t one, uint32_t base) {
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(off), "r"(one), "r"(base));
+    return r;
+}
+
 // One pattern's members: PAT bit j set = the weight of channel j is negative.  a_lo / a_hi: shared address of the
 // lane's two runs of four positions in plane 0, row 0; sw / so: the quad's stream-word and offset lists; members
 // [i0, i1) of the lists.  The stream words and the offset of member i + 1 are fetched while member i is computed,
 // so that the activation loads of a member never wait for its offset (slot i1 exists: the lists are padded).
 template <int PAT>
 __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo, uint32_t a_hi,
-                                           const uint4 *__restrict__ sw, const uint32_t *__restrict__ so, int i0, int i1) {
+                                           const uint4 *__restrict__ sw, const uint32_t *__restrict__ so, int i0, int i1,
+                                           uint32_t one) {
     if (i0 >= i1) return;
     uint4 wn = sw[i0];
     uint32_t on = so[i0];
 #pragma unroll 2
     for (int i = i0; i < i1; i++) {
         const uint4 w = wn;
-        const uint4 x = lds128(a_lo + on);
-        const uint4 y = lds128(a_hi + on);
+        const uint4 x = lds128(add_on_fma_pipe(on, one, a_lo));
+        const uint4 y = lds128(add_on_fma_pipe(on, one, a_hi));
         wn = sw[i + 1];
         on = so[i + 1];
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
             // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
             const int mybeg = lane < 17 ? (int)sbl[lane] : 0;
 #define GEO_BUCKET(B) \
-    run_bucket<B>(accp, accn, a_lo, a_hi, swl, sol, __shfl_sync(0xffffffffu, mybeg, B), __shfl_sync(0xffffffffu, mybeg, B + 1));
+    run_bucket<B>(accp, accn, a_lo, a_hi, swl, sol, __shfl_sync(0xffffffffu, mybeg, B), __shfl_sync(0xffffffffu, mybeg, B + 1), pr.one);
             GEO_BUCKET(0) GEO_BUCKET(1) GEO_BUCKET(2) GEO_BUCKET(3) GEO_BUCKET(4) GEO_BUCKET(5) GEO_BUCKET(6) GEO_BUCKET(7)
             GEO_BUCKET(8) GEO_BUCKET(9) GEO_BUCKET(10) GEO_BUCKET(11) GEO_BUCKET(12) GEO_BUCKET(13) GEO_BUCKET(14) GEO_BUCKET(15)
 #undef GEO_BUCKET
@@ -480,6 +490,7 @@ int launch_accumulate_rows(const Geometry &g, const uint32_t *astream, const voi
     pr.stage_bytes = (int)rp.stage_bytes;
     pr.a_bytes = rp.NPL * rp.PL * 4;
     pr.pairs = g.P * g.G;
+    pr.one = 1;
     const long long total_rq = (long long)g.B * g.Ho * rp.CG;
     const long long ptiles = (total_rq + 64 * rp.NH - 1) / (64 * rp.NH);
     pr.n_items = ptiles * pr.CT * pr.pairs;
