@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "sc_common.h"
+#include "sc_fullbin.h"
 #include "sc_rows.h"
 #include "sc_sorted.h"
 
@@ -141,6 +142,8 @@ static size_t wprep_dense_bytes(const Geometry &g) {
 // dense streams, member offsets, then (long groups only) one sign-sorted section: the row-tile form where the
 // layer's geometry allows it, else the im2col form
 static size_t wprep_bytes(const Geometry &g) {
+    const FullBinPlan fb = fullbin_plan(g);
+    if (fb.layout) return wprep_dense_bytes(g) + fb.bytes;   // full_bin: the weights packed for the binary GEMM
     const RowsPlan rp = rows_plan(g);
     return wprep_dense_bytes(g) + (rp.layout ? rp.total() : sorted_plan(g).total());
 }
@@ -150,7 +153,8 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
     int32_t *aoff = (int32_t *)((char *)wprep + align_up(g.w_stream_words * 4, 256));
     int rc = launch_prepare_weights(g, weight, ws, aoff, s);
     if (rc) return rc;
-    if (rows_plan(g).layout) rc = launch_sort_rows(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    if (fullbin_plan(g).layout) rc = launch_fullbin_pack(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    else if (rows_plan(g).layout) rc = launch_sort_rows(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     else if (sorted_plan(g).layout) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     return rc;
 }
@@ -158,6 +162,8 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
 static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wprep, int32_t *out, cudaStream_t s) {
     const uint32_t *ws = (const uint32_t *)wprep;
     const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
+    if (fullbin_plan(g).layout)
+        return launch_accumulate_fullbin(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
     const RowsPlan rp = rows_plan(g);
     if (rp.eligible) return launch_accumulate_rows(g, as, (const char *)wprep + wprep_dense_bytes(g), out, s);
     if (!rp.layout && sorted_plan(g).eligible)

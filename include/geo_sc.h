@@ -164,6 +164,8 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
  * per (group, chunk of <= 160 members, quad of four output channels) the members sorted by which of the
  * four weights are negative -- one uint4 with the four non-zero stream words per member and pack, one
  * uint16 tile offset per member and 17 pattern boundaries; geo_sc_weight_prep_bytes covers all three.
+ * For GEO_SC_MODE_FULL_BIN the third section holds the weight words once more, in the order the binary
+ * tensor-core GEMM of that mode reads them (tiles of 32 output channels x 2 polarities x 32 words).
  * Neither the size nor the contents of the prepared buffer depend on `batch`: a buffer prepared once
  * serves geo_sc_accumulate calls of any batch size whose descriptor agrees in every other field
  * (geo_sc_accumulate picks the dense or the sign-sorted kernel per call; both sections are there).
