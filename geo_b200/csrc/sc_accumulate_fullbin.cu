@@ -59,7 +59,7 @@ struct FullBinParams {
     const uint32_t *wb;     // [CT][NST][64 columns][32 words in fragment order]
     int32_t *out;           // [B][O][Ho][Wo]
     int M, O, HoWo, Wo, Wp;
-    int P, K, KW, NST;      // KW = K * P words, NST = stages = ceil(KW / 32)
+    int P, K, KW, NST;      // K filter elements (members), KW = K * P words, NST = stages = ceil(KW / 32)
     int img_words, pack_words;
     int splits;
 };
@@ -202,9 +202,9 @@ __global__ void __launch_bounds__(256) fullbin_pack_kernel(const uint32_t *__res
 
 FullBinPlan fullbin_plan(const Geometry &g) {
     FullBinPlan fp = {};
-    fp.layout = g.mode == GEO_SC_MODE_FULL_BIN && g.Kp == 4 && (long long)g.K * g.P < (1LL << 30);
+    fp.layout = g.mode == GEO_SC_MODE_FULL_BIN && g.K == 1 && g.Kp == 4 && (long long)g.G * g.P < (1LL << 30);
     if (!fp.layout) return fp;
-    fp.KW = g.K * g.P;
+    fp.KW = g.G * g.P;   // full_bin: every filter element is a group of one member
     fp.NST = (fp.KW + FB_STAGE_WORDS - 1) / FB_STAGE_WORDS;
     fp.CT = (g.O + 31) / 32;
     fp.bytes = align_up((size_t)fp.CT * fp.NST * 64 * FB_STAGE_WORDS * 4, 256);
@@ -217,7 +217,7 @@ int launch_fullbin_pack(const Geometry &g, const uint32_t *wstream, void *sectio
     long long blocks = (total + 255) / 256;
     const long long cap = (long long)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    fullbin_pack_kernel<<<(unsigned)blocks, 256, 0, s>>>(wstream, g.P, g.K, g.Opad, fp.NST, fp.CT, (uint32_t *)section);
+    fullbin_pack_kernel<<<(unsigned)blocks, 256, 0, s>>>(wstream, g.P, g.G, g.Opad, fp.NST, fp.CT, (uint32_t *)section);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -228,7 +228,7 @@ int launch_accumulate_fullbin(const Geometry &g, const uint32_t *astream, const 
     FullBinParams pr;
     pr.as = astream; pr.aoff = aoff; pr.wb = (const uint32_t *)section; pr.out = out;
     pr.M = (int)g.M; pr.O = g.O; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
-    pr.P = g.P; pr.K = g.K; pr.KW = fp.KW; pr.NST = fp.NST;
+    pr.P = g.P; pr.K = g.G; pr.KW = fp.KW; pr.NST = fp.NST;
     pr.pack_words = g.C * g.Hp * g.Wp;
     pr.img_words = g.P * pr.pack_words;
     static PerDeviceOnce once;

@@ -162,22 +162,28 @@ class TrainStep:
         return loss.detach(), output.detach()
 
     def _update(self):
+        # the loop body of utils_own.py:98-114, with the per-tensor copies, divisions and clamps batched into
+        # multi-tensor calls (a handful of kernels instead of one per parameter)
         with torch.no_grad():
-            for m in self.sc_modules:
-                m.weight.data.copy_(m.weight_org)
-            for master, p in zip(self.param_copy, self.params):
-                if p.grad is not None:
-                    master.grad = p.grad.detach().to(torch.float32) / SCALE_FACTOR
+            if self.sc_modules:
+                torch._foreach_copy_([m.weight.data for m in self.sc_modules], [m.weight_org for m in self.sc_modules])
+            have = [(master, p.grad.detach()) for master, p in zip(self.param_copy, self.params) if p.grad is not None]
+            if have:
+                grads = [g if g.dtype == torch.float32 else g.to(torch.float32) for _, g in have]
+                for (master, _), g in zip(have, torch._foreach_div(grads, SCALE_FACTOR)):
+                    master.grad = g
             if self._plain_sgd():
                 self._sgd_step(self._lr_dev if self._captured else float(self.optimizer.param_groups[0]["lr"]))
             else:
                 self.optimizer.step()
-            for master, p in zip(self.param_copy, self.params):
-                p.data.copy_(master.data)
-            for m in self.sc_modules:
-                m.weight_org.copy_(m.weight.data.clamp(-1, 0.999))
-                if hasattr(m, "invalidate_stream_cache"):
-                    m.invalidate_stream_cache()
+            torch._foreach_copy_([p.data for p in self.params], [m.data for m in self.param_copy])
+            if self.sc_modules:
+                clamped = torch._foreach_clamp_min([m.weight.data for m in self.sc_modules], -1.0)
+                torch._foreach_clamp_max_(clamped, 0.999)
+                torch._foreach_copy_([m.weight_org for m in self.sc_modules], clamped)
+                for m in self.sc_modules:
+                    if hasattr(m, "invalidate_stream_cache"):
+                        m.invalidate_stream_cache()
             self.optimizer.zero_grad(set_to_none=True)
 
     def _plain_sgd(self):
