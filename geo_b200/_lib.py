@@ -51,6 +51,8 @@ def lib():
     L.geo_sc_status_string.argtypes = [i32]
     L.geo_sc_last_error.restype = ctypes.c_char_p
     L.geo_sc_init.restype = i32
+    L.geo_sc_device_error_count.argtypes = [ctypes.POINTER(i32)]
+    L.geo_sc_device_error_count.restype = i32
     for n in ("geo_sc_conv2d_workspace_bytes", "geo_sc_weight_prep_bytes", "geo_sc_act_stream_bytes"):
         getattr(L, n).argtypes = [dp, szp]
         getattr(L, n).restype = i32
@@ -137,6 +139,13 @@ def is_sign_sorted(desc):
     yes = ctypes.c_int32(0)
     check(lib().geo_sc_accumulate_is_sign_sorted(ctypes.byref(desc), ctypes.byref(yes)), "geo_sc_accumulate_is_sign_sorted")
     return bool(yes.value)
+
+
+def device_error_count():
+    """Bounded hardware-barrier waits that ran out on the current device since the library was loaded."""
+    n = ctypes.c_int32(0)
+    check(lib().geo_sc_device_error_count(ctypes.byref(n)), "geo_sc_device_error_count")
+    return n.value
 
 
 def host_stream(bit_length, value, seed_base, seed_index, total_width=7, load_width=8, load_wait=1):

@@ -38,6 +38,13 @@ CONFIGS = {
     "c4_yz16": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "yz_bin", 8, 1, 16),
     "c4_2d": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "2d_bin", 8, 1, 1024),
     "c4_full_bin": ((256, 256, 16, 16), (256, 256, 3, 3), (1, 1), 256, "full_bin", 8, 1, 1024),
+    # layers of the VGG-11-style network at 256 images (L=128, load 2/2)
+    "c5conv1": ((256, 3, 32, 32), (64, 3, 3, 3), (1, 1), 128, "1d_bin", 2, 2, 1024),
+    "c5conv2": ((256, 64, 16, 16), (128, 64, 3, 3), (1, 1), 128, "1d_bin", 2, 2, 1024),
+    "c5conv4": ((256, 256, 8, 8), (256, 256, 3, 3), (1, 1), 128, "1d_bin", 2, 2, 1024),
+    "c5conv6": ((256, 512, 4, 4), (512, 512, 3, 3), (1, 1), 128, "1d_bin", 2, 2, 1024),
+    "c5conv8": ((256, 512, 2, 2), (512, 512, 3, 3), (1, 1), 128, "1d_bin", 2, 2, 1024),
+    "c5fc1": ((256, 512, 1, 1), (512, 512, 1, 1), (0, 0), 128, "1d_bin", 2, 2, 1024),
 }
 
 

@@ -5,6 +5,7 @@
 
 #include "sc_common.h"
 #include "sc_fullbin.h"
+#include "sc_guide_tc.h"
 #include "sc_rows.h"
 #include "sc_sorted.h"
 
@@ -206,6 +207,11 @@ const char *geo_sc_status_string(int status) {
 const char *geo_sc_last_error(void) { return g_err; }
 
 int geo_sc_init(void) { return ensure_tables(); }
+
+int geo_sc_device_error_count(int *count) {
+    if (!count) return fail(GEO_SC_ERR_NULL, "count is NULL");
+    return tc_error_count(count);
+}
 
 int geo_sc_group_geometry(const geo_sc_conv_desc *desc, int32_t *groups, int32_t *members, int32_t *members_padded,
                           int32_t *cout_tile, int32_t *cout_padded) {

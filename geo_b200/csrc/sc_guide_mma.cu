@@ -27,6 +27,7 @@
 
 #include "sc_common.h"
 #include "sc_guide_mma.h"
+#include "sc_guide_tc.h"
 
 namespace geo {
 
@@ -1027,7 +1028,10 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         // widest channel tile that still leaves four CTAs of work per SM
         const long long ptiles = ((long long)d.B * d.H * d.W + 127) / 128;
         int rc;
-        if (p.Cn % 128 == 0 && ptiles * (p.Cn / 128) >= sm_count() * 4) rc = launch_dgrad<4>(d, p.Cn, Dh, wd, grad_act, flag, s);
+        TcTile tile;
+        // wide layers: tcgen05.mma with tensor-memory accumulators and TMA tiles (sc_guide_tc.cu)
+        if (tc_dgrad_plan(d, p.Cn, &tile)) rc = launch_tc_dgrad(d, p.Cn, Dh, wd, grad_act, flag, s);
+        else if (p.Cn % 128 == 0 && ptiles * (p.Cn / 128) >= sm_count() * 4) rc = launch_dgrad<4>(d, p.Cn, Dh, wd, grad_act, flag, s);
         else if (p.Cn % 64 == 0 && ptiles * (p.Cn / 64) >= sm_count() * 4) rc = launch_dgrad<2>(d, p.Cn, Dh, wd, grad_act, flag, s);
         else rc = launch_dgrad<1>(d, p.Cn, Dh, wd, grad_act, flag, s);
         if (rc) return rc;

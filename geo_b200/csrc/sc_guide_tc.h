@@ -1,0 +1,21 @@
+// tcgen05 / TMEM / TMA kernels of the float guide for wide layers (sc_guide_tc.cu).
+#pragma once
+
+#include "sc_common.h"
+#include "sc_guide_mma.h"
+
+namespace geo {
+
+struct TcTile {
+    int bw, bh, nb;   // pixel tile of a CTA: nb images x bh rows x bw columns = 128 pixels
+};
+
+// Whether the activation-gradient GEMM of this layer runs on tcgen05 (wide layers: at least 128 input channels
+// padded to a multiple of 128, column count a multiple of 64, image width a power of two).
+bool tc_dgrad_plan(const MmaDims &d, int Cn, TcTile *tile);
+int launch_tc_dgrad(const MmaDims &d, int Cn, const void *Dh, const void *wd, float *grad_act, const int *flag,
+                    cudaStream_t s);
+// Bounded mbarrier waits that ran out since the library was loaded (0 in a healthy run).
+int tc_error_count(int *count);
+
+}  // namespace geo

@@ -108,6 +108,13 @@ const char *geo_sc_last_error(void);
  * implicitly by the first generation call on a device. */
 int geo_sc_init(void);
 
+/* Kernels of this library that wait on hardware barriers (the tcgen05 / TMA kernels of the guide) bound every wait;
+ * a wait that runs out makes its thread block give up and raises a device-side count.  *count receives that count
+ * for the current device since the library was loaded: 0 in a healthy run, anything else means that the results
+ * of some guide call are not to be trusted.  Synchronises with the device (a small device-to-host copy).  No
+ * counterpart in the reference. */
+int geo_sc_device_error_count(int *count);
+
 /* ---- whole forward --------------------------------------------------------------
  * Replaces sc_extension_cuda.conv2d_add_partial_variable_acc (sc_cuda.cpp:47-63; dim==0 ->
  * GEO_SC_MODE_Z, else GEO_SC_MODE_1D), conv2d_add_yz_variable_acc (sc_cuda.cpp:34-45) and,

@@ -219,3 +219,38 @@ def test_training_layer_shapes_full_batch(cuda_device):
     scale = gw_ref.abs().max().item()
     assert (gw - gw_ref).abs().max().item() <= 5e-5 * scale
     assert (ga - ga_ref).abs().max().item() <= 1e-5 * ga_ref.abs().max().item()
+
+
+WIDE_CASES = [
+    # layers wide enough for the tcgen05 activation-gradient kernel (>= 128 input channels, image width a power of
+    # two): act, weight, (pad_h, pad_w)
+    ((4, 128, 8, 8), (32, 128, 3, 3), (1, 1)),        # two whole 8x8 images per 128-pixel tile
+    ((3, 128, 8, 8), (40, 128, 3, 3), (1, 1)),        # odd batch: the last tile is half outside the batch
+    ((2, 256, 16, 16), (64, 256, 3, 3), (1, 1)),      # half an image per tile, two channel tiles
+    ((2, 128, 16, 16), (32, 128, 5, 5), (2, 2)),      # 5x5 taps
+    ((9, 160, 4, 4), (48, 160, 3, 3), (1, 1)),        # eight 4x4 images per tile, channels padded to 256
+    ((1, 128, 32, 32), (32, 128, 3, 3), (1, 1)),      # four rows of a 32-wide image per tile
+]
+
+
+@pytest.mark.parametrize("mode", ["1d_bin", "full_or", "2d_bin"])
+@pytest.mark.parametrize("case", range(len(WIDE_CASES)))
+def test_guide_gradients_of_wide_layers(cuda_device, mode, case):
+    """Same check as above on shapes that take the tcgen05 / tensor-memory / TMA kernel for the activation
+    gradient; none of its bounded barrier waits may have run out."""
+    from geo_b200 import _lib, ops
+    from oracle import guide as oracle_guide
+
+    ashape, wshape, pad = WIDE_CASES[case]
+    g = torch.Generator().manual_seed(900 + 13 * case + len(mode))
+    a = q7(torch.rand(*ashape, generator=g))
+    w = q7((torch.rand(*wshape, generator=g) * 2 - 1) * 0.25)
+    w.view(-1)[::5] = 0.0
+    desc = ops.desc_for(a, w, 128, mode, pad)
+    go = torch.randn(*ops.out_shape(desc), generator=g)
+    ga_ref, gw_ref = oracle_guide.guide_grads(a, w, go, mode, pad[0], pad[1])
+    ga, gw = ops.guide_backward(a.to(cuda_device), w.to(cuda_device), go.to(cuda_device), desc, quantized=True)
+    torch.cuda.synchronize()
+    assert _lib.device_error_count() == 0
+    _close(gw.cpu(), gw_ref, f"{mode} grad_weight")
+    _close(ga.cpu(), ga_ref, f"{mode} grad_act")
