@@ -891,7 +891,8 @@ MmaPlan mma_plan(const MmaDims &d) {
     p.apad_bytes = align_up((size_t)d.B * d.Hp * d.Wp * d.Cp * 2, 256);
     p.wb_bytes = align_up((size_t)d.G * d.N2 * d.Kp * 2, 256);
     p.dh_bytes = align_up((size_t)3 * d.G * d.M * d.N2 * 2, 256);
-    p.Cn = (d.C + 31) / 32 * 32;
+    // channel rows of Wd: zero padded to the tile of the activation-gradient kernel (128 for the tcgen05 kernel of wide layers)
+    p.Cn = d.C >= 128 ? (d.C + 127) / 128 * 128 : (d.C + 31) / 32 * 32;
     p.wd_bytes = align_up((size_t)p.Cn * d.K2 * d.K3 * d.N2 * 2, 256);
     const long long tiles = (long long)d.G * ((d.Kp + 63) / 64) * (d.N2 / 64);
     long long S = (long long)sm_count() * 8 / tiles;   // at most two full waves of four resident CTAs per SM, no third
@@ -1003,7 +1004,11 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         GEO_CUDA_CHECK(cudaGetLastError());
         return GEO_SC_OK;
     }
-    {
+    TcTile ftile;
+    if (tc_forward_plan(d, &ftile)) {   // wide layers: tcgen05.mma, tensor-memory accumulators, TMA tiles (sc_guide_tc.cu)
+        int rc = launch_tc_forward(d, apad, wb, gout, Dh, flag, s);
+        if (rc) return rc;
+    } else {
         constexpr size_t smem = (size_t)MSTAGE * (128 * 64 + 64 * 64) + 64 * 132 * 4;
         static bool done[64] = {};
         int rc = opt_in_smem(mma_forward_kernel<1>, smem, done);

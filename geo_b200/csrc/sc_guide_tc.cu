@@ -86,6 +86,11 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
@@ -259,6 +264,162 @@ tc_dgrad_kernel(const __grid_constant__ CUtensorMap map_d, const __grid_constant
     }
 }
 
+
+// ---- forward product and D = gout * exp(-y) ------------------------------------------------------------------
+// y[m][n2] = sum over the members k' = (tap, c) of group g of a[pos(m) + tap][c] * Wb[g][n2][k'], then
+// D = gout * exp(-y) split into three bf16 terms (sc_guide_mma.cu: mma_forward_kernel does the same on mma.sync).
+// A CTA owns 128 output positions (whole rows of one image or whole small images) x 128 columns of one group.
+// Stages of 64 members: a 128 x 64 tile of the padded NHWC activations, fetched by one 4-d tensor-map copy whose
+// coordinates carry the tap's offset, and a 128 x 64 tile of Wb.  Two stages (eight MMAs, 128 members) make one
+// accumulator batch, flushed into the epilogue warps' fp32 sums like in the kernel above.
+constexpr int TF_STAGES = 6;
+constexpr int TF_STAGE_BYTES = 2 * TC_TILE_BYTES;
+constexpr int TF_SMEM = TF_STAGES * TF_STAGE_BYTES + 1024;
+
+struct TcForwardParams {
+    const float *gout;        // [B][O][Ho][Wo]
+    __nv_bfloat16 *Dh;        // [3][G][M][N2]
+    const int *inexact;
+    int B, O, Opad, Ho, Wo, HoWo, M, N2, G, K3, mode;
+    int cpb;                  // 64-channel blocks per tap (Cp / 64)
+    int nkb;                  // stages: taps * cpb
+    int bh, nb;               // position tile: nb images x bh rows x Wo columns = 128 positions
+    int tiles_y;              // tiles per image (nb == 1), else 1
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TcForwardParams pr) {
+    if (*pr.inexact) return;
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * TF_STAGES + 4];   // full, empty, acc_full[2], acc_empty[2]
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    unsigned char *tiles = (unsigned char *)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t tiles_s = smem_u32(tiles);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (TF_STAGES + s); };
+    auto accf_bar = [&](int a) { return bar0 + 8u * (2 * TF_STAGES + a); };
+    auto acce_bar = [&](int a) { return bar0 + 8u * (2 * TF_STAGES + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < TF_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abort = &abort_flag;
+
+    int b0, oy0;
+    if (pr.nb > 1) { b0 = blockIdx.x * pr.nb; oy0 = 0; }
+    else { b0 = blockIdx.x / pr.tiles_y; oy0 = (blockIdx.x % pr.tiles_y) * pr.bh; }
+    const int m0 = (b0 * pr.Ho + oy0) * pr.Wo;
+    const int n0 = blockIdx.y * 128, g = blockIdx.z;
+    const int nkb = pr.nkb, nbatch = (nkb + 1) / 2;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % TF_STAGES;
+                if (!mbar_wait(empty_bar(s), ((kb / TF_STAGES) & 1) ^ 1, abort)) break;
+                mbar_expect_tx(full_bar(s), TF_STAGE_BYTES);
+                const int tap = kb / pr.cpb, c0 = (kb % pr.cpb) * 64;
+                int ky, kx;   // 1d_bin groups are filter columns (taps = rows), 2d_bin groups single taps, full_or all taps
+                if (pr.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+                else if (pr.mode == GEO_SC_MODE_2D) { ky = g / pr.K3; kx = g % pr.K3; }
+                else { ky = tap / pr.K3; kx = tap % pr.K3; }
+                const uint32_t dst = tiles_s + (uint32_t)s * TF_STAGE_BYTES;
+                tma_load_4d(dst, &map_a, full_bar(s), c0, kx, oy0 + ky, b0);
+                tma_load_2d(dst + TC_TILE_BYTES, &map_w, full_bar(s), kb * 64, g * pr.N2 + n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % TF_STAGES, batch = kb >> 1, a = batch & 1;
+                if (!mbar_wait(full_bar(s), (kb / TF_STAGES) & 1, abort)) break;
+                if ((kb & 1) == 0 && !mbar_wait(acce_bar(a), ((batch >> 1) & 1) ^ 1, abort)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t st = tiles_s + (uint32_t)s * TF_STAGE_BYTES;
+                const uint64_t adesc = umma_desc(st), bdesc = umma_desc(st + TC_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; k++) umma_bf16(tmem_base + a * 128, adesc + 2 * k, bdesc + 2 * k, ((kb & 1) | k) != 0);
+                umma_commit(empty_bar(s));
+                if ((kb & 1) == 1 || kb == nkb - 1) umma_commit(accf_bar(a));
+            }
+        }
+    } else {
+        const int ew = warp - 2, quarter = warp & 3, half = ew >> 2;
+        float sum[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) sum[i] = 0.f;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 64;
+        bool ok = true;
+        for (int batch = 0; batch < nbatch; batch++) {
+            const int a = batch & 1;
+            ok = mbar_wait(accf_bar(a), (batch >> 1) & 1, abort);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            float v[32];
+            tmem_ld32(lane_addr + a * 128, v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) sum[i] += v[i];
+            tmem_ld32(lane_addr + a * 128 + 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) sum[32 + i] += v[i];
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(a));
+        }
+        const int r = quarter * 32 + lane, m = m0 + r;
+        const int b = m / pr.HoWo, rem = m % pr.HoWo;
+        if (ok && b < pr.B && m < pr.M) {
+            const size_t plane = (size_t)pr.G * pr.M * pr.N2;
+            __nv_bfloat16 *row = pr.Dh + ((size_t)g * pr.M + m) * pr.N2 + n0 + half * 64;
+            const float *grow = pr.gout + (size_t)b * pr.O * pr.HoWo + rem;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; c8++) {
+                uint32_t t0[4], t1[4], t2[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int j = c8 * 8 + e * 2;
+                    const int o0 = (n0 + half * 64 + j) % pr.Opad, o1 = (n0 + half * 64 + j + 1) % pr.Opad;
+                    const float g0 = o0 < pr.O ? __ldg(grow + (size_t)o0 * pr.HoWo) : 0.0f;
+                    const float g1 = o1 < pr.O ? __ldg(grow + (size_t)o1 * pr.HoWo) : 0.0f;
+                    const float v0 = g0 * expf(-sum[j]), v1 = g1 * expf(-sum[j + 1]);
+                    // three-term bf16 split of both values at once (cvt.rn.bf16x2.f32)
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                    const uint32_t p0 = *(uint32_t *)&h;
+                    const float r0 = v0 - __uint_as_float(p0 << 16), r1 = v1 - __uint_as_float(p0 & 0xffff0000u);
+                    h = __floats2bfloat162_rn(r0, r1);
+                    const uint32_t p1 = *(uint32_t *)&h;
+                    const float s0 = r0 - __uint_as_float(p1 << 16), s1 = r1 - __uint_as_float(p1 & 0xffff0000u);
+                    h = __floats2bfloat162_rn(s0, s1);
+                    t0[e] = p0; t1[e] = p1; t2[e] = *(uint32_t *)&h;
+                }
+                *(uint4 *)(row + c8 * 8) = make_uint4(t0[0], t0[1], t0[2], t0[3]);
+                *(uint4 *)(row + plane + c8 * 8) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
+                *(uint4 *)(row + 2 * plane + c8 * 8) = make_uint4(t2[0], t2[1], t2[2], t2[3]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -343,6 +504,77 @@ int launch_tc_dgrad(const MmaDims &d, int Cn, const void *Dh, const void *wd, fl
     const unsigned ptiles = tile.nb > 1 ? (unsigned)((d.B + tile.nb - 1) / tile.nb) : (unsigned)(d.B * pr.tiles_x * pr.tiles_y);
     dim3 grid(ptiles, (unsigned)(Cn / 128), 1);
     tc_dgrad_kernel<<<grid, TC_THREADS, TC_SMEM, s>>>(map_d, map_w, pr);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+// Position tile over an Ho x Wo image: nb images x bh rows x all Wo columns = 128 positions.
+static bool position_tile(int H, int W, int *bh, int *nb) {
+    if (W < 1 || W > 128 || (W & (W - 1)) != 0) return false;
+    if (H * W >= 128) {
+        *bh = 128 / W; *nb = 1;
+        return H % *bh == 0;
+    }
+    *bh = H;
+    if (128 % (W * H) != 0) return false;
+    *nb = 128 / (W * H);
+    return *nb <= 256;
+}
+
+bool tc_forward_plan(const MmaDims &d, TcTile *tile) {
+    static const bool disabled = std::getenv("GEO_SC_NO_TCGEN05") != nullptr;
+    if (disabled || !encode_fn() || d.linear) return false;
+    if (d.N2 % 128 != 0 || d.Cp % 64 != 0) return false;
+    if (d.mode != GEO_SC_MODE_1D && d.mode != GEO_SC_MODE_2D && d.mode != GEO_SC_MODE_FULL_OR) return false;
+    if (d.Kp != d.taps * d.Cp) return false;
+    if ((long long)d.M * d.N2 * 2 >= (1LL << 40)) return false;
+    int bh, nb;
+    if (!position_tile(d.Ho, d.Wo, &bh, &nb)) return false;
+    tile->bw = d.Wo; tile->bh = bh; tile->nb = nb;
+    return true;
+}
+
+int launch_tc_forward(const MmaDims &d, const void *apad, const void *wb, const float *gout, void *Dh, const int *flag,
+                      cudaStream_t s) {
+    TcTile tile;
+    if (!tc_forward_plan(d, &tile)) return fail(GEO_SC_ERR_UNSUPPORTED, "shape not served by the tcgen05 forward kernel");
+    CUtensorMap map_a, map_w;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)d.Cp, (cuuint64_t)d.Wp, (cuuint64_t)d.Hp, (cuuint64_t)d.B};
+        const cuuint64_t strides[3] = {(cuuint64_t)d.Cp * 2, (cuuint64_t)d.Wp * d.Cp * 2, (cuuint64_t)d.Hp * d.Wp * d.Cp * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)tile.bw, (cuuint32_t)tile.bh, (cuuint32_t)tile.nb};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = encode_fn()(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(apad), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (activations) failed: %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)d.Kp, (cuuint64_t)d.G * d.N2};
+        const cuuint64_t strides[1] = {(cuuint64_t)d.Kp * 2};
+        const cuuint32_t box[2] = {64, 128};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode_fn()(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(wb), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (Wb) failed: %d", (int)r);
+    }
+    TcForwardParams pr;
+    pr.gout = gout; pr.Dh = (__nv_bfloat16 *)Dh; pr.inexact = flag;
+    pr.B = d.B; pr.O = d.O; pr.Opad = d.Opad; pr.Ho = d.Ho; pr.Wo = d.Wo; pr.HoWo = d.HoWo; pr.M = d.M; pr.N2 = d.N2; pr.G = d.G;
+    pr.K3 = d.K3; pr.mode = d.mode;
+    pr.cpb = d.Cp / 64; pr.nkb = d.taps * pr.cpb;
+    pr.bh = tile.bh; pr.nb = tile.nb;
+    pr.tiles_y = tile.nb > 1 ? 1 : d.Ho / tile.bh;
+    static PerDeviceOnce once;
+    int rc = per_device_once(once, []() -> int {
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(tc_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TF_SMEM));
+        return GEO_SC_OK;
+    });
+    if (rc) return rc;
+    const unsigned ptiles = tile.nb > 1 ? (unsigned)((d.B + tile.nb - 1) / tile.nb) : (unsigned)(d.B * pr.tiles_y);
+    dim3 grid(ptiles, (unsigned)(d.N2 / 128), (unsigned)d.G);
+    tc_forward_kernel<<<grid, TC_THREADS, TF_SMEM, s>>>(map_a, map_w, pr);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

@@ -15,6 +15,11 @@ struct TcTile {
 bool tc_dgrad_plan(const MmaDims &d, int Cn, TcTile *tile);
 int launch_tc_dgrad(const MmaDims &d, int Cn, const void *Dh, const void *wd, float *grad_act, const int *flag,
                     cudaStream_t s);
+// Whether the forward product (and D = gout * exp(-y)) of this layer runs on tcgen05: input channels a multiple of
+// 64, column count a multiple of 128, output width a power of two.
+bool tc_forward_plan(const MmaDims &d, TcTile *tile);
+int launch_tc_forward(const MmaDims &d, const void *apad, const void *wb, const float *gout, void *Dh, const int *flag,
+                      cudaStream_t s);
 // Bounded mbarrier waits that ran out since the library was loaded (0 in a healthy run).
 int tc_error_count(int *count);
 

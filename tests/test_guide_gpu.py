@@ -230,6 +230,9 @@ WIDE_CASES = [
     ((2, 128, 16, 16), (32, 128, 5, 5), (2, 2)),      # 5x5 taps
     ((9, 160, 4, 4), (48, 160, 3, 3), (1, 1)),        # eight 4x4 images per tile, channels padded to 256
     ((1, 128, 32, 32), (32, 128, 3, 3), (1, 1)),      # four rows of a 32-wide image per tile
+    ((2, 128, 16, 16), (64, 128, 5, 5), (2, 2)),      # 128 columns: the forward product runs on tcgen05 too
+    ((9, 192, 4, 4), (128, 192, 3, 3), (1, 1)),       # 4x4 images, 256 columns, three 64-channel blocks per tap
+    ((5, 64, 2, 2), (64, 64, 3, 3), (1, 1)),          # 2x2 images, 32 per tile; forward on tcgen05, gradient not
 ]
 
 
