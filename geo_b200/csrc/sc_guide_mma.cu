@@ -896,11 +896,13 @@ MmaPlan mma_plan(const MmaDims &d) {
     p.wd_bytes = align_up((size_t)p.Cn * d.K2 * d.K3 * d.N2 * 2, 256);
     const long long tiles = (long long)d.G * ((d.Kp + 63) / 64) * (d.N2 / 64);
     long long S = (long long)sm_count() * 8 / tiles;   // at most two full waves of four resident CTAs per SM, no third
-    const long long maxS = (d.M + WP - 1) / WP;
+    // slices are whole stages of the weight-gradient kernel: 32 positions (mma.sync), 64 for wide layers (tcgen05)
+    const int wpos = d.Cp % 128 == 0 && d.N2 % 128 == 0 ? 64 : WP;
+    const long long maxS = (d.M + wpos - 1) / wpos;
     if (S > maxS) S = maxS;
     if (S < 1) S = 1;
     long long len = (d.M + S - 1) / S;
-    len = (len + WP - 1) / WP * WP;
+    len = (len + wpos - 1) / wpos * wpos;
     p.slice_len = (int)len;
     p.S = (int)((d.M + len - 1) / len);
     // the fused kernel: two resident CTAs per SM, each writing two slices
@@ -1018,7 +1020,13 @@ int launch_mma_backward(const Geometry &g, const float *act, const float *weight
         mma_forward_kernel<1><<<grid, 256, smem, s>>>(d, apad, wb, gout, Dh, vec_ok, flag);
         GEO_CUDA_CHECK(cudaGetLastError());
     }
-    if (grad_weight) {
+    TcTile wtile;
+    if (grad_weight && tc_wgrad_plan(d, p.slice_len, &wtile)) {   // wide layers: tcgen05 (sc_guide_tc.cu)
+        int rc = launch_tc_wgrad(d, apad, Dh, partial, p.S, p.slice_len, flag, s);
+        if (rc) return rc;
+        launch_wgrad_reduce(d, p.S, partial, weight, grad_weight, flag, s);
+        GEO_CUDA_CHECK(cudaGetLastError());
+    } else if (grad_weight) {
         constexpr size_t smem = (size_t)WSTG * (WP * 128 * 4);
         static bool done[64] = {};
         int rc = opt_in_smem(mma_wgrad_kernel, smem, done);

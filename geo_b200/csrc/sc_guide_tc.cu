@@ -420,6 +420,157 @@ tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
 }
 
+// ---- weight gradient ----------------------------------------------------------------------------------------
+// partial[slice][g][k'][n2] = sum over the slice's positions m of a[pos(m) + tap][c] * D_term[g][m][n2] over the
+// three terms: the contraction runs over positions, so both operands are "MN-major" for the tensor core -- a stage
+// holds 64 positions as rows of 128 bytes, [64 m][64 channels] twice for the 128 members k' = (tap, c0 .. c0 + 127)
+// of the tile and [64 m][64 columns] twice per term for its 128 columns, exactly as the tensor-map copies deliver
+// them.  Descriptor: 128-byte swizzle, leading-byte-offset = distance between the two 64-wide blocks (8 KB),
+// stride-byte-offset = distance between groups of eight positions (1 KB); an MMA consumes 16 positions (2 KB).
+// The epilogue is the one of the activation-gradient kernel: the sum over positions is long and of mixed sign, so
+// every stage's accumulator is added into fp32 registers.  One CTA per (slice of positions, 128 members, 128 columns,
+// group); mma_wgrad_reduce_kernel adds the slices and applies the sign masks.
+constexpr int TW_BLOCK_BYTES = 64 * 128;                       // 64 positions x 64 bf16
+constexpr int TW_STAGE_BYTES = 8 * TW_BLOCK_BYTES;             // A: 2 blocks, D: 3 terms x 2 blocks
+constexpr int TW_SMEM = TC_STAGES * TW_STAGE_BYTES + 1024;
+constexpr uint32_t TW_IDESC = TC_IDESC | (1u << 15) | (1u << 16);   // A and B MN-major
+
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16_mn(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(TW_IDESC), "r"(accumulate)
+                 : "memory");
+}
+
+struct TcWgradParams {
+    float *partial;           // [S][G][Kp][N2]
+    const int *inexact;
+    int M, Ho, Wo, HoWo, N2, G, Kp, Cp, K3, mode;
+    int slice_len;            // positions per slice, a multiple of 64
+    int n2tiles;              // N2 / 128
+    uint32_t lbo, sbo;
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_d, TcWgradParams pr) {
+    if (*pr.inexact) return;
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * TC_STAGES + 4];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    unsigned char *tiles = (unsigned char *)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t tiles_s = smem_u32(tiles);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (TC_STAGES + s); };
+    auto accf_bar = [&](int a) { return bar0 + 8u * (2 * TC_STAGES + a); };
+    auto acce_bar = [&](int a) { return bar0 + 8u * (2 * TC_STAGES + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < TC_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abort = &abort_flag;
+
+    const int slice = blockIdx.x, k0 = blockIdx.y * 128;
+    const int g = blockIdx.z / pr.n2tiles, n0 = (blockIdx.z % pr.n2tiles) * 128;
+    const int tap = k0 / pr.Cp, c0 = k0 % pr.Cp;
+    int ky, kx;
+    if (pr.mode == GEO_SC_MODE_1D) { ky = tap; kx = g; }
+    else if (pr.mode == GEO_SC_MODE_2D) { ky = g / pr.K3; kx = g % pr.K3; }
+    else { ky = tap / pr.K3; kx = tap % pr.K3; }
+    const int mbeg = slice * pr.slice_len, mend = min(pr.M, mbeg + pr.slice_len);
+    const int n_iters = (mend - mbeg + 63) / 64;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < n_iters; it++) {
+                const int s = it % TC_STAGES;
+                if (!mbar_wait(empty_bar(s), ((it / TC_STAGES) & 1) ^ 1, abort)) break;
+                mbar_expect_tx(full_bar(s), TW_STAGE_BYTES);
+                const int m0 = mbeg + it * 64;
+                const int b0 = m0 / pr.HoWo, oy0 = (m0 % pr.HoWo) / pr.Wo;
+                const uint32_t dst = tiles_s + (uint32_t)s * TW_STAGE_BYTES;
+                tma_load_4d(dst, &map_a, full_bar(s), c0, kx, oy0 + ky, b0);
+                tma_load_4d(dst + TW_BLOCK_BYTES, &map_a, full_bar(s), c0 + 64, kx, oy0 + ky, b0);
+                for (int term = 0; term < 3; term++)
+                    for (int h = 0; h < 2; h++)
+                        tma_load_5d(dst + (2 + term * 2 + h) * TW_BLOCK_BYTES, &map_d, full_bar(s), n0 + h * 64, 0, oy0, b0,
+                                    term * pr.G + g);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int it = 0; it < n_iters; it++) {
+                const int s = it % TC_STAGES, a = it & 1;
+                if (!mbar_wait(full_bar(s), (it / TC_STAGES) & 1, abort)) break;
+                if (!mbar_wait(acce_bar(a), ((it >> 1) & 1) ^ 1, abort)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t st = tiles_s + (uint32_t)s * TW_STAGE_BYTES;
+                for (int term = 0; term < 3; term++) {
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {   // 16 positions = two groups of eight rows = 2 KB further
+                        const uint64_t adesc = umma_desc_mn(st + k * 2048, pr.lbo, pr.sbo);
+                        const uint64_t bdesc = umma_desc_mn(st + (2 + term * 2) * TW_BLOCK_BYTES + k * 2048, pr.lbo, pr.sbo);
+                        umma_bf16_mn(tmem_base + a * 128, adesc, bdesc, (term | k) != 0);
+                    }
+                }
+                umma_commit(empty_bar(s));
+                umma_commit(accf_bar(a));
+            }
+        }
+    } else {
+        const int ew = warp - 2, quarter = warp & 3, half = ew >> 2;
+        float sum[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) sum[i] = 0.f;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 64;
+        bool ok = true;
+        for (int it = 0; it < n_iters; it++) {
+            const int a = it & 1;
+            ok = mbar_wait(accf_bar(a), (it >> 1) & 1, abort);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            float v[32];
+            tmem_ld32(lane_addr + a * 128, v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) sum[i] += v[i];
+            tmem_ld32(lane_addr + a * 128 + 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) sum[32 + i] += v[i];
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(a));
+        }
+        if (ok) {
+            const int k = k0 + quarter * 32 + lane;   // accumulator row = member of the tile
+            float *dst = pr.partial + (((size_t)slice * pr.G + g) * pr.Kp + k) * pr.N2 + n0 + half * 64;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) *(float4 *)(dst + j) = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -575,6 +726,71 @@ int launch_tc_forward(const MmaDims &d, const void *apad, const void *wb, const 
     const unsigned ptiles = tile.nb > 1 ? (unsigned)((d.B + tile.nb - 1) / tile.nb) : (unsigned)(d.B * pr.tiles_y);
     dim3 grid(ptiles, (unsigned)(d.N2 / 128), (unsigned)d.G);
     tc_forward_kernel<<<grid, TC_THREADS, TF_SMEM, s>>>(map_a, map_w, pr);
+    GEO_CUDA_CHECK(cudaGetLastError());
+    return GEO_SC_OK;
+}
+
+bool tc_wgrad_plan(const MmaDims &d, int slice_len, TcTile *tile) {
+    static const bool disabled = std::getenv("GEO_SC_NO_TCGEN05") != nullptr;
+    if (disabled || !encode_fn()) return false;
+    if (d.N2 % 128 != 0 || d.Cp % 128 != 0 || d.Kp != d.taps * d.Cp) return false;
+    if (d.mode != GEO_SC_MODE_1D && d.mode != GEO_SC_MODE_2D && d.mode != GEO_SC_MODE_FULL_OR) return false;
+    if (slice_len % 64 != 0 || d.M % 64 != 0) return false;
+    const int W = d.Wo, H = d.Ho;
+    if (W < 1 || W > 64 || (W & (W - 1)) != 0) return false;
+    int bh, nb;
+    if (H * W >= 64) { bh = 64 / W; nb = 1; if (H % bh != 0) return false; }
+    else { bh = H; if (64 % (W * H) != 0) return false; nb = 64 / (W * H); }
+    if ((long long)d.M * d.N2 * 2 >= (1LL << 40)) return false;
+    tile->bw = W; tile->bh = bh; tile->nb = nb;
+    return true;
+}
+
+int launch_tc_wgrad(const MmaDims &d, const void *apad, const void *Dh, float *partial, int S, int slice_len, const int *flag,
+                    cudaStream_t s) {
+    TcTile tile;
+    if (!tc_wgrad_plan(d, slice_len, &tile)) return fail(GEO_SC_ERR_UNSUPPORTED, "shape not served by the tcgen05 weight-gradient kernel");
+    CUtensorMap map_a, map_d;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)d.Cp, (cuuint64_t)d.Wp, (cuuint64_t)d.Hp, (cuuint64_t)d.B};
+        const cuuint64_t strides[3] = {(cuuint64_t)d.Cp * 2, (cuuint64_t)d.Wp * d.Cp * 2, (cuuint64_t)d.Hp * d.Wp * d.Cp * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)tile.bw, (cuuint32_t)tile.bh, (cuuint32_t)tile.nb};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = encode_fn()(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(apad), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (activations) failed: %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[5] = {(cuuint64_t)d.N2, (cuuint64_t)d.Wo, (cuuint64_t)d.Ho, (cuuint64_t)d.B, (cuuint64_t)(3 * d.G)};
+        const cuuint64_t strides[4] = {(cuuint64_t)d.N2 * 2, (cuuint64_t)d.Wo * d.N2 * 2, (cuuint64_t)d.HoWo * d.N2 * 2,
+                                       (cuuint64_t)d.M * d.N2 * 2};
+        const cuuint32_t box[5] = {64, (cuuint32_t)tile.bw, (cuuint32_t)tile.bh, (cuuint32_t)tile.nb, 1};
+        const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUresult r = encode_fn()(&map_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void *>(Dh), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (D) failed: %d", (int)r);
+    }
+    TcWgradParams pr;
+    pr.partial = partial; pr.inexact = flag;
+    pr.M = d.M; pr.Ho = d.Ho; pr.Wo = d.Wo; pr.HoWo = d.HoWo; pr.N2 = d.N2; pr.G = d.G; pr.Kp = d.Kp; pr.Cp = d.Cp; pr.K3 = d.K3;
+    pr.mode = d.mode;
+    pr.slice_len = slice_len;
+    pr.n2tiles = d.N2 / 128;
+    // leading-byte-offset: from one 64-wide block of members (or columns) to the next; stride-byte-offset: from one
+    // group of eight positions to the next
+    static const bool swapped = std::getenv("GEO_SC_TC_WGRAD_SWAP") != nullptr;
+    pr.lbo = swapped ? 1024 : TW_BLOCK_BYTES;
+    pr.sbo = swapped ? TW_BLOCK_BYTES : 1024;
+    static PerDeviceOnce once;
+    int rc = per_device_once(once, []() -> int {
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TW_SMEM));
+        return GEO_SC_OK;
+    });
+    if (rc) return rc;
+    dim3 grid((unsigned)S, (unsigned)(d.Kp / 128), (unsigned)(d.G * pr.n2tiles));
+    tc_wgrad_kernel<<<grid, TC_THREADS, TW_SMEM, s>>>(map_a, map_d, pr);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }

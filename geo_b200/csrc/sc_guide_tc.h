@@ -20,6 +20,11 @@ int launch_tc_dgrad(const MmaDims &d, int Cn, const void *Dh, const void *wd, fl
 bool tc_forward_plan(const MmaDims &d, TcTile *tile);
 int launch_tc_forward(const MmaDims &d, const void *apad, const void *wb, const float *gout, void *Dh, const int *flag,
                       cudaStream_t s);
+// Whether the weight-gradient GEMM runs on tcgen05: input channels a multiple of 128, column count a multiple of
+// 128, output width a power of two up to 64, slices of whole 64-position blocks.
+bool tc_wgrad_plan(const MmaDims &d, int slice_len, TcTile *tile);
+int launch_tc_wgrad(const MmaDims &d, const void *apad, const void *Dh, float *partial, int S, int slice_len, const int *flag,
+                    cudaStream_t s);
 // Bounded mbarrier waits that ran out since the library was loaded (0 in a healthy run).
 int tc_error_count(int *count);
 

@@ -233,6 +233,8 @@ WIDE_CASES = [
     ((2, 128, 16, 16), (64, 128, 5, 5), (2, 2)),      # 128 columns: the forward product runs on tcgen05 too
     ((9, 192, 4, 4), (128, 192, 3, 3), (1, 1)),       # 4x4 images, 256 columns, three 64-channel blocks per tap
     ((5, 64, 2, 2), (64, 64, 3, 3), (1, 1)),          # 2x2 images, 32 per tile; forward on tcgen05, gradient not
+    ((4, 256, 8, 8), (128, 256, 3, 3), (1, 1)),       # all three GEMMs on tcgen05; weight gradient: one image per stage
+    ((16, 128, 2, 2), (64, 128, 3, 3), (1, 1)),       # weight gradient: sixteen 2x2 images per stage
 ]
 
 
