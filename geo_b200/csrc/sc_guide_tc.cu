@@ -780,9 +780,8 @@ int launch_tc_wgrad(const MmaDims &d, const void *apad, const void *Dh, float *p
     pr.n2tiles = d.N2 / 128;
     // leading-byte-offset: from one 64-wide block of members (or columns) to the next; stride-byte-offset: from one
     // group of eight positions to the next
-    static const bool swapped = std::getenv("GEO_SC_TC_WGRAD_SWAP") != nullptr;
-    pr.lbo = swapped ? 1024 : TW_BLOCK_BYTES;
-    pr.sbo = swapped ? TW_BLOCK_BYTES : 1024;
+    pr.lbo = TW_BLOCK_BYTES;
+    pr.sbo = 1024;
     static PerDeviceOnce once;
     int rc = per_device_once(once, []() -> int {
         GEO_CUDA_CHECK(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TW_SMEM));
