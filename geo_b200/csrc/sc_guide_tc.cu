@@ -272,9 +272,11 @@ tc_dgrad_kernel(const __grid_constant__ CUtensorMap map_d, const __grid_constant
 // Stages of 64 members: a 128 x 64 tile of the padded NHWC activations, fetched by one 4-d tensor-map copy whose
 // coordinates carry the tap's offset, and a 128 x 64 tile of Wb.  Two stages (eight MMAs, 128 members) make one
 // accumulator batch, flushed into the epilogue warps' fp32 sums like in the kernel above.
-constexpr int TF_STAGES = 6;
+constexpr int TF_STAGES = 4;
 constexpr int TF_STAGE_BYTES = 2 * TC_TILE_BYTES;
-constexpr int TF_SMEM = TF_STAGES * TF_STAGE_BYTES + 1024;
+constexpr int TF_GOUT_BYTES = 128 * 128 * 4;                       // gout of the tile: 128 channels x 128 positions fp32
+constexpr int TF_SMEM = TF_STAGES * TF_STAGE_BYTES + TF_GOUT_BYTES + 1024;
+static_assert(TF_STAGES * TF_STAGE_BYTES >= 6 * TC_TILE_BYTES, "the stage buffers double as staging for the three terms of D");
 
 struct TcForwardParams {
     const float *gout;        // [B][O][Ho][Wo]
@@ -285,13 +287,27 @@ struct TcForwardParams {
     int nkb;                  // stages: taps * cpb
     int bh, nb;               // position tile: nb images x bh rows x Wo columns = 128 positions
     int tiles_y;              // tiles per image (nb == 1), else 1
+    int staged;               // gout arrives by TMA and D leaves by TMA through shared memory (else plain loads / stores)
+    int ppi, ob;              // staged: positions per image in the tile, channels in the gout box
 };
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];\n"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1)
-tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TcForwardParams pr) {
+tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                  const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_o, TcForwardParams pr) {
     if (*pr.inexact) return;
     extern __shared__ unsigned char tc_smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * TF_STAGES + 4];   // full, empty, acc_full[2], acc_empty[2]
+    __shared__ __align__(8) uint64_t bars[2 * TF_STAGES + 5];   // full, empty, acc_full[2], acc_empty[2], gout
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     unsigned char *tiles = (unsigned char *)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -307,6 +323,7 @@ tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         abort_flag = 0;
         for (int s = 0; s < TF_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 8); }
+        mbar_init(bar0 + 8u * (2 * TF_STAGES + 4), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -318,6 +335,8 @@ tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abort = &abort_flag;
+    const uint32_t gout_bar = bar0 + 8u * (2 * TF_STAGES + 4);
+    unsigned char *gout_tile = tiles + TF_STAGES * TF_STAGE_BYTES;
 
     int b0, oy0;
     if (pr.nb > 1) { b0 = blockIdx.x * pr.nb; oy0 = 0; }
@@ -328,6 +347,10 @@ tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
+            if (pr.staged) {   // gout of the tile, [image][channel][position]; channels past c_out arrive as zeros
+                mbar_expect_tx(gout_bar, (uint32_t)(pr.ob * 128 * 4));
+                tma_load_3d(smem_u32(gout_tile), &map_g, gout_bar, oy0 * pr.Wo, n0 % pr.Opad, b0);
+            }
             for (int kb = 0; kb < nkb; kb++) {
                 const int s = kb % TF_STAGES;
                 if (!mbar_wait(empty_bar(s), ((kb / TF_STAGES) & 1) ^ 1, abort)) break;
@@ -382,7 +405,46 @@ tc_forward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         const int r = quarter * 32 + lane, m = m0 + r;
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
-        if (ok && b < pr.B && m < pr.M) {
+        if (pr.staged) {
+            // gout from shared memory, D through shared memory: the thread's 64 columns are one 128-byte row of the
+            // (term, half) box, written in the 128-byte swizzle that the tensor-map store undoes; the stage buffers
+            // are free (every MMA that read them has completed before the last accumulator was handed over)
+            if (ok) ok = mbar_wait(gout_bar, 0, abort);
+            const float *gs = (const float *)gout_tile + (size_t)(r / pr.ppi) * pr.ob * pr.ppi + r % pr.ppi;
+            if (ok) {
+#pragma unroll
+                for (int c8 = 0; c8 < 8; c8++) {
+                    uint32_t t0[4], t1[4], t2[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int j = c8 * 8 + e * 2;
+                        const int o0 = (half * 64 + j) % pr.ob, o1 = (half * 64 + j + 1) % pr.ob;
+                        const float v0 = gs[o0 * pr.ppi] * expf(-sum[j]), v1 = gs[o1 * pr.ppi] * expf(-sum[j + 1]);
+                        __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                        const uint32_t p0 = *(uint32_t *)&h;
+                        const float r0 = v0 - __uint_as_float(p0 << 16), r1 = v1 - __uint_as_float(p0 & 0xffff0000u);
+                        h = __floats2bfloat162_rn(r0, r1);
+                        const uint32_t p1 = *(uint32_t *)&h;
+                        const float s0 = r0 - __uint_as_float(p1 << 16), s1 = r1 - __uint_as_float(p1 & 0xffff0000u);
+                        h = __floats2bfloat162_rn(s0, s1);
+                        t0[e] = p0; t1[e] = p1; t2[e] = *(uint32_t *)&h;
+                    }
+                    unsigned char *row = tiles + (size_t)half * TC_TILE_BYTES + r * 128 + ((c8 ^ (r & 7)) << 4);
+                    *(uint4 *)(row) = make_uint4(t0[0], t0[1], t0[2], t0[3]);
+                    *(uint4 *)(row + 2 * TC_TILE_BYTES) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
+                    *(uint4 *)(row + 4 * TC_TILE_BYTES) = make_uint4(t2[0], t2[1], t2[2], t2[3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("bar.sync 1, 256;\n" ::: "memory");   // the eight epilogue warps
+            if (ew == 0 && lane == 0 && !*abort) {
+                for (int term = 0; term < 3; term++)
+                    for (int hh = 0; hh < 2; hh++)
+                        tma_store_3d(&map_o, tiles_s + (uint32_t)(term * 2 + hh) * TC_TILE_BYTES, n0 + hh * 64, m0, term * pr.G + g);
+                asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // shared memory is read out before the CTA may leave
+            }
+        } else if (ok && b < pr.B && m < pr.M) {
             const size_t plane = (size_t)pr.G * pr.M * pr.N2;
             __nv_bfloat16 *row = pr.Dh + ((size_t)g * pr.M + m) * pr.N2 + n0 + half * 64;
             const float *grow = pr.gout + (size_t)b * pr.O * pr.HoWo + rem;
@@ -710,7 +772,28 @@ int launch_tc_forward(const MmaDims &d, const void *apad, const void *wb, const 
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (Wb) failed: %d", (int)r);
     }
+    // gout arrives by TMA when the positions of an image inside the tile are at least 16 bytes; D leaves by TMA then
+    const int ppi = tile.nb > 1 ? d.HoWo : 128, ob = d.Opad < 128 ? d.Opad : 128;
+    const bool staged = ppi % 4 == 0 && ((uintptr_t)gout & 15) == 0 && (d.HoWo * 4) % 16 == 0;
+    CUtensorMap map_g = map_a, map_o = map_a;   // placeholders when not staged (never dereferenced)
+    if (staged) {
+        const cuuint64_t gdims[3] = {(cuuint64_t)d.HoWo, (cuuint64_t)d.O, (cuuint64_t)d.B};
+        const cuuint64_t gstrides[2] = {(cuuint64_t)d.HoWo * 4, (cuuint64_t)d.O * d.HoWo * 4};
+        const cuuint32_t gbox[3] = {(cuuint32_t)ppi, (cuuint32_t)ob, (cuuint32_t)tile.nb};
+        const cuuint32_t gestr[3] = {1, 1, 1};
+        CUresult r = encode_fn()(&map_g, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(gout), gdims, gstrides, gbox, gestr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (gout) failed: %d", (int)r);
+        const cuuint64_t odims[3] = {(cuuint64_t)d.N2, (cuuint64_t)d.M, (cuuint64_t)(3 * d.G)};
+        const cuuint64_t ostrides[2] = {(cuuint64_t)d.N2 * 2, (cuuint64_t)d.M * d.N2 * 2};
+        const cuuint32_t obox[3] = {64, 128, 1};
+        r = encode_fn()(&map_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, Dh, odims, ostrides, obox, gestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(GEO_SC_ERR_CUDA, "cuTensorMapEncodeTiled (D store) failed: %d", (int)r);
+    }
     TcForwardParams pr;
+    pr.staged = staged ? 1 : 0; pr.ppi = ppi; pr.ob = ob;
     pr.gout = gout; pr.Dh = (__nv_bfloat16 *)Dh; pr.inexact = flag;
     pr.B = d.B; pr.O = d.O; pr.Opad = d.Opad; pr.Ho = d.Ho; pr.Wo = d.Wo; pr.HoWo = d.HoWo; pr.M = d.M; pr.N2 = d.N2; pr.G = d.G;
     pr.K3 = d.K3; pr.mode = d.mode;
@@ -725,7 +808,7 @@ int launch_tc_forward(const MmaDims &d, const void *apad, const void *wb, const 
     if (rc) return rc;
     const unsigned ptiles = tile.nb > 1 ? (unsigned)((d.B + tile.nb - 1) / tile.nb) : (unsigned)(d.B * pr.tiles_y);
     dim3 grid(ptiles, (unsigned)(d.N2 / 128), (unsigned)d.G);
-    tc_forward_kernel<<<grid, TC_THREADS, TF_SMEM, s>>>(map_a, map_w, pr);
+    tc_forward_kernel<<<grid, TC_THREADS, TF_SMEM, s>>>(map_a, map_w, map_g, map_o, pr);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
