@@ -71,31 +71,34 @@ __global__ void __launch_bounds__(128, 3) accumulate_fullbin_kernel(FullBinParam
     const int m0 = blockIdx.x * 128, ct = blockIdx.y;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
-    // gather: thread t copies position t, all 32 words of a stage
-    int abase;
+    // gather: lane = word of the stage, warp w copies rows w, w + 4, ...: the 32 lanes of a copy instruction write the
+    // 32 words of one row (32 banks), where one row per lane would put the whole warp on two banks
+    __shared__ int s_abase[128];
     {
         int m = m0 + t;
         if (m >= pr.M) m = pr.M - 1;
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
-        abase = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+        s_abase[t] = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
     }
+    __syncthreads();
     const int st0 = (int)((long long)pr.NST * blockIdx.z / pr.splits);
     const int st1 = (int)((long long)pr.NST * (blockIdx.z + 1) / pr.splits);
     int ld = st0;
-    // member and pack of the first word of the next stage to load
-    int ld_k = (st0 * FB_STAGE_WORDS) / pr.P, ld_p = (st0 * FB_STAGE_WORDS) % pr.P;
+    const uint32_t word_byte = (uint32_t)frag_pos(lane) * 4;
     auto issue = [&]() {
         if (ld < st1) {
             const uint32_t a_s = smem_base + (uint32_t)((ld - st0) % FB_NSTAGE) * FB_STAGE_BYTES, b_s = a_s + FB_A_BYTES;
-            int k = ld_k, p = ld_p;
-#pragma unroll 4
-            for (int j = 0; j < FB_STAGE_WORDS; j++) {
-                // words past the last member read member 0 again; their weight words are zero
-                const int kk = k < pr.K ? k : 0;
-                cp4(a_s + row_byte(t, frag_pos(j) * 4), pr.as + (size_t)p * pr.pack_words + abase + __ldg(pr.aoff + kk * 4));
-                if (++p == pr.P) { p = 0; k++; }
+            // this lane's word of the stage: member k, pack p; words past the last member read member 0 (weights zero)
+            const int kw = ld * FB_STAGE_WORDS + lane;
+            int k = kw / pr.P;
+            const int p = kw - k * pr.P;
+            if (k >= pr.K) k = 0;
+            const uint32_t *src = pr.as + (size_t)p * pr.pack_words + __ldg(pr.aoff + k * 4);
+#pragma unroll 8
+            for (int i = 0; i < 32; i++) {
+                const int row = warp + 4 * i;
+                cp4(a_s + row_byte(row, word_byte), src + s_abase[row]);
             }
-            ld_k = k; ld_p = p;
             const uint4 *wsrc = (const uint4 *)(pr.wb + ((size_t)ct * pr.NST + ld) * 64 * FB_STAGE_WORDS);
 #pragma unroll
             for (int i = 0; i < 4; i++) {   // 64 rows x 8 chunks = 512 chunks of 16 bytes
