@@ -273,7 +273,7 @@ def run_native(args):
             "gpu_launches_source": ("kernels named geo::* in a CUPTI trace of one eager step" if traced else
                                     "per-call bookkeeping of the Python front end") + f": {per_step} per step",
             "clocks": clocks,
-            "roofline": {"bound": "int_alu", "kernel": "geo::accumulate_sorted_kernel / geo::accumulate_kernel (SC AND/OR/popcount)",
+            "roofline": {"bound": "int_alu", "kernel": "geo::accumulate_rows_kernel (conv2, conv3) / geo::accumulate_kernel (conv1, fc): SC AND/OR/popcount",
                          "achieved": achieved / 1e12, "peak": peak_lop3 / 1e12, "unit": "TLOP3/s",
                          "frac": achieved / peak_lop3 if peak_lop3 else None,
                          # achieved / frac use the definition's count (2 * MAC * packs).  The sign-sorted kernel
@@ -303,8 +303,8 @@ def run_native(args):
 
 
 # DRAM bytes per accumulate launch of the default workload (4-layer CNN, 256 images), mean of the four
-# layers' launches: 16.07 + 61.31 + 23.99 + 4.80 MB read, < 0.1 MB written (one ncu capture).
-ACC_DRAM_BYTES_PER_LAUNCH = 26.54e6
+# layers' launches: 16.07 + 61.35 + 24.04 + 4.80 MB read, < 0.1 MB written (one ncu capture).
+ACC_DRAM_BYTES_PER_LAUNCH = 26.56e6
 
 
 def run_vgg11(device, rank, world, dist, timer):
