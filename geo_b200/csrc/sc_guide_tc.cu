@@ -668,7 +668,7 @@ bool tc_dgrad_plan(const MmaDims &d, int Cn, TcTile *tile) {
         if (128 % (bw * bh) != 0) return false;
         nb = 128 / (bw * bh);
     }
-    if (bw > 256 || bh > 256 || nb > 256) return false;
+    if (bw > 256 || bh > 256 || nb > 256 || nb > d.B) return false;   // a box never exceeds the tensor it is cut from
     if ((long long)d.M * d.N2 * 2 >= (1LL << 40)) return false;
     tile->bw = bw; tile->bh = bh; tile->nb = nb;
     return true;
@@ -742,7 +742,7 @@ bool tc_forward_plan(const MmaDims &d, TcTile *tile) {
     if (d.Kp != d.taps * d.Cp) return false;
     if ((long long)d.M * d.N2 * 2 >= (1LL << 40)) return false;
     int bh, nb;
-    if (!position_tile(d.Ho, d.Wo, &bh, &nb)) return false;
+    if (!position_tile(d.Ho, d.Wo, &bh, &nb) || nb > d.B) return false;
     tile->bw = d.Wo; tile->bh = bh; tile->nb = nb;
     return true;
 }
@@ -824,6 +824,7 @@ bool tc_wgrad_plan(const MmaDims &d, int slice_len, TcTile *tile) {
     int bh, nb;
     if (H * W >= 64) { bh = 64 / W; nb = 1; if (H % bh != 0) return false; }
     else { bh = H; if (64 % (W * H) != 0) return false; nb = 64 / (W * H); }
+    if (nb > d.B) return false;
     if ((long long)d.M * d.N2 * 2 >= (1LL << 40)) return false;
     tile->bw = W; tile->bh = bh; tile->nb = nb;
     return true;
