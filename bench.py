@@ -273,7 +273,7 @@ def run_native(args):
             "gpu_launches_source": ("kernels named geo::* in a CUPTI trace of one eager step" if traced else
                                     "per-call bookkeeping of the Python front end") + f": {per_step} per step",
             "clocks": clocks,
-            "roofline": {"bound": "int_alu", "kernel": "geo::accumulate_rows_kernel (conv2, conv3) / geo::accumulate_kernel (conv1, fc): SC AND/OR/popcount",
+            "roofline": {"bound": "int_alu", "kernel": "geo::accumulate_rows_kernel (conv2, conv3) / geo::accumulate_short_kernel (conv1) / geo::accumulate_kernel (fc): SC AND/OR/popcount",
                          "achieved": achieved / 1e12, "peak": peak_lop3 / 1e12, "unit": "TLOP3/s",
                          "frac": achieved / peak_lop3 if peak_lop3 else None,
                          # achieved / frac use the definition's count (2 * MAC * packs).  The sign-sorted kernel

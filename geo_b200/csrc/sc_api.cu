@@ -7,6 +7,7 @@
 #include "sc_fullbin.h"
 #include "sc_guide_tc.h"
 #include "sc_rows.h"
+#include "sc_short.h"
 #include "sc_sorted.h"
 
 namespace geo {
@@ -140,13 +141,16 @@ void make_load_plan(int L, int tw, int lu, int lw, LoadPlan *plan) {
 static size_t wprep_dense_bytes(const Geometry &g) {
     return align_up(g.w_stream_words * 4, 256) + align_up(g.aoff_entries * 4, 256);
 }
-// dense streams, member offsets, then (long groups only) one sign-sorted section: the row-tile form where the
-// layer's geometry allows it, else the im2col form
+// dense streams, member offsets, then one section for the kernel that applies one logic op per weight: for long
+// groups the sign-sorted lists (the row-tile form where the layer's geometry allows it, else the im2col form), for
+// short groups the per-chunk sorted lists of sc_accumulate_short.cu
 static size_t wprep_bytes(const Geometry &g) {
     const FullBinPlan fb = fullbin_plan(g);
     if (fb.layout) return wprep_dense_bytes(g) + fb.bytes;   // full_bin: the weights packed for the binary GEMM
     const RowsPlan rp = rows_plan(g);
-    return wprep_dense_bytes(g) + (rp.layout ? rp.total() : sorted_plan(g).total());
+    if (rp.layout) return wprep_dense_bytes(g) + rp.total();
+    const SortedPlan so = sorted_plan(g);
+    return wprep_dense_bytes(g) + (so.layout ? so.total() : short_plan(g).total());
 }
 
 static int prepare_all(const Geometry &g, const float *weight, void *wprep, cudaStream_t s) {
@@ -157,6 +161,7 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
     if (fullbin_plan(g).layout) rc = launch_fullbin_pack(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     else if (rows_plan(g).layout) rc = launch_sort_rows(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     else if (sorted_plan(g).layout) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    else if (short_plan(g).layout) rc = launch_sort_short(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     return rc;
 }
 
@@ -169,6 +174,8 @@ static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wpr
     if (rp.eligible) return launch_accumulate_rows(g, as, (const char *)wprep + wprep_dense_bytes(g), out, s);
     if (!rp.layout && sorted_plan(g).eligible)
         return launch_accumulate_sorted(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
+    if (!rp.layout && !sorted_plan(g).layout && short_plan(g).eligible)
+        return launch_accumulate_short(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
     return launch_accumulate(g, as, ws, aoff, out, s);
 }
 static size_t astream_bytes(const Geometry &g) { return align_up(g.act_stream_words * 4, 256); }
@@ -232,7 +239,9 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes) {
     if (rc) return rc;
     if (!yes) return fail(GEO_SC_ERR_NULL, "yes is NULL");
     const RowsPlan rp = rows_plan(g);
-    *yes = rp.eligible || (!rp.layout && sorted_plan(g).eligible) ? 1 : 0;
+    const bool sorted = rp.eligible || (!rp.layout && sorted_plan(g).eligible);
+    const bool short_sorted = !rp.layout && !sorted_plan(g).layout && short_plan(g).eligible;
+    *yes = g.mode != GEO_SC_MODE_FULL_BIN && (sorted || short_sorted) ? 1 : 0;
     return GEO_SC_OK;
 }
 

@@ -149,11 +149,11 @@ size_t geo_sc_static_scratch_bytes(void);
 int geo_sc_conv2d_forward_static(const geo_sc_conv_desc *desc, const float *act_device, const float *weight_device,
                                  int32_t *out_device, void *stream);
 
-/* Which accumulation kernel serves this descriptor: *yes = 1 for the sign-sorted kernel (long groups:
- * the members of a group are sorted per four output channels by the signs of their weights when the
- * weights are prepared, and each weight costs one 32-bit logic op per activation word instead of the
- * two of the dense form), 0 for the dense kernel.  Results are identical; the figure matters only for
- * counting executed logic ops. */
+/* Which accumulation kernel serves this descriptor: *yes = 1 for a sign-sorted kernel (the members of a
+ * group, or of a 16-member chunk of it where groups are short, are sorted per four output channels by the
+ * signs of their weights when the weights are prepared, and each weight costs one 32-bit logic op per
+ * activation word instead of the two of the dense form), 0 for the dense kernel.  Results are identical;
+ * the figure matters only for counting executed logic ops. */
 int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
 
 /* ---- the three stages, for callers that cache weight streams across calls ---------

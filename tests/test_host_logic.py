@@ -61,11 +61,13 @@ def test_group_geometry_per_mode():
     assert _lib.group_geometry(d("full_or")) == (1, 180, 64, 64)
     assert _lib.group_geometry(d("2d_bin")) == (15, 12, 64, 64)              # groups = filter taps, members = channels
     assert _lib.group_geometry(d("full_bin")) == (180, 1, 64, 64)            # every filter element its own group
-    # which accumulate kernel a descriptor gets: long groups (>= 64 padded members) the sign-sorted one
+    # which accumulate kernel a descriptor gets: long groups (>= 64 padded members) the sign-sorted one, short
+    # groups the per-chunk sorted one (both one logic op per weight), tiny launches and full_bin neither
     big = lambda mode: _lib.make_desc(8, 32, 16, 16, 32, 5, 5, 128, mode, pad_h=2, pad_w=2)  # noqa: E731
     assert _lib.is_sign_sorted(big("1d_bin")) and _lib.is_sign_sorted(big("full_or"))
-    assert not _lib.is_sign_sorted(big("z_bin")) and not _lib.is_sign_sorted(big("2d_bin"))
-    assert not _lib.is_sign_sorted(d("1d_bin"))                               # 36 members per group: dense kernel
+    assert _lib.is_sign_sorted(big("z_bin")) and _lib.is_sign_sorted(big("2d_bin"))
+    assert not _lib.is_sign_sorted(big("full_bin"))
+    assert not _lib.is_sign_sorted(d("1d_bin"))                               # 70 positions: dense kernel
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 10, 3, 3, 32))[2:] == (16, 16)
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 32, 3, 3, 32))[2:] == (32, 32)
 

@@ -100,6 +100,38 @@ def test_random_shapes_modes_and_plans(cuda_device, oracle_lib):
     assert kernels == {True, False}
 
 
+SHORT_GROUP_CASES = [
+    # act, weight, pad, mode, z_unit, L: members per group as laid out / what the case is for
+    ((4, 3, 8, 8), (8, 3, 1, 3), (0, 1), "1d_bin", 1, 128),      # 3 -> 4 members, one stage per group
+    ((4, 2, 8, 8), (20, 2, 3, 3), (1, 1), "1d_bin", 1, 64),      # 6 -> 8
+    ((4, 3, 8, 8), (33, 3, 3, 3), (1, 1), "1d_bin", 1, 128),     # 9 -> 12, ragged c_out
+    ((4, 3, 10, 8), (32, 3, 5, 5), (2, 2), "1d_bin", 1, 128),    # 15 -> 16: first layer of the 4-layer CNN
+    ((3, 6, 9, 12), (16, 6, 5, 5), (2, 2), "z_bin", 1, 32),      # 25 -> 32: two chunks per group
+    ((3, 32, 8, 8), (40, 32, 3, 3), (1, 1), "yz_bin", 16, 256),  # 48: three chunks per group
+    ((3, 32, 8, 8), (12, 32, 3, 3), (1, 1), "full_or", 1, 128),  # 288 members, c_out padded to 16: six quads' worth of chunks
+    ((4, 130, 8, 8), (16, 130, 3, 3), (1, 1), "z_bin", 1, 256),  # P * G * 32 = 33 280: 32-bit running sums
+    ((3, 5, 7, 20), (16, 5, 3, 3), (0, 0), "2d_bin", 1, 64),     # ragged last position tile (M = 270)
+]
+
+
+@pytest.mark.parametrize("case", range(len(SHORT_GROUP_CASES)))
+def test_short_group_kernel_matches_oracle(cuda_device, oracle_lib, case):
+    """The sign-sorted kernel for short groups at every stage length (4, 8, 12, 16 members), with one and
+    several chunks per group, packed and 32-bit running sums, and zero weights (dropped from its lists)."""
+    from geo_b200 import _lib, ops
+
+    ashape, wshape, pad, mode, z, L = SHORT_GROUP_CASES[case]
+    a, w = _rand(ashape, wshape, 900 + case)
+    w.view(-1)[::5] = 0
+    kw = dict(z_unit=z, total_width=7, load_width=2, load_wait_w=2, load_wait_a=2)
+    d = ops.desc_for(a, w, L, mode, pad, **kw)
+    assert _lib.is_sign_sorted(d)
+    geom = _lib.group_geometry_full(d)
+    assert geom[2] < 64 or geom[4] == 16   # short groups as laid out, or a c_out padded to 16
+    y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, pad, **kw).cpu().numpy()
+    assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, pad_h=pad[0], pad_w=pad[1], **kw))
+
+
 def test_small_stream_lengths(cuda_device, oracle_lib):
     from geo_b200 import ops
 
