@@ -365,7 +365,7 @@ def run_layers(peak_lop3):
         rows.append({"config": name, "mode": r["mode"], "L": r["L"], "ms_accumulate": r["ms_accumulate"],
                      "ms_forward": r["ms_forward"], "sc_bitops_per_s": r["sc_bitops_per_s"],
                      "frac": r["frac_of_lop3_peak"], "executed_frac": r["executed_frac_of_lop3_peak"],
-                     "sign_sorted": r["sign_sorted"]})
+                     "sign_sorted": r["sign_sorted"], "kernel": r["kernel"]})
         torch.cuda.empty_cache()
     return {"unit": "fraction of the measured LOP3 peak (definition: 2*MAC*packs logic ops per forward)",
             "rows": rows, "reference_gpu_kernel": reference_gpu_kernel()}

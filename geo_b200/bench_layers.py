@@ -96,7 +96,7 @@ def run_config(name, batch=None, reps=10, peak=None, device="cuda:0", guide=Fals
     rate = lop3 / (t_c * 1e-3)
     G, K, NT, Opad = _lib.group_geometry(d)
     executed = ops.executed_lop3(d)
-    return {"config": name, "sign_sorted": bool(_lib.is_sign_sorted(d)),
+    return {"config": name, "kernel": _lib.accumulate_kernel(d), "sign_sorted": bool(_lib.is_sign_sorted(d)),
             "executed_frac_of_lop3_peak": executed / (t_c * 1e-3) / peak if peak else None, "act": list(ash), "weight": list(wsh), "L": L, "mode": mode, "groups": G, "members": K,
             "ms_weight_streams": t_w, "ms_act_streams": t_a, "ms_accumulate": t_c, "ms_forward": t_all,
             "ms_guide_backward": t_g, "guide_tflops": (6 * lop3 / (2 * ((L + 31) // 32)) * 2 / (t_g * 1e-3) / 1e12) if t_g else None,

@@ -27,8 +27,9 @@ struct AccParams {
     int32_t *out;         // [B][O][Ho][Wo]
     int M, O, Opad, HoWo, Wo, Wp;
     int P, G, K;          // K: members per group as laid out (padded to a multiple of 16)
-    int img_words;        // P*C*Hp*Wp
-    int pack_words;       // C*Hp*Wp
+    int img_words;        // words between images, between packs; factor on the member offsets (act_img_words ...)
+    int pack_words;
+    int aoff_mul;
     int splits;           // CTAs along grid.z sharing one output tile; > 1 => atomic accumulation
 };
 
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
 #pragma unroll
                 for (int i = 0; i < (KC + RSTEP - 1) / RSTEP; i++)
                     if (KC % RSTEP == 0 || r0 + i * RSTEP < KC)
-                        cp_async4(dst + (uint32_t)(i * RSTEP * MT) * 4, src + __ldg(aoff + r0 + i * RSTEP));
+                        cp_async4(dst + (uint32_t)(i * RSTEP * MT) * 4, src + __ldg(aoff + r0 + i * RSTEP) * pr.aoff_mul);
             }
 #pragma unroll
             for (int i = 0; i < WPASS; i++)
@@ -251,8 +252,9 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
     pr.as = astream; pr.ws = wstream; pr.aoff = aoff; pr.out = out;
     pr.M = (int)g.M; pr.O = g.O; pr.Opad = g.Opad; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
     pr.P = g.P; pr.G = g.G; pr.K = g.Kp;
-    pr.pack_words = g.C * g.Hp * g.Wp;
-    pr.img_words = g.P * pr.pack_words;
+    pr.pack_words = act_pack_words(g);
+    pr.img_words = act_img_words(g);
+    pr.aoff_mul = act_member_scale(g);
     pr.splits = 1;
     // Long groups use 32-member stages (half as many barriers per LOP3); short ones 16-member
     // stages, because a stage is always executed in full and its zero-filled tail rows are wasted.

@@ -60,7 +60,7 @@ struct FullBinParams {
     int32_t *out;           // [B][O][Ho][Wo]
     int M, O, HoWo, Wo, Wp;
     int P, K, KW, NST;      // K filter elements (members), KW = K * P words, NST = stages = ceil(KW / 32)
-    int img_words, pack_words;
+    int img_words, pack_words, aoff_mul;
     int splits;
 };
 
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(128, 3) accumulate_fullbin_kernel(FullBinParam
             int k = kw / pr.P;
             const int p = kw - k * pr.P;
             if (k >= pr.K) k = 0;
-            const uint32_t *src = pr.as + (size_t)p * pr.pack_words + __ldg(pr.aoff + k * 4);
+            const uint32_t *src = pr.as + (size_t)p * pr.pack_words + (size_t)__ldg(pr.aoff + k * 4) * pr.aoff_mul;
 #pragma unroll 8
             for (int i = 0; i < 32; i++) {
                 const int row = warp + 4 * i;
@@ -232,8 +232,9 @@ int launch_accumulate_fullbin(const Geometry &g, const uint32_t *astream, const 
     pr.as = astream; pr.aoff = aoff; pr.wb = (const uint32_t *)section; pr.out = out;
     pr.M = (int)g.M; pr.O = g.O; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
     pr.P = g.P; pr.K = g.G; pr.KW = fp.KW; pr.NST = fp.NST;
-    pr.pack_words = g.C * g.Hp * g.Wp;
-    pr.img_words = g.P * pr.pack_words;
+    pr.pack_words = act_pack_words(g);
+    pr.img_words = act_img_words(g);
+    pr.aoff_mul = act_member_scale(g);
     static PerDeviceOnce once;
     int rc = per_device_once(once, []() -> int {
         GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_fullbin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

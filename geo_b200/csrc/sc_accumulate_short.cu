@@ -38,7 +38,7 @@ struct ShortParams {
     int img_words, pack_words;
     int splits;
     uint32_t row_bytes;   // 1024, as a run-time value (see imad)
-    int four;
+    int four;   // bytes per unit of the member offset table: 4, times the batch in the position-fastest image
 };
 
 __device__ __forceinline__ void cp4(uint32_t smem_addr, const void *gptr) {
@@ -108,7 +108,9 @@ __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&ac
 }
 
 // PACKED: the running sums of two channels share a register as two 16-bit halves (P*G*32 <= 32767 required)
-template <int KC, int NSTAGE, int MINB, bool PACKED>
+// POSF: 1x1 images in the position-fastest stream image -- a member's 256 positions are 1 KB of consecutive words
+// and are copied 16 bytes at a time (batch a multiple of 4)
+template <int KC, int NSTAGE, int MINB, bool PACKED, bool POSF>
 __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(ShortParams pr) {
     constexpr int A_BYTES = KC * 1024, W_BYTES = 4 * KC * 16;
     constexpr int STAGE = A_BYTES + W_BYTES + 4 * kShortMetaBytes;
@@ -126,6 +128,9 @@ __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(Shor
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
         abase[j] = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
     }
+    // POSF: this thread copies positions [pf_base, pf_base + 4) of rows t / 64, t / 64 + 2, ...; a chunk past the
+    // batch is moved back inside it (its positions are never stored)
+    const int pf_base = min(m0 + (t & 63) * 4, pr.M - 4);
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
     // This CTA owns the (pack, group) pairs [pair0, pair1) of the P*G pairs; the sum over pairs is an integer
@@ -141,13 +146,21 @@ __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(Shor
             const uint32_t rows = smem_base + (uint32_t)(ld_s % NSTAGE) * STAGE;
             const int32_t *aoff = pr.aoff + ld_g * pr.K + ld_c * KC;
             const uint32_t *asrc = pr.as + (size_t)ld_p * pr.pack_words;
-            const uint32_t *s0 = asrc + abase[0], *s1 = asrc + abase[1];
-            const uint32_t d0 = rows + (uint32_t)t * 4;
+            if (POSF) {
+                const uint32_t *s0 = asrc + pf_base;
+                const uint32_t d0 = rows + (uint32_t)(t & 63) * 16;
 #pragma unroll
-            for (int r = 0; r < KC; r++) {
-                const int off = __ldg(aoff + r);
-                cp4(d0 + r * 1024, word_address(s0, off, pr.four));
-                cp4(d0 + r * 1024 + 512, word_address(s1, off, pr.four));
+                for (int r = 0; r < KC; r += 2)
+                    if (r + 1 < KC || t < 64) cp16(d0 + (r + (t >> 6)) * 1024, word_address(s0, __ldg(aoff + r + (t >> 6)), pr.four));
+            } else {
+                const uint32_t *s0 = asrc + abase[0], *s1 = asrc + abase[1];
+                const uint32_t d0 = rows + (uint32_t)t * 4;
+#pragma unroll
+                for (int r = 0; r < KC; r++) {
+                    const int off = __ldg(aoff + r);
+                    cp4(d0 + r * 1024, word_address(s0, off, pr.four));
+                    cp4(d0 + r * 1024 + 512, word_address(s1, off, pr.four));
+                }
             }
             const size_t gcq = ((size_t)ld_g * pr.NCH + ld_c) * pr.Q + q0;   // the CTA's four quads are contiguous
             if (t < 4 * KC) cp16(rows + A_BYTES + t * 16, pr.wl + ((size_t)ld_p * pr.G * pr.NCH * pr.Q + gcq) * KC + t);
@@ -299,12 +312,12 @@ __global__ void __launch_bounds__(128) sort_short_kernel(const uint32_t *__restr
     }
 }
 
-template <int KC, int NSTAGE, int MINB, bool PACKED>
+template <int KC, int NSTAGE, int MINB, bool PACKED, bool POSF>
 int launch_short(const Geometry &g, ShortParams pr, cudaStream_t s) {
     constexpr size_t SMEM = (size_t)NSTAGE * (KC * 1024 + 4 * KC * 16 + 4 * kShortMetaBytes);
     static PerDeviceOnce once;
     int rc = per_device_once(once, []() -> int {
-        GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_short_kernel<KC, NSTAGE, MINB, PACKED>,
+        GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_short_kernel<KC, NSTAGE, MINB, PACKED, POSF>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
         return GEO_SC_OK;
     });
@@ -323,7 +336,7 @@ int launch_short(const Geometry &g, ShortParams pr, cudaStream_t s) {
     pr.splits = (int)splits;
     grid.z = (unsigned)splits;
     if (splits > 1) GEO_CUDA_CHECK(cudaMemsetAsync(pr.out, 0, (size_t)g.M * g.O * sizeof(int32_t), s));
-    accumulate_short_kernel<KC, NSTAGE, MINB, PACKED><<<grid, kShThreads, SMEM, s>>>(pr);
+    accumulate_short_kernel<KC, NSTAGE, MINB, PACKED, POSF><<<grid, kShThreads, SMEM, s>>>(pr);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
@@ -335,9 +348,9 @@ ShortPlan short_plan(const Geometry &g) {
     sp.layout = g.mode != GEO_SC_MODE_FULL_BIN && (g.Kp < 64 || g.Opad % 32 != 0);
     // A CTA's tile is 256 positions x 16 channels: with fewer positions the dense kernel's smaller tiles win, and so
     // they do where consecutive positions are not consecutive words of the stream image (images narrower than four
-    // columns, linear layers): there a gathered word costs a memory sector, and the dense tile shares it among up to
-    // 64 channels.
-    sp.eligible = sp.layout && g.M >= 192 && g.Wo >= 4;
+    // columns): there a gathered word costs a memory sector, and the dense tile shares it among up to 64 channels.
+    // Linear layers (1x1 images) have the position-fastest image and qualify when 16-byte copies are aligned.
+    sp.eligible = sp.layout && g.M >= 192 && (g.Wo >= 4 || (g.pos_fast && g.B % 4 == 0));
     sp.KC = g.Kp < 16 ? g.Kp : 16;           // groups are laid out in multiples of 4 (up to 16 members) or of 16
     sp.NCH = g.Kp / sp.KC;
     sp.Q = g.Opad / 4;
@@ -364,17 +377,30 @@ int launch_accumulate_short(const Geometry &g, const uint32_t *astream, const in
     pr.meta = (const unsigned char *)section + sp.wl_bytes;
     pr.M = (int)g.M; pr.O = g.O; pr.Q = sp.Q; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
     pr.P = g.P; pr.G = g.G; pr.K = g.Kp; pr.NCH = sp.NCH;
-    pr.pack_words = g.C * g.Hp * g.Wp;
-    pr.img_words = g.P * pr.pack_words;
+    pr.pack_words = act_pack_words(g);
+    pr.img_words = act_img_words(g);
     pr.splits = 1;
-    pr.row_bytes = 1024; pr.four = 4;
+    pr.row_bytes = 1024; pr.four = 4 * act_member_scale(g);
     // with packed sums the kernel fits 128 registers: four CTAs per SM instead of three
     const bool packed = (long long)g.P * g.G * 32 <= 32767;
-    switch (sp.KC) {
-    case 4: return packed ? launch_short<4, 6, 4, true>(g, pr, s) : launch_short<4, 6, 3, false>(g, pr, s);
-    case 8: return packed ? launch_short<8, 5, 4, true>(g, pr, s) : launch_short<8, 6, 3, false>(g, pr, s);
-    case 12: return packed ? launch_short<12, 4, 4, true>(g, pr, s) : launch_short<12, 4, 3, false>(g, pr, s);
-    default: return packed ? launch_short<16, 3, 4, true>(g, pr, s) : launch_short<16, 4, 3, false>(g, pr, s);
+    const int variant = sp.KC * 4 + (packed ? 2 : 0) + (g.pos_fast ? 1 : 0);
+    switch (variant) {
+    case 4 * 4 + 0: return launch_short<4, 6, 3, false, false>(g, pr, s);
+    case 4 * 4 + 1: return launch_short<4, 6, 3, false, true>(g, pr, s);
+    case 4 * 4 + 2: return launch_short<4, 6, 4, true, false>(g, pr, s);
+    case 4 * 4 + 3: return launch_short<4, 6, 4, true, true>(g, pr, s);
+    case 8 * 4 + 0: return launch_short<8, 6, 3, false, false>(g, pr, s);
+    case 8 * 4 + 1: return launch_short<8, 6, 3, false, true>(g, pr, s);
+    case 8 * 4 + 2: return launch_short<8, 5, 4, true, false>(g, pr, s);
+    case 8 * 4 + 3: return launch_short<8, 5, 4, true, true>(g, pr, s);
+    case 12 * 4 + 0: return launch_short<12, 4, 3, false, false>(g, pr, s);
+    case 12 * 4 + 1: return launch_short<12, 4, 3, false, true>(g, pr, s);
+    case 12 * 4 + 2: return launch_short<12, 4, 4, true, false>(g, pr, s);
+    case 12 * 4 + 3: return launch_short<12, 4, 4, true, true>(g, pr, s);
+    case 16 * 4 + 0: return launch_short<16, 4, 3, false, false>(g, pr, s);
+    case 16 * 4 + 1: return launch_short<16, 4, 3, false, true>(g, pr, s);
+    case 16 * 4 + 2: return launch_short<16, 3, 4, true, false>(g, pr, s);
+    default: return launch_short<16, 3, 4, true, true>(g, pr, s);
     }
 }
 

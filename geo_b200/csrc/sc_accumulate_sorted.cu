@@ -36,7 +36,7 @@ struct SortedParams {
     int32_t *out;          // [B][O][Ho][Wo]
     int M, O, HoWo, Wo, Wp;
     int P, G, Kp, NCH, KCH, SL, Q;
-    int img_words, pack_words, splits;
+    int img_words, pack_words, aoff_mul, splits;
 };
 
 // One pattern's members: PAT bit j set = the weight of channel j is negative.
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(NQ * 32, 2) accumulate_sorted_kernel(SortedPar
                 const uint32_t *src = pr.as + p * pr.pack_words + abase;
                 const int32_t *aoff = pr.aoff + g * pr.Kp + k0;
                 for (int r = t >> 7; r < rows; r += RSTEP)
-                    cp4(smem_base + (uint32_t)(r * 128 + (t & 127)) * 4, src + __ldg(aoff + r));
+                    cp4(smem_base + (uint32_t)(r * 128 + (t & 127)) * 4, src + __ldg(aoff + r) * pr.aoff_mul);
                 // the NQ quads' lists are contiguous in global memory
                 const uint4 *wsrc = pr.sw + ((size_t)p * pr.G * pr.NCH * pr.Q + gcq0) * pr.SL;
                 for (int i = t; i < NQ * pr.SL; i += NQ * 32) cp16(sw_base + (uint32_t)i * 16, wsrc + i);
@@ -248,8 +248,9 @@ int launch_accumulate_sorted(const Geometry &g, const uint32_t *astream, const i
     pr.sbeg = (const uint16_t *)((const char *)sorted + sp.sw_bytes + sp.srow_bytes);
     pr.M = (int)g.M; pr.O = g.O; pr.HoWo = g.Ho * g.Wo; pr.Wo = g.Wo; pr.Wp = g.Wp;
     pr.P = g.P; pr.G = g.G; pr.Kp = g.Kp; pr.NCH = sp.NCH; pr.KCH = sp.KCH; pr.SL = sp.SL; pr.Q = sp.Q;
-    pr.pack_words = g.C * g.Hp * g.Wp;
-    pr.img_words = g.P * pr.pack_words;
+    pr.pack_words = act_pack_words(g);
+    pr.img_words = act_img_words(g);
+    pr.aoff_mul = act_member_scale(g);
     constexpr int NQ = 8;
     const size_t smem = (size_t)sp.KCH * 128 * 4 + (size_t)NQ * sp.SL * 18 + NQ * 36;
     static PerDeviceOnce once;

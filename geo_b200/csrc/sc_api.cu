@@ -74,6 +74,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->L = d->bit_length; g->P = (g->L + 31) / 32;
     g->mode = d->mode;
     g->guide_linear = 0;
+    g->pos_fast = (Hp == 1 && Wp == 1) ? 1 : 0;
     if (d->generator < GEO_SC_GEN_LFSR || d->generator > GEO_SC_GEN_RAND) return fail(GEO_SC_ERR_MODE, "generator %d", d->generator);
     g->generator = d->generator;
     g->seed = d->seed;
@@ -165,18 +166,29 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
     return rc;
 }
 
+// which kernel a launch gets (GEO_SC_KERNEL_*): the one place that decides
+static int accumulate_kernel_of(const Geometry &g) {
+    if (fullbin_plan(g).layout) return GEO_SC_KERNEL_FULL_BIN;
+    const RowsPlan rp = rows_plan(g);
+    if (rp.eligible) return GEO_SC_KERNEL_SORTED_ROWS;
+    if (rp.layout) return GEO_SC_KERNEL_DENSE;   // the row-tile section is the only sorted one in the buffer
+    const SortedPlan so = sorted_plan(g);
+    if (so.eligible) return GEO_SC_KERNEL_SORTED_IM2COL;
+    if (so.layout) return GEO_SC_KERNEL_DENSE;
+    return short_plan(g).eligible ? GEO_SC_KERNEL_SORTED_SHORT : GEO_SC_KERNEL_DENSE;
+}
+
 static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wprep, int32_t *out, cudaStream_t s) {
     const uint32_t *ws = (const uint32_t *)wprep;
     const int32_t *aoff = (const int32_t *)((const char *)wprep + align_up(g.w_stream_words * 4, 256));
-    if (fullbin_plan(g).layout)
-        return launch_accumulate_fullbin(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
-    const RowsPlan rp = rows_plan(g);
-    if (rp.eligible) return launch_accumulate_rows(g, as, (const char *)wprep + wprep_dense_bytes(g), out, s);
-    if (!rp.layout && sorted_plan(g).eligible)
-        return launch_accumulate_sorted(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
-    if (!rp.layout && !sorted_plan(g).layout && short_plan(g).eligible)
-        return launch_accumulate_short(g, as, aoff, (const char *)wprep + wprep_dense_bytes(g), out, s);
-    return launch_accumulate(g, as, ws, aoff, out, s);
+    const void *section = (const char *)wprep + wprep_dense_bytes(g);
+    switch (accumulate_kernel_of(g)) {
+    case GEO_SC_KERNEL_FULL_BIN: return launch_accumulate_fullbin(g, as, aoff, section, out, s);
+    case GEO_SC_KERNEL_SORTED_ROWS: return launch_accumulate_rows(g, as, section, out, s);
+    case GEO_SC_KERNEL_SORTED_IM2COL: return launch_accumulate_sorted(g, as, aoff, section, out, s);
+    case GEO_SC_KERNEL_SORTED_SHORT: return launch_accumulate_short(g, as, aoff, section, out, s);
+    default: return launch_accumulate(g, as, ws, aoff, out, s);
+    }
 }
 static size_t astream_bytes(const Geometry &g) { return align_up(g.act_stream_words * 4, 256); }
 
@@ -238,10 +250,17 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes) {
     int rc = make_geometry(desc, &g);
     if (rc) return rc;
     if (!yes) return fail(GEO_SC_ERR_NULL, "yes is NULL");
-    const RowsPlan rp = rows_plan(g);
-    const bool sorted = rp.eligible || (!rp.layout && sorted_plan(g).eligible);
-    const bool short_sorted = !rp.layout && !sorted_plan(g).layout && short_plan(g).eligible;
-    *yes = g.mode != GEO_SC_MODE_FULL_BIN && (sorted || short_sorted) ? 1 : 0;
+    const int k = accumulate_kernel_of(g);
+    *yes = k == GEO_SC_KERNEL_SORTED_ROWS || k == GEO_SC_KERNEL_SORTED_IM2COL || k == GEO_SC_KERNEL_SORTED_SHORT ? 1 : 0;
+    return GEO_SC_OK;
+}
+
+int geo_sc_accumulate_kernel(const geo_sc_conv_desc *desc, int *kernel) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (!kernel) return fail(GEO_SC_ERR_NULL, "kernel is NULL");
+    *kernel = accumulate_kernel_of(g);
     return GEO_SC_OK;
 }
 

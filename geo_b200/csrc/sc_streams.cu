@@ -95,6 +95,10 @@ struct GenParams {
     int L, P, mode, z, G, K, Kp, Opad;
     int RW;    // words per pattern row in the global table
     int RWS;   // ... in shared memory: odd, so that the rows of different values fall into different banks
+    // activation-stream image: word(b, p, c, yx) = b * img_stride + p * pack_stride + c * chan_stride + yx
+    // ([batch][pack][c][Hp][Wp], or [pack][c][batch] on 1x1 padded images: `pos_fast`)
+    int pos_fast;
+    unsigned img_stride, pack_stride, chan_stride;
 };
 
 static GenParams gen_params(const Geometry &g) {
@@ -104,6 +108,10 @@ static GenParams gen_params(const Geometry &g) {
     p.L = g.L; p.P = g.P; p.mode = g.mode; p.z = g.z; p.G = g.G; p.K = g.K; p.Kp = g.Kp; p.Opad = g.Opad;
     p.RW = row_words(g.L);
     p.RWS = p.RW | 1;
+    p.pos_fast = g.pos_fast;
+    p.img_stride = (unsigned)act_img_words(g);
+    p.pack_stride = (unsigned)act_pack_words(g);
+    p.chan_stride = (unsigned)(g.Hp * g.Wp * act_member_scale(g));
     return p;
 }
 
@@ -220,7 +228,9 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned yx = idx % plane;
         const unsigned bc = idx / plane;
-        const int c = (int)(bc % (unsigned)gp.C), b = (int)(bc / (unsigned)gp.C);
+        // consecutive threads write consecutive words: channel-major in general, batch-major on 1x1 images
+        const int c = (int)(gp.pos_fast ? bc / (unsigned)gp.B : bc % (unsigned)gp.C);
+        const int b = (int)(gp.pos_fast ? bc % (unsigned)gp.B : bc / (unsigned)gp.C);
         const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
         const int yi = y - gp.pad_h, xi = x - gp.pad_w;
         int V = 0;
@@ -231,9 +241,9 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
         const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
         const unsigned sidx = (unsigned)((cc * gp.Hp + y) * gp.Wp + x);
         const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
-        uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
+        uint32_t *dst = as + (size_t)b * gp.img_stride + (size_t)c * gp.chan_stride + yx;
         for (int p = 0; p < gp.P; p++)
-            dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+            dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
     }
 }
 
@@ -257,7 +267,6 @@ __global__ void __launch_bounds__(256) epilogue_streams_kernel(GenParams gp, Loa
 
     const unsigned Wx = 2u * (unsigned)gp.W;                 // width of the counts
     const unsigned q = Wx >> 2, rows = (unsigned)gp.B * gp.C * gp.H, total = rows * q;
-    const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
     const float fL = (float)gp.L;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const unsigned r = i / q, j = i % q;                 // r = (b * C + c) * H + oy
@@ -278,9 +287,9 @@ __global__ void __launch_bounds__(256) epilogue_streams_kernel(GenParams gp, Loa
             const int V = (int)ceilf(fminf(fmaxf(v[e] * fL, 0.0f), fL - 1.0f));
             const unsigned sidx = (unsigned)((cc * gp.Hp + (int)y) * gp.Wp + (int)x);
             const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
-            uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + y * (unsigned)gp.Wp + x;
+            uint32_t *dst = as + (size_t)b * gp.img_stride + (size_t)c * gp.chan_stride + y * (unsigned)gp.Wp + x;
             for (int p = 0; p < gp.P; p++)
-                dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+                dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
         }
     }
 }
@@ -327,7 +336,8 @@ __global__ void __launch_bounds__(256) act_streams_acc_kernel(GenParams gp, uint
     const float fL = (float)gp.L;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned yx = idx % plane, bc = idx / plane;
-        const int c = (int)(bc % (unsigned)gp.C), b = (int)(bc / (unsigned)gp.C);
+        const int c = (int)(gp.pos_fast ? bc / (unsigned)gp.B : bc % (unsigned)gp.C);
+        const int b = (int)(gp.pos_fast ? bc % (unsigned)gp.B : bc / (unsigned)gp.C);
         const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
         const int yi = y - gp.pad_h, xi = x - gp.pad_w;
         int V = 0;
@@ -335,11 +345,11 @@ __global__ void __launch_bounds__(256) act_streams_acc_kernel(GenParams gp, uint
             const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
             V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
         }
-        uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
-        const size_t pstride = (size_t)gp.C * plane;
+        uint32_t *dst = as + (size_t)b * gp.img_stride + (size_t)c * gp.chan_stride + yx;
+        const size_t pstride = gp.pack_stride;
         // ACC: one generator per element; RAND: one per (channel, y, x), shared over the batch like the LFSR seeds
         const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
-        const uint32_t id = RAND ? (uint32_t)(cc * (int)plane) + yx : idx;
+        const uint32_t id = RAND ? (uint32_t)(cc * (int)plane) + yx : ((uint32_t)b * (uint32_t)gp.C + (uint32_t)c) * plane + yx;
         acc_stream<RAND>(seed, id, V, gp.L, gp.P, [&](int p, uint32_t w) { dst[(size_t)p * pstride] = w; });
     }
 }

@@ -362,6 +362,9 @@ def act_streams_canonical(buf, desc):
     P = (desc.bit_length + 31) // 32
     Hp, Wp = desc.h_in + 2 * desc.pad_h, desc.w_in + 2 * desc.pad_w
     n = desc.batch * P * desc.c_in * Hp * Wp
+    if Hp == 1 and Wp == 1:   # 1x1 padded images: the library lays the image out [pack][c][batch]
+        v = buf[: n * 4].view(torch.int32).view(P, desc.c_in, desc.batch)
+        return v.permute(2, 1, 0).reshape(desc.batch, desc.c_in, 1, 1, P).contiguous()
     v = buf[: n * 4].view(torch.int32).view(desc.batch, P, desc.c_in, Hp, Wp)
     return v.permute(0, 2, 3, 4, 1).contiguous()
 

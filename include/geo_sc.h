@@ -156,6 +156,15 @@ int geo_sc_conv2d_forward_static(const geo_sc_conv_desc *desc, const float *act_
  * the figure matters only for counting executed logic ops. */
 int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
 
+/* The same choice by name: *kernel = one of the values below.  No counterpart in the reference (it has one
+ * kernel); used by the benchmarks to label their rows and by the tests to know which kernel a case exercises. */
+#define GEO_SC_KERNEL_DENSE 0          /* sc_accumulate.cu */
+#define GEO_SC_KERNEL_SORTED_IM2COL 1  /* sc_accumulate_sorted.cu */
+#define GEO_SC_KERNEL_SORTED_ROWS 2    /* sc_accumulate_rows.cu */
+#define GEO_SC_KERNEL_SORTED_SHORT 3   /* sc_accumulate_short.cu */
+#define GEO_SC_KERNEL_FULL_BIN 4       /* sc_accumulate_fullbin.cu */
+int geo_sc_accumulate_kernel(const geo_sc_conv_desc *desc, int *kernel);
+
 /* ---- the three stages, for callers that cache weight streams across calls ---------
  * (weights change once per optimiser step and never during evaluation).
  *
@@ -179,7 +188,9 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
  *
  * geo_sc_generate_act_streams replaces the generation loops at
  * sc_cuda_kernel.cu:667-691,1079-1102,1218-1236 and the quantise/pad ops in sc_cuda.cpp.
- * Layout: uint32 words [batch][pack][c_in][h_in+2*pad_h][w_in+2*pad_w].
+ * Layout: uint32 words [batch][pack][c_in][h_in+2*pad_h][w_in+2*pad_w]; where the padded image is 1x1
+ * (linear layers) [pack][c_in][batch] instead, so that the positions of a member -- the batch rows -- are
+ * consecutive words and a stream buffer is only valid for the batch size it was generated with.
  *
  * geo_sc_accumulate replaces stream_compute_add_direct_variable (:694-1002) and
  * matmul_outer (:43-86); it picks the dense or the sign-sorted kernel from the descriptor alone. */

@@ -68,6 +68,12 @@ def test_group_geometry_per_mode():
     assert _lib.is_sign_sorted(big("z_bin")) and _lib.is_sign_sorted(big("2d_bin"))
     assert not _lib.is_sign_sorted(big("full_bin"))
     assert not _lib.is_sign_sorted(d("1d_bin"))                               # 70 positions: dense kernel
+    assert [_lib.accumulate_kernel(big(m)) for m in ("1d_bin", "z_bin", "2d_bin", "full_bin")] == \
+        ["sorted_rows", "sorted_short", "sorted_short", "full_bin"]
+    assert _lib.accumulate_kernel(d("1d_bin")) == "dense"
+    lin = lambda b: _lib.make_desc(b, 64, 1, 1, 32, 1, 1, 128, "yz_bin", z_unit=16)  # noqa: E731
+    assert _lib.accumulate_kernel(lin(256)) == "sorted_short"                 # position-fastest image, aligned copies
+    assert _lib.accumulate_kernel(lin(255)) == "dense"                        # batch not a multiple of 4
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 10, 3, 3, 32))[2:] == (16, 16)
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 32, 3, 3, 32))[2:] == (32, 32)
 
