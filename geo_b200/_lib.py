@@ -73,6 +73,7 @@ def lib():
     L.geo_sc_bn_fixed_backward.argtypes = [i32, i32, i32, i32] + [vp] * 9 + [sz, vp]
     L.geo_sc_accumulate_is_sign_sorted.argtypes = [dp, ctypes.POINTER(i32)]
     L.geo_sc_accumulate_kernel.argtypes = [dp, ctypes.POINTER(i32)]
+    L.geo_sc_act_stream_layout.argtypes = [dp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     L.geo_sc_quantize.argtypes = [vp, vp, sz, i32, vp]
     L.geo_sc_counts_to_float.argtypes = [vp, vp, sz, i32, vp]
     L.geo_sc_bn_pool_act_forward.argtypes = [i32, i32, i32, i32, i32, f32, f32] + [vp] * 12 + [sz, vp]
@@ -90,7 +91,7 @@ def lib():
     for n in ("geo_sc_conv2d_forward", "geo_sc_linear_forward", "geo_sc_prepare_weights",
               "geo_sc_generate_act_streams", "geo_sc_accumulate", "geo_sc_group_geometry", "geo_sc_host_stream",
               "geo_sc_measure_lop3_peak", "geo_sc_guide_backward_bytes", "geo_sc_guide_backward",
-              "geo_sc_guide_backward_quantized", "geo_sc_quantize", "geo_sc_counts_to_float", "geo_sc_accumulate_is_sign_sorted", "geo_sc_accumulate_kernel", "geo_sc_bn_pool_act_forward", "geo_sc_bn_pool_act_backward",
+              "geo_sc_guide_backward_quantized", "geo_sc_quantize", "geo_sc_counts_to_float", "geo_sc_accumulate_is_sign_sorted", "geo_sc_accumulate_kernel", "geo_sc_act_stream_layout", "geo_sc_bn_pool_act_forward", "geo_sc_bn_pool_act_backward",
               "geo_sc_bn_fixed_scratch_bytes",
               "geo_sc_bn_fixed_forward", "geo_sc_bn_fixed_backward", "geo_sc_pool_act_forward",
               "geo_sc_pool_act_backward"):
@@ -143,6 +144,13 @@ def accumulate_kernel(desc):
     k = ctypes.c_int32(0)
     check(lib().geo_sc_accumulate_kernel(ctypes.byref(desc), ctypes.byref(k)), "geo_sc_accumulate_kernel")
     return KERNEL_NAMES[k.value]
+
+
+def act_stream_layout(desc):
+    """(batch_innermost, batch extent) of the activation-stream image of this descriptor."""
+    bf, bp = ctypes.c_int32(0), ctypes.c_int32(0)
+    check(lib().geo_sc_act_stream_layout(ctypes.byref(desc), ctypes.byref(bf), ctypes.byref(bp)), "geo_sc_act_stream_layout")
+    return bool(bf.value), bp.value
 
 
 def is_sign_sorted(desc):

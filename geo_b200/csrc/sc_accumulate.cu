@@ -27,8 +27,8 @@ struct AccParams {
     int32_t *out;         // [B][O][Ho][Wo]
     int M, O, Opad, HoWo, Wo, Wp;
     int P, G, K;          // K: members per group as laid out (padded to a multiple of 16)
-    int img_words;        // words between images, between packs; factor on the member offsets (act_img_words ...)
-    int pack_words;
+    int img_words;        // words between images, between packs, between pixels (act_img_words ...): the pixel
+    int pack_words;       // stride also scales the member offsets
     int aoff_mul;
     int splits;           // CTAs along grid.z sharing one output tile; > 1 => atomic accumulation
 };
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(NTHREADS, MINB) accumulate_kernel(AccParams pr
         int m = m0 + mcol;
         if (m >= pr.M) m = pr.M - 1;
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
-        abase[j] = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+        abase[j] = b * pr.img_words + ((rem / pr.Wo) * pr.Wp + (rem % pr.Wo)) * pr.aoff_mul;
     }
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
@@ -254,7 +254,7 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
     pr.P = g.P; pr.G = g.G; pr.K = g.Kp;
     pr.pack_words = act_pack_words(g);
     pr.img_words = act_img_words(g);
-    pr.aoff_mul = act_member_scale(g);
+    pr.aoff_mul = act_pixel_stride(g);
     pr.splits = 1;
     // Long groups use 32-member stages (half as many barriers per LOP3); short ones 16-member
     // stages, because a stage is always executed in full and its zero-filled tail rows are wasted.

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(128, 3) accumulate_fullbin_kernel(FullBinParam
         int m = m0 + t;
         if (m >= pr.M) m = pr.M - 1;
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
-        s_abase[t] = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+        s_abase[t] = b * pr.img_words + ((rem / pr.Wo) * pr.Wp + (rem % pr.Wo)) * pr.aoff_mul;
     }
     __syncthreads();
     const int st0 = (int)((long long)pr.NST * blockIdx.z / pr.splits);
@@ -234,7 +234,7 @@ int launch_accumulate_fullbin(const Geometry &g, const uint32_t *astream, const 
     pr.P = g.P; pr.K = g.G; pr.KW = fp.KW; pr.NST = fp.NST;
     pr.pack_words = act_pack_words(g);
     pr.img_words = act_img_words(g);
-    pr.aoff_mul = act_member_scale(g);
+    pr.aoff_mul = act_pixel_stride(g);
     static PerDeviceOnce once;
     int rc = per_device_once(once, []() -> int {
         GEO_CUDA_CHECK(cudaFuncSetAttribute(accumulate_fullbin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

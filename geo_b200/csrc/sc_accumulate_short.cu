@@ -35,10 +35,10 @@ struct ShortParams {
     int32_t *out;                // [B][O][Ho][Wo]
     int M, O, Q, HoWo, Wo, Wp;
     int P, G, K, NCH;            // K: members per group as laid out
-    int img_words, pack_words;
+    int img_words, pack_words, pix_stride, Bp;
     int splits;
     uint32_t row_bytes;   // 1024, as a run-time value (see imad)
-    int four;   // bytes per unit of the member offset table: 4, times the batch in the position-fastest image
+    int four;   // bytes per unit of the member offset table: 4, times the pixel stride of the stream image
 };
 
 __device__ __forceinline__ void cp4(uint32_t smem_addr, const void *gptr) {
@@ -108,8 +108,8 @@ __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&ac
 }
 
 // PACKED: the running sums of two channels share a register as two 16-bit halves (P*G*32 <= 32767 required)
-// POSF: 1x1 images in the position-fastest stream image -- a member's 256 positions are 1 KB of consecutive words
-// and are copied 16 bytes at a time (batch a multiple of 4)
+// POSF: 1x1 images in the batch-innermost stream image -- a member's 256 positions are 1 KB of consecutive words
+// and are copied 16 bytes at a time
 template <int KC, int NSTAGE, int MINB, bool PACKED, bool POSF>
 __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(ShortParams pr) {
     constexpr int A_BYTES = KC * 1024, W_BYTES = 4 * KC * 16;
@@ -126,11 +126,11 @@ __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(Shor
         int m = m0 + t + j * kShThreads;
         if (m >= pr.M) m = pr.M - 1;
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
-        abase[j] = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+        abase[j] = b * pr.img_words + ((rem / pr.Wo) * pr.Wp + (rem % pr.Wo)) * pr.pix_stride;
     }
     // POSF: this thread copies positions [pf_base, pf_base + 4) of rows t / 64, t / 64 + 2, ...; a chunk past the
-    // batch is moved back inside it (its positions are never stored)
-    const int pf_base = min(m0 + (t & 63) * 4, pr.M - 4);
+    // padded batch is moved back inside it (its positions are never stored)
+    const int pf_base = min(m0 + (t & 63) * 4, pr.Bp - 4);
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
     // This CTA owns the (pack, group) pairs [pair0, pair1) of the P*G pairs; the sum over pairs is an integer
@@ -349,8 +349,8 @@ ShortPlan short_plan(const Geometry &g) {
     // A CTA's tile is 256 positions x 16 channels: with fewer positions the dense kernel's smaller tiles win, and so
     // they do where consecutive positions are not consecutive words of the stream image (images narrower than four
     // columns): there a gathered word costs a memory sector, and the dense tile shares it among up to 64 channels.
-    // Linear layers (1x1 images) have the position-fastest image and qualify when 16-byte copies are aligned.
-    sp.eligible = sp.layout && g.M >= 192 && (g.Wo >= 4 || (g.pos_fast && g.B % 4 == 0));
+    // Linear layers (1x1 images) have the batch-innermost image: their positions are consecutive words.
+    sp.eligible = sp.layout && g.M >= 192 && (g.Wo >= 4 || (g.batch_fast && g.Hp * g.Wp == 1));
     sp.KC = g.Kp < 16 ? g.Kp : 16;           // groups are laid out in multiples of 4 (up to 16 members) or of 16
     sp.NCH = g.Kp / sp.KC;
     sp.Q = g.Opad / 4;
@@ -379,11 +379,13 @@ int launch_accumulate_short(const Geometry &g, const uint32_t *astream, const in
     pr.P = g.P; pr.G = g.G; pr.K = g.Kp; pr.NCH = sp.NCH;
     pr.pack_words = act_pack_words(g);
     pr.img_words = act_img_words(g);
+    pr.pix_stride = act_pixel_stride(g);
+    pr.Bp = g.Bp;
     pr.splits = 1;
-    pr.row_bytes = 1024; pr.four = 4 * act_member_scale(g);
+    pr.row_bytes = 1024; pr.four = 4 * act_pixel_stride(g);
     // with packed sums the kernel fits 128 registers: four CTAs per SM instead of three
     const bool packed = (long long)g.P * g.G * 32 <= 32767;
-    const int variant = sp.KC * 4 + (packed ? 2 : 0) + (g.pos_fast ? 1 : 0);
+    const int variant = sp.KC * 4 + (packed ? 2 : 0) + (g.batch_fast && g.Hp * g.Wp == 1 ? 1 : 0);
     switch (variant) {
     case 4 * 4 + 0: return launch_short<4, 6, 3, false, false>(g, pr, s);
     case 4 * 4 + 1: return launch_short<4, 6, 3, false, true>(g, pr, s);

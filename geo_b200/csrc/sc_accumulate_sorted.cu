@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(NQ * 32, 2) accumulate_sorted_kernel(SortedPar
         int m = m0 + (t & 127);
         if (m >= pr.M) m = pr.M - 1;
         const int b = m / pr.HoWo, rem = m % pr.HoWo;
-        abase = b * pr.img_words + (rem / pr.Wo) * pr.Wp + (rem % pr.Wo);
+        abase = b * pr.img_words + ((rem / pr.Wo) * pr.Wp + (rem % pr.Wo)) * pr.aoff_mul;
     }
     const int pairs = pr.P * pr.G;
     const int pair0 = (int)((long long)pairs * blockIdx.z / pr.splits);
@@ -250,7 +250,7 @@ int launch_accumulate_sorted(const Geometry &g, const uint32_t *astream, const i
     pr.P = g.P; pr.G = g.G; pr.Kp = g.Kp; pr.NCH = sp.NCH; pr.KCH = sp.KCH; pr.SL = sp.SL; pr.Q = sp.Q;
     pr.pack_words = act_pack_words(g);
     pr.img_words = act_img_words(g);
-    pr.aoff_mul = act_member_scale(g);
+    pr.aoff_mul = act_pixel_stride(g);
     constexpr int NQ = 8;
     const size_t smem = (size_t)sp.KCH * 128 * 4 + (size_t)NQ * sp.SL * 18 + NQ * 36;
     static PerDeviceOnce once;

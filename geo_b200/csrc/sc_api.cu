@@ -74,7 +74,8 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->L = d->bit_length; g->P = (g->L + 31) / 32;
     g->mode = d->mode;
     g->guide_linear = 0;
-    g->pos_fast = (Hp == 1 && Wp == 1) ? 1 : 0;
+    g->Bp = (d->batch + 3) / 4 * 4;
+    g->batch_fast = (Hp == 1 && Wp == 1) ? 1 : 0;
     if (d->generator < GEO_SC_GEN_LFSR || d->generator > GEO_SC_GEN_RAND) return fail(GEO_SC_ERR_MODE, "generator %d", d->generator);
     g->generator = d->generator;
     g->seed = d->seed;
@@ -98,7 +99,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->Opad = (g->O + g->NT - 1) / g->NT * g->NT;
     const long long lim = (1LL << 31) - 1;
     long long M = (long long)g->B * g->Ho * g->Wo;
-    long long aw = (long long)g->B * g->P * g->C * g->Hp * g->Wp;
+    long long aw = (long long)(g->batch_fast ? g->Bp : g->B) * g->P * g->C * g->Hp * g->Wp;
     // members as laid out: short groups are padded to a multiple of 4 (one stage holds the whole
     // group), longer ones to a multiple of 16 (stages of 16 or 32 members)
     const long long Kp = K <= 16 ? (K + 3) / 4 * 4 : (K + 15) / 16 * 16;
@@ -279,6 +280,15 @@ int geo_sc_act_stream_bytes(const geo_sc_conv_desc *desc, size_t *bytes) {
     if (rc) return rc;
     if (!bytes) return fail(GEO_SC_ERR_NULL, "bytes is NULL");
     *bytes = astream_bytes(g);
+    return GEO_SC_OK;
+}
+
+int geo_sc_act_stream_layout(const geo_sc_conv_desc *desc, int *batch_innermost, int *batch_padded) {
+    Geometry g;
+    int rc = make_geometry(desc, &g);
+    if (rc) return rc;
+    if (batch_innermost) *batch_innermost = g.batch_fast;
+    if (batch_padded) *batch_padded = g.batch_fast ? g.Bp : g.B;
     return GEO_SC_OK;
 }
 

@@ -31,7 +31,8 @@ struct Geometry {
     int Opad;                // c_out rounded up to NT
     int tw, lu, lw_w, lw_a;  // progressive loading
     int guide_linear;        // guide without the exp(-y) factor (full_bin: the guide is the plain convolution)
-    int pos_fast;            // 1x1 padded images: the stream image is [pack][c][batch] (see act_img_words)
+    int batch_fast;          // the stream image has the batch innermost (see act_img_words)
+    int Bp;                  // batch rounded up to a multiple of 4: the batch extent of a batch-innermost image
     int generator;           // GEO_SC_GEN_*
     uint32_t seed;           // GEO_SC_GEN_ACC
     long long M;             // output positions B*Ho*Wo
@@ -44,12 +45,13 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g);
 
 // Layout of the activation-stream image.  In general [batch][pack][c][Hp][Wp]: a member (c, ky, kx) of a group is a
 // fixed word offset from an output position's origin, and consecutive positions of an output row are consecutive
-// words.  On 1x1 padded images (linear layers) consecutive positions would be whole images apart and every gathered
-// word would cost a memory sector, so there the image is [pack][c][batch]: positions are consecutive words again.
-// Both are the same formula: word(b, p, c, y, x) = b * img + p * pack + (c * Hp * Wp) * member_scale + y * Wp + x.
-inline int act_img_words(const Geometry &g) { return g.pos_fast ? 1 : g.P * g.C * g.Hp * g.Wp; }
-inline int act_pack_words(const Geometry &g) { return g.pos_fast ? g.C * g.B : g.C * g.Hp * g.Wp; }
-inline int act_member_scale(const Geometry &g) { return g.pos_fast ? g.B : 1; }   // multiplies the member offset table
+// words.  The batch-innermost form [pack][c][Hp][Wp][Bp] (Bp = batch rounded up to 4, images past the batch all
+// zero) makes the same pixel of consecutive images consecutive words: linear layers (1x1 padded images), whose
+// positions are the images, and the layers of sc_accumulate_taps.cu, whose tiles hold one pixel of many images.
+// Both are one formula: word(b, p, c, y, x) = b * img + p * pack + ((c * Hp + y) * Wp + x) * pixel_stride.
+inline int act_img_words(const Geometry &g) { return g.batch_fast ? 1 : g.P * g.C * g.Hp * g.Wp; }
+inline int act_pack_words(const Geometry &g) { return g.C * g.Hp * g.Wp * (g.batch_fast ? g.Bp : 1); }
+inline int act_pixel_stride(const Geometry &g) { return g.batch_fast ? g.Bp : 1; }   // also scales the member offset table
 
 // Progressive-loading plan: the distinct right-shifts applied to a value and, per pack,
 // the stream bits (MSB-first masks) during which each shift is in force.

@@ -95,10 +95,10 @@ struct GenParams {
     int L, P, mode, z, G, K, Kp, Opad;
     int RW;    // words per pattern row in the global table
     int RWS;   // ... in shared memory: odd, so that the rows of different values fall into different banks
-    // activation-stream image: word(b, p, c, yx) = b * img_stride + p * pack_stride + c * chan_stride + yx
-    // ([batch][pack][c][Hp][Wp], or [pack][c][batch] on 1x1 padded images: `pos_fast`)
-    int pos_fast;
-    unsigned img_stride, pack_stride, chan_stride;
+    // activation-stream image: word(b, p, c, yx) = b * img_stride + p * pack_stride + (c * Hp * Wp + yx) * pix_stride
+    // ([batch][pack][c][Hp][Wp], or batch-innermost [pack][c][Hp][Wp][Bp]: see act_img_words)
+    int batch_fast, Bp;
+    unsigned img_stride, pack_stride, pix_stride;
 };
 
 static GenParams gen_params(const Geometry &g) {
@@ -108,10 +108,11 @@ static GenParams gen_params(const Geometry &g) {
     p.L = g.L; p.P = g.P; p.mode = g.mode; p.z = g.z; p.G = g.G; p.K = g.K; p.Kp = g.Kp; p.Opad = g.Opad;
     p.RW = row_words(g.L);
     p.RWS = p.RW | 1;
-    p.pos_fast = g.pos_fast;
+    p.batch_fast = g.batch_fast;
+    p.Bp = g.Bp;
     p.img_stride = (unsigned)act_img_words(g);
     p.pack_stride = (unsigned)act_pack_words(g);
-    p.chan_stride = (unsigned)(g.Hp * g.Wp * act_member_scale(g));
+    p.pix_stride = (unsigned)act_pixel_stride(g);
     return p;
 }
 
@@ -223,25 +224,26 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
     load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
 
     const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
-    const unsigned total = (unsigned)gp.B * gp.C * plane;
+    const unsigned nb = (unsigned)(gp.batch_fast ? gp.Bp : gp.B);
+    const unsigned total = nb * gp.C * plane;
     const float fL = (float)gp.L;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const unsigned yx = idx % plane;
-        const unsigned bc = idx / plane;
-        // consecutive threads write consecutive words: channel-major in general, batch-major on 1x1 images
-        const int c = (int)(gp.pos_fast ? bc / (unsigned)gp.B : bc % (unsigned)gp.C);
-        const int b = (int)(gp.pos_fast ? bc % (unsigned)gp.B : bc / (unsigned)gp.C);
+        // consecutive threads write consecutive words: pixels of one channel in general, images of one pixel in the
+        // batch-innermost image (whose images past the batch are written as zeros)
+        unsigned yx, c, b;
+        if (gp.batch_fast) { b = idx % nb; const unsigned r = idx / nb; yx = r % plane; c = r / plane; }
+        else { yx = idx % plane; const unsigned bc = idx / plane; c = bc % (unsigned)gp.C; b = bc / (unsigned)gp.C; }
         const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
         const int yi = y - gp.pad_h, xi = x - gp.pad_w;
         int V = 0;
-        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W) {
+        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W && b < (unsigned)gp.B) {
             const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
             V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
         }
-        const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
+        const int cc = gp.mode == GEO_SC_MODE_YZ ? (int)c % gp.z : (int)c;
         const unsigned sidx = (unsigned)((cc * gp.Hp + y) * gp.Wp + x);
         const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
-        uint32_t *dst = as + (size_t)b * gp.img_stride + (size_t)c * gp.chan_stride + yx;
+        uint32_t *dst = as + (size_t)b * gp.img_stride + ((size_t)c * plane + yx) * gp.pix_stride;
         for (int p = 0; p < gp.P; p++)
             dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
     }
@@ -287,7 +289,7 @@ __global__ void __launch_bounds__(256) epilogue_streams_kernel(GenParams gp, Loa
             const int V = (int)ceilf(fminf(fmaxf(v[e] * fL, 0.0f), fL - 1.0f));
             const unsigned sidx = (unsigned)((cc * gp.Hp + (int)y) * gp.Wp + (int)x);
             const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
-            uint32_t *dst = as + (size_t)b * gp.img_stride + (size_t)c * gp.chan_stride + y * (unsigned)gp.Wp + x;
+            uint32_t *dst = as + (size_t)b * gp.img_stride + ((size_t)c * (unsigned)(gp.Hp * gp.Wp) + y * (unsigned)gp.Wp + x) * gp.pix_stride;
             for (int p = 0; p < gp.P; p++)
                 dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
         }
@@ -332,20 +334,22 @@ template <bool RAND>
 __global__ void __launch_bounds__(256) act_streams_acc_kernel(GenParams gp, uint32_t seed, const float *__restrict__ act,
                                                               uint32_t *__restrict__ as) {
     const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
-    const unsigned total = (unsigned)gp.B * gp.C * plane;
+    const unsigned nb = (unsigned)(gp.batch_fast ? gp.Bp : gp.B);
+    const unsigned total = nb * gp.C * plane;
     const float fL = (float)gp.L;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const unsigned yx = idx % plane, bc = idx / plane;
-        const int c = (int)(gp.pos_fast ? bc / (unsigned)gp.B : bc % (unsigned)gp.C);
-        const int b = (int)(gp.pos_fast ? bc % (unsigned)gp.B : bc / (unsigned)gp.C);
+        unsigned yx, uc, b;
+        if (gp.batch_fast) { b = idx % nb; const unsigned r = idx / nb; yx = r % plane; uc = r / plane; }
+        else { yx = idx % plane; const unsigned bc = idx / plane; uc = bc % (unsigned)gp.C; b = bc / (unsigned)gp.C; }
+        const int c = (int)uc;
         const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
         const int yi = y - gp.pad_h, xi = x - gp.pad_w;
         int V = 0;
-        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W) {
+        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W && b < (unsigned)gp.B) {
             const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
             V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
         }
-        uint32_t *dst = as + (size_t)b * gp.img_stride + (size_t)c * gp.chan_stride + yx;
+        uint32_t *dst = as + (size_t)b * gp.img_stride + ((size_t)c * plane + yx) * gp.pix_stride;
         const size_t pstride = gp.pack_stride;
         // ACC: one generator per element; RAND: one per (channel, y, x), shared over the batch like the LFSR seeds
         const int cc = gp.mode == GEO_SC_MODE_YZ ? c % gp.z : c;
@@ -415,7 +419,7 @@ int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, c
     LoadPlan plan;
     make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
     const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
-    const long long total = (long long)g.B * g.C * g.Hp * g.Wp;
+    const long long total = (long long)(g.batch_fast ? g.Bp : g.B) * g.C * g.Hp * g.Wp;
     if (g.generator == GEO_SC_GEN_ACC) act_streams_acc_kernel<false><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
     else if (g.generator == GEO_SC_GEN_RAND) act_streams_acc_kernel<true><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
     else act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
@@ -432,7 +436,7 @@ int launch_epilogue_streams(const Geometry &g, const XSource &xs, const float *w
     make_load_plan(g.L, g.tw, g.lu, g.lw_a, &plan);
     const size_t smem = (size_t)g.L * gp.RWS * 4 + (size_t)g.L * 2;
     // the kernel writes the interior of every padded image; the border holds the all-zero streams of level 0
-    if (g.pad_h || g.pad_w) GEO_CUDA_CHECK(cudaMemsetAsync(astream, 0, g.act_stream_words * 4, s));
+    if (g.pad_h || g.pad_w || (g.batch_fast && g.Bp != g.B)) GEO_CUDA_CHECK(cudaMemsetAsync(astream, 0, g.act_stream_words * 4, s));
     const long long total = (long long)g.B * g.C * g.H * (g.W / 2);
     const float levels = (float)(1 << prec);
     epilogue_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, xs, wq, bq, levels, 1.0f / levels, act_out, astream);

@@ -361,10 +361,11 @@ def act_streams_canonical(buf, desc):
     """View the activation-stream buffer as int32 [B,C,Hp,Wp,P] (the oracle's layout)."""
     P = (desc.bit_length + 31) // 32
     Hp, Wp = desc.h_in + 2 * desc.pad_h, desc.w_in + 2 * desc.pad_w
-    n = desc.batch * P * desc.c_in * Hp * Wp
-    if Hp == 1 and Wp == 1:   # 1x1 padded images: the library lays the image out [pack][c][batch]
-        v = buf[: n * 4].view(torch.int32).view(P, desc.c_in, desc.batch)
-        return v.permute(2, 1, 0).reshape(desc.batch, desc.c_in, 1, 1, P).contiguous()
+    batch_innermost, Bp = _lib.act_stream_layout(desc)
+    n = Bp * P * desc.c_in * Hp * Wp
+    if batch_innermost:   # [pack][c][Hp][Wp][batch padded to 4]
+        v = buf[: n * 4].view(torch.int32).view(P, desc.c_in, Hp, Wp, Bp)[..., : desc.batch]
+        return v.permute(4, 1, 2, 3, 0).contiguous()
     v = buf[: n * 4].view(torch.int32).view(desc.batch, P, desc.c_in, Hp, Wp)
     return v.permute(0, 2, 3, 4, 1).contiguous()
 

@@ -188,9 +188,11 @@ int geo_sc_accumulate_kernel(const geo_sc_conv_desc *desc, int *kernel);
  *
  * geo_sc_generate_act_streams replaces the generation loops at
  * sc_cuda_kernel.cu:667-691,1079-1102,1218-1236 and the quantise/pad ops in sc_cuda.cpp.
- * Layout: uint32 words [batch][pack][c_in][h_in+2*pad_h][w_in+2*pad_w]; where the padded image is 1x1
- * (linear layers) [pack][c_in][batch] instead, so that the positions of a member -- the batch rows -- are
- * consecutive words and a stream buffer is only valid for the batch size it was generated with.
+ * Layout: uint32 words [batch][pack][c_in][h_in+2*pad_h][w_in+2*pad_w], or -- for the descriptors for which
+ * geo_sc_act_stream_layout says so -- batch-innermost [pack][c_in][h_in+2*pad_h][w_in+2*pad_w][batch_padded]
+ * with the batch rounded up to a multiple of 4 and the images past it all zero: the same pixel of
+ * consecutive images is then consecutive words (linear layers, whose positions are the images).  A stream
+ * buffer is only valid for the descriptor (batch included) it was generated with.
  *
  * geo_sc_accumulate replaces stream_compute_add_direct_variable (:694-1002) and
  * matmul_outer (:43-86); it picks the dense or the sign-sorted kernel from the descriptor alone. */
@@ -198,6 +200,7 @@ int geo_sc_weight_prep_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
 int geo_sc_prepare_weights(const geo_sc_conv_desc *desc, const float *weight_device, void *wprep_device,
                            size_t wprep_bytes, void *stream);
 int geo_sc_act_stream_bytes(const geo_sc_conv_desc *desc, size_t *bytes);
+int geo_sc_act_stream_layout(const geo_sc_conv_desc *desc, int *batch_innermost, int *batch_padded);
 int geo_sc_generate_act_streams(const geo_sc_conv_desc *desc, const float *act_device, void *astream_device,
                                 size_t astream_bytes, void *stream);
 int geo_sc_accumulate(const geo_sc_conv_desc *desc, const void *astream_device, const void *wprep_device,

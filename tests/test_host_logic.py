@@ -72,8 +72,9 @@ def test_group_geometry_per_mode():
         ["sorted_rows", "sorted_short", "sorted_short", "full_bin"]
     assert _lib.accumulate_kernel(d("1d_bin")) == "dense"
     lin = lambda b: _lib.make_desc(b, 64, 1, 1, 32, 1, 1, 128, "yz_bin", z_unit=16)  # noqa: E731
-    assert _lib.accumulate_kernel(lin(256)) == "sorted_short"                 # position-fastest image, aligned copies
-    assert _lib.accumulate_kernel(lin(255)) == "dense"                        # batch not a multiple of 4
+    assert _lib.accumulate_kernel(lin(256)) == "sorted_short"                 # batch-innermost image, 16-byte copies
+    assert _lib.accumulate_kernel(lin(255)) == "sorted_short"                 # the image pads the batch to 256
+    assert _lib.act_stream_layout(lin(255)) == (True, 256) and _lib.act_stream_layout(big("1d_bin"))[0] is False
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 10, 3, 3, 32))[2:] == (16, 16)
     assert _lib.group_geometry(_lib.make_desc(1, 3, 8, 8, 32, 3, 3, 32))[2:] == (32, 32)
 

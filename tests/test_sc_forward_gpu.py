@@ -44,7 +44,7 @@ def test_stream_words_of_a_linear_layer_match_oracle(cuda_device, oracle_lib):
     """1x1 images: the stream image is laid out [pack][c][batch]; its words are the oracle's all the same."""
     from geo_b200 import ops
 
-    for B in (5, 8):
+    for B in (5, 8, 203):
         a, w = _rand((B, 12, 1, 1), (9, 12, 1, 1), 77 + B)
         for mode in ("yz_bin", "1d_bin", "full_bin"):
             kw = dict(z_unit=4, total_width=7, load_width=2, load_wait_w=2, load_wait_a=2)
@@ -127,8 +127,9 @@ SHORT_GROUP_CASES = [
     ((3, 32, 8, 8), (12, 32, 3, 3), (1, 1), "full_or", 1, 128),  # 288 members, c_out padded to 16: six quads' worth of chunks
     ((4, 130, 8, 8), (16, 130, 3, 3), (1, 1), "z_bin", 1, 256),  # P * G * 32 = 33 280: 32-bit running sums
     ((3, 5, 7, 20), (16, 5, 3, 3), (0, 0), "2d_bin", 1, 64),     # ragged last position tile (M = 270)
-    ((300, 64, 1, 1), (40, 64, 1, 1), (0, 0), "yz_bin", 16, 128),  # linear layer: position-fastest image, 16-byte copies, ragged tile
+    ((300, 64, 1, 1), (40, 64, 1, 1), (0, 0), "yz_bin", 16, 128),  # linear layer: batch-innermost image, 16-byte copies, ragged tile
     ((256, 40, 1, 1), (24, 40, 1, 1), (0, 0), "yz_bin", 8, 32),    # linear layer, 8-member groups
+    ((203, 24, 1, 1), (16, 24, 1, 1), (0, 0), "yz_bin", 12, 64),   # linear layer, batch not a multiple of 4
 ]
 
 
