@@ -136,7 +136,7 @@ def group_geometry_full(desc):
     return g.value, k.value, kp.value, nt.value, op.value
 
 
-KERNEL_NAMES = ("dense", "sorted_im2col", "sorted_rows", "sorted_short", "full_bin")
+KERNEL_NAMES = ("dense", "sorted_im2col", "sorted_rows", "sorted_short", "full_bin", "sorted_taps")
 
 
 def accumulate_kernel(desc):

@@ -20,7 +20,7 @@ LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libgeo_sc.so")
 EXT_DIR = os.path.join(PKG, "ext")  # holds sc_extension_cuda*.so and sc_extension*.so
 
-CUDA_SOURCES = ["sc_api.cu", "sc_streams.cu", "sc_accumulate.cu", "sc_accumulate_sorted.cu", "sc_accumulate_rows.cu", "sc_accumulate_short.cu", "sc_accumulate_fullbin.cu", "sc_peak.cu", "sc_guide.cu", "sc_guide_mma.cu", "sc_guide_tc.cu", "sc_bn.cu", "sc_static.cu"]
+CUDA_SOURCES = ["sc_api.cu", "sc_streams.cu", "sc_accumulate.cu", "sc_accumulate_sorted.cu", "sc_accumulate_rows.cu", "sc_accumulate_taps.cu", "sc_accumulate_short.cu", "sc_accumulate_fullbin.cu", "sc_peak.cu", "sc_guide.cu", "sc_guide_mma.cu", "sc_guide_tc.cu", "sc_bn.cu", "sc_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

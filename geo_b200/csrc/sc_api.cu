@@ -9,6 +9,7 @@
 #include "sc_rows.h"
 #include "sc_short.h"
 #include "sc_sorted.h"
+#include "sc_taps.h"
 
 namespace geo {
 
@@ -75,7 +76,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->mode = d->mode;
     g->guide_linear = 0;
     g->Bp = (d->batch + 3) / 4 * 4;
-    g->batch_fast = (Hp == 1 && Wp == 1) ? 1 : 0;
+    g->batch_fast = 0;   // decided below, once the group geometry is known
     if (d->generator < GEO_SC_GEN_LFSR || d->generator > GEO_SC_GEN_RAND) return fail(GEO_SC_ERR_MODE, "generator %d", d->generator);
     g->generator = d->generator;
     g->seed = d->seed;
@@ -99,7 +100,7 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
     g->Opad = (g->O + g->NT - 1) / g->NT * g->NT;
     const long long lim = (1LL << 31) - 1;
     long long M = (long long)g->B * g->Ho * g->Wo;
-    long long aw = (long long)(g->batch_fast ? g->Bp : g->B) * g->P * g->C * g->Hp * g->Wp;
+    long long aw = (long long)g->Bp * g->P * g->C * g->Hp * g->Wp;   // bound for either layout
     // members as laid out: short groups are padded to a multiple of 4 (one stage holds the whole
     // group), longer ones to a multiple of 16 (stages of 16 or 32 members)
     const long long Kp = K <= 16 ? (K + 3) / 4 * 4 : (K + 15) / 16 * 16;
@@ -111,9 +112,11 @@ int make_geometry(const geo_sc_conv_desc *d, Geometry *g) {
                     "an index exceeds 31 bits (positions %lld, act words %lld, weight words %lld, outputs %lld)", M, aw,
                     ww, ow);
     g->G = (int)G; g->K = (int)K; g->Kp = (int)Kp; g->M = M;
-    g->act_stream_words = (size_t)aw;
     g->w_stream_words = (size_t)ww;
     g->aoff_entries = (size_t)(G * Kp);
+    // batch-innermost stream image: linear layers and the layers of the tap-tile kernel
+    g->batch_fast = (g->Hp * g->Wp == 1 || taps_plan(*g).layout) ? 1 : 0;
+    g->act_stream_words = (size_t)(g->batch_fast ? g->Bp : g->B) * g->P * g->C * g->Hp * g->Wp;
     return GEO_SC_OK;
 }
 
@@ -149,6 +152,8 @@ static size_t wprep_dense_bytes(const Geometry &g) {
 static size_t wprep_bytes(const Geometry &g) {
     const FullBinPlan fb = fullbin_plan(g);
     if (fb.layout) return wprep_dense_bytes(g) + fb.bytes;   // full_bin: the weights packed for the binary GEMM
+    const TapsPlan tp = taps_plan(g);
+    if (tp.layout) return wprep_dense_bytes(g) + tp.total();
     const RowsPlan rp = rows_plan(g);
     if (rp.layout) return wprep_dense_bytes(g) + rp.total();
     const SortedPlan so = sorted_plan(g);
@@ -161,6 +166,7 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
     int rc = launch_prepare_weights(g, weight, ws, aoff, s);
     if (rc) return rc;
     if (fullbin_plan(g).layout) rc = launch_fullbin_pack(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
+    else if (taps_plan(g).layout) rc = launch_sort_taps(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     else if (rows_plan(g).layout) rc = launch_sort_rows(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     else if (sorted_plan(g).layout) rc = launch_sort_members(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
     else if (short_plan(g).layout) rc = launch_sort_short(g, ws, (char *)wprep + wprep_dense_bytes(g), s);
@@ -170,6 +176,8 @@ static int prepare_all(const Geometry &g, const float *weight, void *wprep, cuda
 // which kernel a launch gets (GEO_SC_KERNEL_*): the one place that decides
 static int accumulate_kernel_of(const Geometry &g) {
     if (fullbin_plan(g).layout) return GEO_SC_KERNEL_FULL_BIN;
+    const TapsPlan tp = taps_plan(g);
+    if (tp.layout) return tp.eligible ? GEO_SC_KERNEL_SORTED_TAPS : GEO_SC_KERNEL_DENSE;
     const RowsPlan rp = rows_plan(g);
     if (rp.eligible) return GEO_SC_KERNEL_SORTED_ROWS;
     if (rp.layout) return GEO_SC_KERNEL_DENSE;   // the row-tile section is the only sorted one in the buffer
@@ -185,6 +193,7 @@ static int accumulate_any(const Geometry &g, const uint32_t *as, const void *wpr
     const void *section = (const char *)wprep + wprep_dense_bytes(g);
     switch (accumulate_kernel_of(g)) {
     case GEO_SC_KERNEL_FULL_BIN: return launch_accumulate_fullbin(g, as, aoff, section, out, s);
+    case GEO_SC_KERNEL_SORTED_TAPS: return launch_accumulate_taps(g, as, section, out, s);
     case GEO_SC_KERNEL_SORTED_ROWS: return launch_accumulate_rows(g, as, section, out, s);
     case GEO_SC_KERNEL_SORTED_IM2COL: return launch_accumulate_sorted(g, as, aoff, section, out, s);
     case GEO_SC_KERNEL_SORTED_SHORT: return launch_accumulate_short(g, as, aoff, section, out, s);
@@ -252,7 +261,10 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes) {
     if (rc) return rc;
     if (!yes) return fail(GEO_SC_ERR_NULL, "yes is NULL");
     const int k = accumulate_kernel_of(g);
-    *yes = k == GEO_SC_KERNEL_SORTED_ROWS || k == GEO_SC_KERNEL_SORTED_IM2COL || k == GEO_SC_KERNEL_SORTED_SHORT ? 1 : 0;
+    *yes = k == GEO_SC_KERNEL_SORTED_ROWS || k == GEO_SC_KERNEL_SORTED_IM2COL || k == GEO_SC_KERNEL_SORTED_SHORT ||
+                   k == GEO_SC_KERNEL_SORTED_TAPS
+               ? 1
+               : 0;
     return GEO_SC_OK;
 }
 

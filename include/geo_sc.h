@@ -163,6 +163,7 @@ int geo_sc_accumulate_is_sign_sorted(const geo_sc_conv_desc *desc, int *yes);
 #define GEO_SC_KERNEL_SORTED_ROWS 2    /* sc_accumulate_rows.cu */
 #define GEO_SC_KERNEL_SORTED_SHORT 3   /* sc_accumulate_short.cu */
 #define GEO_SC_KERNEL_FULL_BIN 4       /* sc_accumulate_fullbin.cu */
+#define GEO_SC_KERNEL_SORTED_TAPS 5    /* sc_accumulate_taps.cu */
 int geo_sc_accumulate_kernel(const geo_sc_conv_desc *desc, int *kernel);
 
 /* ---- the three stages, for callers that cache weight streams across calls ---------
