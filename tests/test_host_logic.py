@@ -71,6 +71,11 @@ def test_group_geometry_per_mode():
     assert [_lib.accumulate_kernel(big(m)) for m in ("1d_bin", "z_bin", "2d_bin", "full_bin")] == \
         ["sorted_rows", "sorted_short", "sorted_short", "full_bin"]
     assert _lib.accumulate_kernel(d("1d_bin")) == "dense"
+    wide = lambda mode, b=64: _lib.make_desc(b, 128, 8, 8, 128, 3, 3, 128, mode, pad_h=1, pad_w=1)  # noqa: E731
+    assert [_lib.accumulate_kernel(wide(m)) for m in ("1d_bin", "full_or", "2d_bin", "z_bin")] == \
+        ["sorted_taps", "sorted_taps", "sorted_taps", "sorted_short"]          # >= 64 channels: tap tiles
+    assert _lib.act_stream_layout(wide("1d_bin", 30)) == (True, 32) and _lib.act_stream_layout(wide("z_bin"))[0] is False
+    assert _lib.accumulate_kernel(wide("1d_bin", 3)) == "dense"                # 64 runs of four images make a tile
     lin = lambda b: _lib.make_desc(b, 64, 1, 1, 32, 1, 1, 128, "yz_bin", z_unit=16)  # noqa: E731
     assert _lib.accumulate_kernel(lin(256)) == "sorted_short"                 # batch-innermost image, 16-byte copies
     assert _lib.accumulate_kernel(lin(255)) == "sorted_short"                 # the image pads the batch to 256

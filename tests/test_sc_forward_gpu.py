@@ -151,6 +151,40 @@ def test_short_group_kernel_matches_oracle(cuda_device, oracle_lib, case):
     assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, pad_h=pad[0], pad_w=pad[1], **kw))
 
 
+TAP_TILE_CASES = [
+    # act, weight, pad, mode, L
+    ((2, 64, 8, 8), (40, 64, 3, 3), (1, 1), "1d_bin", 128),      # one tile mixes every border class (union of live taps)
+    ((5, 64, 6, 7), (64, 64, 3, 3), (1, 1), "full_or", 64),      # batch padded 5 -> 8, non-square image
+    ((18, 100, 4, 4), (96, 100, 3, 3), (1, 1), "1d_bin", 128),   # 100 channels: ragged last channel chunk
+    ((66, 200, 2, 2), (64, 200, 3, 3), (1, 1), "2d_bin", 32),    # 2x2 images: most taps dead; three chunks per tap
+    ((12, 64, 5, 5), (33, 64, 5, 5), (2, 2), "1d_bin", 256),     # 5x5 filter, ragged c_out
+    ((31, 64, 6, 6), (32, 64, 3, 3), (0, 0), "full_or", 128),    # no padding: no tap is ever dead
+    ((6, 64, 3, 9), (64, 64, 3, 3), (2, 1), "1d_bin", 64),       # padding wider than the filter needs: whole groups dead at the border
+    ((44, 72, 1, 6), (64, 72, 1, 3), (0, 1), "2d_bin", 128),     # one-row images
+    ((64, 128, 4, 4), (128, 128, 3, 3), (1, 1), "1d_bin", 128),  # several tiles, one border class each
+]
+
+
+@pytest.mark.parametrize("case", range(len(TAP_TILE_CASES)))
+def test_tap_tile_kernel_matches_oracle(cuda_device, oracle_lib, case):
+    """The tap-tile kernel (batch-innermost stream image, dead taps skipped per border class) against the oracle,
+    stream words included."""
+    from geo_b200 import _lib, ops
+
+    ashape, wshape, pad, mode, L = TAP_TILE_CASES[case]
+    a, w = _rand(ashape, wshape, 1300 + case)
+    w.view(-1)[::7] = 0
+    kw = dict(z_unit=4, total_width=7, load_width=2, load_wait_w=2, load_wait_a=2)
+    d = ops.desc_for(a, w, L, mode, pad, **kw)
+    assert _lib.accumulate_kernel(d) == "sorted_taps"
+    assert _lib.act_stream_layout(d) == (True, (ashape[0] + 3) // 4 * 4)
+    asg = ops.act_streams_canonical(ops.generate_act_streams(a.to(cuda_device), d), d).cpu().numpy()
+    aso = oracle_lib.act_streams(oracle_lib.pad_act(a, pad[0], pad[1]), L, mode, 4, 7, 2, 2)
+    assert np.array_equal(asg.view(np.uint32), aso)
+    y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, pad, **kw).cpu().numpy()
+    assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, pad_h=pad[0], pad_w=pad[1], **kw))
+
+
 def test_small_stream_lengths(cuda_device, oracle_lib):
     from geo_b200 import ops
 
