@@ -75,7 +75,8 @@ def test_group_geometry_per_mode():
     assert [_lib.accumulate_kernel(wide(m)) for m in ("1d_bin", "full_or", "2d_bin", "z_bin")] == \
         ["sorted_taps", "sorted_taps", "sorted_taps", "sorted_short"]          # >= 64 channels: tap tiles
     assert _lib.act_stream_layout(wide("1d_bin", 30)) == (True, 32) and _lib.act_stream_layout(wide("z_bin"))[0] is False
-    assert _lib.accumulate_kernel(wide("1d_bin", 3)) == "dense"                # 64 runs of four images make a tile
+    tiny = _lib.make_desc(3, 128, 4, 4, 128, 3, 3, 128, "1d_bin", pad_h=1, pad_w=1)
+    assert _lib.accumulate_kernel(tiny) == "dense"                             # fewer than the 64 runs of four images of a tile
     lin = lambda b: _lib.make_desc(b, 64, 1, 1, 32, 1, 1, 128, "yz_bin", z_unit=16)  # noqa: E731
     assert _lib.accumulate_kernel(lin(256)) == "sorted_short"                 # batch-innermost image, 16-byte copies
     assert _lib.accumulate_kernel(lin(255)) == "sorted_short"                 # the image pads the batch to 256
