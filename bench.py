@@ -304,7 +304,7 @@ def run_native(args):
 
 # DRAM bytes per accumulate launch of the default workload (4-layer CNN, 256 images), mean of the four
 # layers' launches: 16.07 + 61.35 + 24.04 + 4.80 MB read, < 0.1 MB written (one ncu capture).
-ACC_DRAM_BYTES_PER_LAUNCH = 26.56e6
+ACC_DRAM_BYTES_PER_LAUNCH = 34.95e6
 
 
 def run_vgg11(device, rank, world, dist, timer):

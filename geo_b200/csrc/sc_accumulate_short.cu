@@ -36,7 +36,7 @@ struct ShortParams {
     int M, O, Q, HoWo, Wo, Wp;
     int P, G, K, NCH;            // K: members per group as laid out
     int img_words, pack_words, pix_stride, Bp;
-    int splits;
+    int splits, CT;   // CTAs sharing one output tile; channel tiles (of 16)
     uint32_t row_bytes;   // 1024, as a run-time value (see imad)
     int four;   // bytes per unit of the member offset table: 4, times the pixel stride of the stream image
 };
@@ -116,8 +116,11 @@ __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(Shor
     constexpr int STAGE = A_BYTES + W_BYTES + 4 * kShortMetaBytes;
     extern __shared__ __align__(16) unsigned char smem[];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int m0 = blockIdx.x * kShMT;
-    const int q0 = blockIdx.y * 4;
+    // the CTAs that share a position tile (other channels, other pairs) are neighbours in launch order, so that the
+    // tile's stream words are fetched from DRAM once and then found in L2
+    const int cta_ct = (int)(blockIdx.x % pr.CT), cta_split = (int)((blockIdx.x / pr.CT) % pr.splits);
+    const int m0 = (int)(blockIdx.x / (pr.CT * pr.splits)) * kShMT;
+    const int q0 = cta_ct * 4;
 
     // gather: this thread copies columns t and t + 128 of every member row
     int abase[2];
@@ -136,8 +139,8 @@ __global__ void __launch_bounds__(kShThreads, MINB) accumulate_short_kernel(Shor
     // This CTA owns the (pack, group) pairs [pair0, pair1) of the P*G pairs; the sum over pairs is an integer
     // sum, so splitting it over CTAs and adding atomically is exact and order-free.
     const int pairs = pr.P * pr.G;
-    const int pair0 = (int)((long long)pairs * blockIdx.z / pr.splits);
-    const int pair1 = (int)((long long)pairs * (blockIdx.z + 1) / pr.splits);
+    const int pair0 = (int)((long long)pairs * cta_split / pr.splits);
+    const int pair1 = (int)((long long)pairs * (cta_split + 1) / pr.splits);
     const int nstages = (pair1 - pair0) * pr.NCH;
 
     int ld_p = pair0 / pr.G, ld_g = pair0 % pr.G, ld_c = 0, ld_s = 0;
@@ -334,7 +337,9 @@ int launch_short(const Geometry &g, ShortParams pr, cudaStream_t s) {
         if (best < 0 || cost < best) { best = cost; splits = c; }
     }
     pr.splits = (int)splits;
-    grid.z = (unsigned)splits;
+    pr.CT = (int)grid.y;
+    if (tiles * splits > 0x7fffffffLL) return fail(GEO_SC_ERR_TOO_LARGE, "%lld x %lld CTAs", tiles, splits);
+    grid = dim3((unsigned)(tiles * splits), 1, 1);
     if (splits > 1) GEO_CUDA_CHECK(cudaMemsetAsync(pr.out, 0, (size_t)g.M * g.O * sizeof(int32_t), s));
     accumulate_short_kernel<KC, NSTAGE, MINB, PACKED, POSF><<<grid, kShThreads, SMEM, s>>>(pr);
     GEO_CUDA_CHECK(cudaGetLastError());
