@@ -183,12 +183,12 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(GenParams gp, Load
     uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RWS);
     load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
 
-    const long long total = (long long)gp.G * gp.Kp * gp.Opad;
+    // 32-bit index arithmetic: the geometry check bounds the prepared streams by 2^31 words
+    const unsigned total = (unsigned)gp.G * (unsigned)gp.Kp * (unsigned)gp.Opad;
     const float fL = (float)gp.L;
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int o = (int)(idx % gp.Opad);
-        const int gk = (int)(idx / gp.Opad);
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const int o = (int)(idx % (unsigned)gp.Opad);
+        const int gk = (int)(idx / (unsigned)gp.Opad);
         const int k = gk % gp.Kp, g = gk / gp.Kp;   // k >= K: padding member, zero streams
         int c, ky, kx, sidx;
         decode_weight_member(gp, g, k, &c, &ky, &kx, &sidx);
