@@ -42,12 +42,28 @@ def algorithmic_work(desc):
     return 2 * mac * packs, nbytes
 
 
+def live_tap_fraction(desc):
+    """Fraction of the (output pixel, filter tap) pairs whose input pixel lies inside the unpadded image: the
+    rest meets the all-zero streams of the padding, which the tap-tile kernel skips."""
+    def axis(n, pad, k):
+        out = n + 2 * pad - k + 1
+        live = sum(1 for o in range(out) for t in range(k) if 0 <= o + t - pad < n)
+        return live / float(out * k)
+    return axis(desc.h_in, desc.pad_h, desc.k_h) * axis(desc.w_in, desc.pad_w, desc.k_w)
+
+
 def executed_lop3(desc):
     """32-bit logic ops the accumulation kernel actually issues for the OR accumulation: the definition's
-    count for the dense kernel, at most half of it for the sign-sorted kernel (one op per weight instead of
-    one per weight and polarity; members whose four weights are all zero are skipped on top of that)."""
+    count for the dense kernel, at most half of it for the sign-sorted kernels (one op per weight instead of
+    one per weight and polarity; members whose four weights are all zero are skipped on top of that), and of
+    that half only the taps inside the image for the tap-tile kernel (at batch sizes that fill a tile with one
+    border class; smaller batches skip less)."""
     lop3, _ = algorithmic_work(desc)
-    return lop3 // 2 if _lib.is_sign_sorted(desc) else lop3
+    if not _lib.is_sign_sorted(desc):
+        return lop3
+    if _lib.accumulate_kernel(desc) == "sorted_taps":
+        return int(lop3 // 2 * live_tap_fraction(desc))
+    return lop3 // 2
 
 
 def _stream_ptr(device):
