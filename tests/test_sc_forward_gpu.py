@@ -185,6 +185,22 @@ def test_tap_tile_kernel_matches_oracle(cuda_device, oracle_lib, case):
     assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, pad_h=pad[0], pad_w=pad[1], **kw))
 
 
+def test_dense_kernel_on_the_batch_innermost_image(cuda_device, oracle_lib):
+    """Layers of the tap-tile kernel whose launch is too small for one of its tiles run on the dense kernel, over
+    the same batch-innermost stream image."""
+    from geo_b200 import _lib, ops
+
+    for ashape, wshape, pad, mode in [((3, 128, 4, 4), (40, 128, 3, 3), (1, 1), "1d_bin"),
+                                      ((2, 64, 5, 3), (32, 64, 3, 3), (1, 1), "full_or"),
+                                      ((5, 64, 2, 2), (32, 64, 3, 3), (1, 1), "2d_bin")]:
+        a, w = _rand(ashape, wshape, 1700 + ashape[0])
+        kw = dict(total_width=7, load_width=2, load_wait_w=2, load_wait_a=2)
+        d = ops.desc_for(a, w, 128, mode, pad, **kw)
+        assert _lib.accumulate_kernel(d) == "dense" and _lib.act_stream_layout(d)[0]
+        y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), 128, mode, pad, **kw).cpu().numpy()
+        assert np.array_equal(y, oracle_lib.conv2d(a, w, 128, mode, pad_h=pad[0], pad_w=pad[1], **kw))
+
+
 def test_small_stream_lengths(cuda_device, oracle_lib):
     from geo_b200 import ops
 

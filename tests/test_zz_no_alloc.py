@@ -44,6 +44,11 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda_device):
         ((8, 32, 12, 12), (64, 32, 5, 5), (2, 2), 128, "1d_bin", dict(total_width=7, load_width=2, load_wait_w=2)),
         # the counter-based "accurate" generator with a fixed seed
         ((4, 8, 10, 10), (12, 8, 3, 3), (1, 1), 64, "1d_bin", dict(generator="acc", seed=11)),
+        # 64 input channels: the stream image is batch-innermost (batch padded 6 -> 8); this entry point's dense
+        # kernel reads it through the same offsets
+        ((6, 64, 6, 6), (16, 64, 3, 3), (1, 1), 64, "1d_bin", dict(total_width=7, load_width=2, load_wait_w=2)),
+        # a linear layer (batch-innermost image as well)
+        ((9, 48, 1, 1), (20, 48, 1, 1), (0, 0), 128, "yz_bin", dict(z_unit=16)),
     ]
     for ashape, wshape, pad, L, mode, kw in calls:
         a = q7(torch.rand(*ashape, generator=g)).to(cuda_device)
