@@ -73,7 +73,7 @@ struct TapsParams {
 };
 
 template <int PAT>
-__device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo, uint32_t a_hi,
+__device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo,
                                            const uint4 *__restrict__ sw, const uint32_t *__restrict__ so, int i0, int i1,
                                            uint32_t one) {
     if (i0 >= i1) return;
@@ -82,8 +82,9 @@ __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&ac
 #pragma unroll 2
     for (int i = i0; i < i1; i++) {
         const uint4 w = wn;
-        const uint4 x = lds128(add_on_fma_pipe(on, one, a_lo));
-        const uint4 y = lds128(add_on_fma_pipe(on, one, a_hi));
+        const uint32_t a = add_on_fma_pipe(on, one, a_lo);
+        const uint4 x = lds128(a);
+        const uint4 y = lds128(a + 512);   // the lane's second run: 32 runs of 16 bytes further on
         wn = sw[i + 1];   // slot i1 exists: the lists are padded, and what follows them in the stage is readable
         on = so[i + 1];
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(kTapsThreads, 1) accumulate_taps_kernel(TapsPa
         }
         {
             const uint32_t stage = smem_base + (uint32_t)(s & 1) * pr.stage_bytes;
-            const uint32_t a_lo = stage + (uint32_t)(h * 64 + lane) * 16, a_hi = a_lo + 32 * 16;
+            const uint32_t a_lo = stage + (uint32_t)(h * 64 + lane) * 16;
             const unsigned char *stage_ptr = smem + (size_t)(s & 1) * pr.stage_bytes;
             const uint4 *swl = (const uint4 *)(stage_ptr + sw_off) + ql * pr.SL;
             const uint32_t *sol = (const uint32_t *)(stage_ptr + so_off) + ql * pr.SL;
@@ -267,7 +268,7 @@ __global__ void __launch_bounds__(kTapsThreads, 1) accumulate_taps_kernel(TapsPa
             // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
             const int mybeg = lane < 17 ? (int)sbl[lane] : 0;
 #define GEO_BUCKET(B) \
-    run_bucket<B>(accp, accn, a_lo, a_hi, swl, sol, __shfl_sync(0xffffffffu, mybeg, B), __shfl_sync(0xffffffffu, mybeg, B + 1), pr.one);
+    run_bucket<B>(accp, accn, a_lo, swl, sol, __shfl_sync(0xffffffffu, mybeg, B), __shfl_sync(0xffffffffu, mybeg, B + 1), pr.one);
             GEO_BUCKET(0) GEO_BUCKET(1) GEO_BUCKET(2) GEO_BUCKET(3) GEO_BUCKET(4) GEO_BUCKET(5) GEO_BUCKET(6) GEO_BUCKET(7)
             GEO_BUCKET(8) GEO_BUCKET(9) GEO_BUCKET(10) GEO_BUCKET(11) GEO_BUCKET(12) GEO_BUCKET(13) GEO_BUCKET(14) GEO_BUCKET(15)
 #undef GEO_BUCKET
