@@ -169,7 +169,7 @@ def test_fused_epilogue_equals_the_separate_kernels(cuda_device, training):
     (geo_sc_epilogue_forward) against the chain of separate entry points, bit for bit: the rounded activation, the
     stream image including its zero border, the saved statistics and the running statistics; and the backward
     pass reading counts against the one reading the float value."""
-    from geo_b200 import ops
+    from geo_b200 import _lib, ops
 
     g = torch.Generator().manual_seed(12)
     cases = [
@@ -178,6 +178,10 @@ def test_fused_epilogue_equals_the_separate_kernels(cuda_device, training):
         ((3, 5, 8, 8), 64, (7, 5, 2, 256, "yz_bin", 2, 8, 1)),
         ((4, 16, 4, 8), 256, (9, 2, 0, 32, "z_bin", 4, 3, 4)),
         ((2, 3, 6, 4), 32, (4, 1, 0, 16, "full_or", 4, 8, 1)),
+        # next layers with >= 64 channels take the batch-innermost stream image (batch padded to a multiple of 4)
+        ((6, 64, 8, 8), 128, (32, 3, 1, 128, "1d_bin", 4, 2, 2)),
+        ((5, 72, 4, 8), 64, (40, 3, 1, 256, "full_or", 4, 8, 1)),
+        ((9, 64, 12, 8), 128, (33, 3, 0, 64, "2d_bin", 4, 8, 1)),
     ]
     for shape, L_in, (O2, k, pad, L2, mode, z, lu, lw) in cases:
         B, C, H, W = shape
@@ -189,6 +193,8 @@ def test_fused_epilogue_equals_the_separate_kernels(cuda_device, training):
         rm2, rv2 = rm1.clone(), rv1.clone()
         nd = ops.make_desc(B, C, H // 2, W // 2, O2, k, k, L2, mode, pad_h=pad, pad_w=pad, z_unit=z, total_width=7,
                            load_width=lu, load_wait_w=lw, load_wait_a=lw)
+        if C >= 64:
+            assert _lib.act_stream_layout(nd) == (True, (B + 3) // 4 * 4)
         act, streams, mean, invstd, scale, wq, bq = ops.epilogue_forward(counts, L_in, nd, bw, bb, rm1, rv1, training, 0.1, 1e-5)
         x = ops.counts_to_float(counts, L_in)
         y, mean2, invstd2, scale2, wq2, bq2 = ops.bn_pool_act_forward(x, bw, bb, rm2, rv2, training, 0.1, 1e-5)
