@@ -224,28 +224,75 @@ __global__ void __launch_bounds__(256) act_streams_kernel(GenParams gp, LoadPlan
     load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
 
     const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
-    const unsigned nb = (unsigned)(gp.batch_fast ? gp.Bp : gp.B);
-    const unsigned total = nb * gp.C * plane;
+    const unsigned total = (unsigned)gp.B * gp.C * plane;
     const float fL = (float)gp.L;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        // consecutive threads write consecutive words: pixels of one channel in general, images of one pixel in the
-        // batch-innermost image (whose images past the batch are written as zeros)
-        unsigned yx, c, b;
-        if (gp.batch_fast) { b = idx % nb; const unsigned r = idx / nb; yx = r % plane; c = r / plane; }
-        else { yx = idx % plane; const unsigned bc = idx / plane; c = bc % (unsigned)gp.C; b = bc / (unsigned)gp.C; }
+        const unsigned yx = idx % plane, bc = idx / plane;
+        const unsigned c = bc % (unsigned)gp.C, b = bc / (unsigned)gp.C;
         const int y = (int)(yx / (unsigned)gp.Wp), x = (int)(yx % (unsigned)gp.Wp);
         const int yi = y - gp.pad_h, xi = x - gp.pad_w;
         int V = 0;
-        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W && b < (unsigned)gp.B) {
+        if (yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W) {
             const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
             V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
         }
         const int cc = gp.mode == GEO_SC_MODE_YZ ? (int)c % gp.z : (int)c;
         const unsigned sidx = (unsigned)((cc * gp.Hp + y) * gp.Wp + x);
         const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
-        uint32_t *dst = as + (size_t)b * gp.img_stride + ((size_t)c * plane + yx) * gp.pix_stride;
+        uint32_t *dst = as + ((size_t)b * gp.P * gp.C + c) * plane + yx;
         for (int p = 0; p < gp.P; p++)
-            dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+            dst[(size_t)p * gp.C * plane] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+    }
+}
+
+// The same for a batch-innermost stream image ([pack][c][Hp][Wp][Bp]): a CTA turns tiles of 32 images x 32
+// elements of the padded image through shared memory, so that the activation reads run along an image row and the
+// stream-word stores along the batch -- both consecutive.  Images past the batch are written as zeros.
+__global__ void __launch_bounds__(256) act_streams_batch_kernel(GenParams gp, LoadPlan plan, const float *__restrict__ act,
+                                                                uint32_t *__restrict__ as) {
+    extern __shared__ uint32_t smem[];
+    uint32_t *s_pat = smem;
+    uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RWS);
+    __shared__ uint16_t s_level[32][33];
+    load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
+
+    const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
+    const unsigned E = (unsigned)gp.C * plane;   // elements of one padded image
+    const unsigned nbt = ((unsigned)gp.Bp + 31) / 32, net = (E + 31) / 32;
+    const unsigned tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const float fL = (float)gp.L;
+    for (unsigned tile = blockIdx.x; tile < nbt * net; tile += gridDim.x) {
+        const unsigned b0 = (tile % nbt) * 32, e0 = (tile / nbt) * 32;
+        {   // lanes along the elements: the level of element e0 + tx in images b0 + ty, + 8, ...
+            const unsigned e = e0 + tx, c = e / plane, yx = e % plane;
+            const int yi = (int)(yx / (unsigned)gp.Wp) - gp.pad_h, xi = (int)(yx % (unsigned)gp.Wp) - gp.pad_w;
+            const bool inside = e < E && yi >= 0 && yi < gp.H && xi >= 0 && xi < gp.W;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const unsigned b = b0 + ty + 8 * k;
+                int V = 0;
+                if (inside && b < (unsigned)gp.B) {
+                    const float a = act[(((size_t)b * gp.C + c) * gp.H + yi) * gp.W + xi] * fL;
+                    V = (int)ceilf(fminf(fmaxf(a, 0.0f), fL - 1.0f));
+                }
+                s_level[ty + 8 * k][tx] = (uint16_t)V;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; k++) {   // lanes along the batch: the stream words of element e0 + ty + 8k in image b0 + tx
+            const unsigned e = e0 + ty + 8 * k, b = b0 + tx;
+            if (e < E && b < (unsigned)gp.Bp) {
+                const int V = s_level[tx][ty + 8 * k];
+                const unsigned c = e / plane, yx = e % plane;
+                const unsigned sidx = gp.mode == GEO_SC_MODE_YZ ? (c % (unsigned)gp.z) * plane + yx : e;
+                const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
+                uint32_t *dst = as + (size_t)e * gp.pix_stride + b;
+                for (int p = 0; p < gp.P; p++)
+                    dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -491,7 +538,10 @@ int launch_act_streams(const Geometry &g, const float *act, uint32_t *astream, c
     const long long total = (long long)(g.batch_fast ? g.Bp : g.B) * g.C * g.Hp * g.Wp;
     if (g.generator == GEO_SC_GEN_ACC) act_streams_acc_kernel<false><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
     else if (g.generator == GEO_SC_GEN_RAND) act_streams_acc_kernel<true><<<grid_for(total), 256, 0, s>>>(gp, g.seed, act, astream);
-    else act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
+    else if (g.batch_fast) {
+        const long long tiles = (long long)((g.Bp + 31) / 32) * (((long long)g.C * g.Hp * g.Wp + 31) / 32);
+        act_streams_batch_kernel<<<grid_for(tiles * 256), 256, smem, s>>>(gp, plan, act, astream);
+    } else act_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, act, astream);
     GEO_CUDA_CHECK(cudaGetLastError());
     return GEO_SC_OK;
 }
