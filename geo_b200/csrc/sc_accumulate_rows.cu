@@ -62,6 +62,12 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
 // base + off computed as a multiply-add by a run-time one: the integer multiply-add issues on the FMA pipe, which
 // this kernel leaves idle, instead of the ALU pipe that the LOP3s saturate.
 __device__ __forceinline__ uint32_t add_on_fma_pipe(uint32_t off, uint32_t one, uint32_t base) {
@@ -71,23 +77,19 @@ __device__ __forceinline__ uint32_t add_on_fma_pipe(uint32_t off, uint32_t one, 
 }
 
 // One pattern's members: PAT bit j set = the weight of channel j is negative.  a_lo / a_hi: shared address of the
-// lane's two runs of four positions in plane 0, row 0; sw / so: the quad's stream-word and offset lists; members
-// [i0, i1) of the lists.  The stream words and the offset of member i + 1 are fetched while member i is computed,
-// so that the activation loads of a member never wait for its offset (slot i1 exists: the lists are padded).
+// lane's two runs of four positions in plane 0, row 0; sw / so: shared addresses of the quad's stream-word and
+// offset lists; members [i0, i1) of the lists.  Every load carries an explicit 32-bit shared address (the list walk
+// through generic pointers cost 6 % of the kernel on the second conv of the CNN); the loop is unrolled twice
+// (once: 12 % slower, four times: registers spill).
 template <int PAT>
 __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo, uint32_t a_hi,
-                                           const uint4 *__restrict__ sw, const uint32_t *__restrict__ so, int i0, int i1,
-                                           uint32_t one) {
-    if (i0 >= i1) return;
-    uint4 wn = sw[i0];
-    uint32_t on = so[i0];
+                                           uint32_t sw, uint32_t so, int i0, int i1, uint32_t one) {
 #pragma unroll 2
     for (int i = i0; i < i1; i++) {
-        const uint4 w = wn;
+        const uint4 w = lds128(sw + (uint32_t)i * 16);
+        const uint32_t on = lds32(so + (uint32_t)i * 4);
         const uint4 x = lds128(add_on_fma_pipe(on, one, a_lo));
         const uint4 y = lds128(add_on_fma_pipe(on, one, a_hi));
-        wn = sw[i + 1];
-        on = so[i + 1];
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -250,8 +252,8 @@ __global__ void __launch_bounds__(kRowsThreads, 1) accumulate_rows_kernel(RowsPa
             const uint32_t stage = smem_base + (uint32_t)(s & 1) * pr.stage_bytes;
             const uint32_t a_lo = stage + lane_off[0], a_hi = stage + lane_off[1];
             const unsigned char *stage_ptr = smem + (size_t)(s & 1) * pr.stage_bytes;
-            const uint4 *swl = (const uint4 *)(stage_ptr + sw_off) + ql * pr.SL;
-            const uint32_t *sol = (const uint32_t *)(stage_ptr + so_off) + ql * pr.SL;
+            const uint32_t swl = stage + (uint32_t)sw_off + (uint32_t)(ql * pr.SL) * 16;
+            const uint32_t sol = stage + (uint32_t)so_off + (uint32_t)(ql * pr.SL) * 4;
             const uint16_t *sbl = (const uint16_t *)(smem + (size_t)(s & 1) * pr.stage_bytes + sb_off) + ql * 24;
             // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
             const int mybeg = lane < 17 ? (int)sbl[lane] : 0;

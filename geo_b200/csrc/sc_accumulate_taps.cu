@@ -43,6 +43,11 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
 // base + off as a multiply-add by a run-time one: issues on the FMA pipe instead of the ALU pipe of the LOP3s
 __device__ __forceinline__ uint32_t add_on_fma_pipe(uint32_t off, uint32_t one, uint32_t base) {
     uint32_t r;
@@ -72,21 +77,19 @@ struct TapsParams {
     uint32_t one;
 };
 
+// One pattern's members: PAT bit j set = the weight of channel j is negative.  a_lo: shared address of the lane's
+// first run in row 0 of the stage's tile; sw / so: shared addresses of the quad's lists of stream words and of row
+// offsets; members [i0, i1).  All loads carry explicit 32-bit shared addresses: with generic pointers the list
+// walk cost 3 % of the kernel's time.
 template <int PAT>
-__device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo,
-                                           const uint4 *__restrict__ sw, const uint32_t *__restrict__ so, int i0, int i1,
-                                           uint32_t one) {
-    if (i0 >= i1) return;
-    uint4 wn = sw[i0];
-    uint32_t on = so[i0];
+__device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t a_lo, uint32_t sw,
+                                           uint32_t so, int i0, int i1, uint32_t one) {
 #pragma unroll 2
     for (int i = i0; i < i1; i++) {
-        const uint4 w = wn;
-        const uint32_t a = add_on_fma_pipe(on, one, a_lo);
+        const uint4 w = lds128(sw + (uint32_t)i * 16);
+        const uint32_t a = add_on_fma_pipe(lds32(so + (uint32_t)i * 4), one, a_lo);
         const uint4 x = lds128(a);
         const uint4 y = lds128(a + 512);   // the lane's second run: 32 runs of 16 bytes further on
-        wn = sw[i + 1];   // slot i1 exists: the lists are padded, and what follows them in the stage is readable
-        on = so[i + 1];
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -262,8 +265,8 @@ __global__ void __launch_bounds__(kTapsThreads, 1) accumulate_taps_kernel(TapsPa
             const uint32_t stage = smem_base + (uint32_t)(s & 1) * pr.stage_bytes;
             const uint32_t a_lo = stage + (uint32_t)(h * 64 + lane) * 16;
             const unsigned char *stage_ptr = smem + (size_t)(s & 1) * pr.stage_bytes;
-            const uint4 *swl = (const uint4 *)(stage_ptr + sw_off) + ql * pr.SL;
-            const uint32_t *sol = (const uint32_t *)(stage_ptr + so_off) + ql * pr.SL;
+            const uint32_t swl = stage + (uint32_t)sw_off + (uint32_t)(ql * pr.SL) * 16;
+            const uint32_t sol = stage + (uint32_t)so_off + (uint32_t)(ql * pr.SL) * 4;
             const uint16_t *sbl = (const uint16_t *)(stage_ptr + sb_off) + ql * 24;
             // lane b holds the first slot of pattern b; the loops get their bounds by shuffle
             const int mybeg = lane < 17 ? (int)sbl[lane] : 0;
