@@ -70,10 +70,6 @@ __device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c) {
     return r;
 }
 
-// One pattern's members: PAT bit j set = the weight of channel j is negative.  ra: shared address of the lane's
-// first run of four positions in row 0 of the stage's tile (the second run is 512 bytes on); wl / ol: the quad's
-// lists of stream words and of rows; members [i0, i1).  The entry of member i + 1 is fetched while member i is
-// computed (slot i1 exists: what follows a list in shared memory is readable, and its value is not used).
 // base + 4 * off as one wide multiply-add (FMA pipe) instead of a 64-bit add in two halves (ALU pipe)
 __device__ __forceinline__ const uint32_t *word_address(const uint32_t *base, int off, int four) {
     const uint32_t *r;
@@ -81,6 +77,10 @@ __device__ __forceinline__ const uint32_t *word_address(const uint32_t *base, in
     return r;
 }
 
+// One pattern's members: PAT bit j set = the weight of channel j is negative.  ra: shared address of the lane's
+// first run of four positions in row 0 of the stage's tile (the second run is 512 bytes on); wl / ol: the quad's
+// lists of stream words and of rows; members [i0, i1).  The entry of member i + 1 is fetched while member i is
+// computed (slot i1 exists: what follows a list in shared memory is readable, and its value is not used).
 template <int PAT>
 __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t ra, uint32_t wl,
                                            uint32_t ol, int i0, int i1, uint32_t row_bytes) {
