@@ -7,8 +7,8 @@
 // the positive or the negative accumulator of each channel; members whose four weights are all zero (the
 // padding of a group, zero weights) are dropped from the lists.  What differs is the scale: a stage is one chunk of
 // at most 16 members of one group, sorted on its own, so a pattern's loop runs once or twice and what counts is
-// that everything around it is cheap -- the pattern bounds of a chunk are 16 bytes read with one load, the
-// list entry of the next member is fetched while the current one is computed, and the branches are direct.
+// that everything around it is cheap -- the pattern bounds of a chunk are 16 bytes read with one load, every
+// load carries an explicit 32-bit shared address, and the branches are direct.
 //
 // A warp owns one quad and 256 positions (a lane: two runs of four), a CTA four quads; tiles are im2col tiles as in
 // the dense kernel: 256 positions x KC members per stage, gathered with 4-byte cp.async through the member offset
@@ -78,23 +78,17 @@ __device__ __forceinline__ const uint32_t *word_address(const uint32_t *base, in
 }
 
 // One pattern's members: PAT bit j set = the weight of channel j is negative.  ra: shared address of the lane's
-// first run of four positions in row 0 of the stage's tile (the second run is 512 bytes on); wl / ol: the quad's
-// lists of stream words and of rows; members [i0, i1).  The entry of member i + 1 is fetched while member i is
-// computed (slot i1 exists: what follows a list in shared memory is readable, and its value is not used).
+// first run of four positions in row 0 of the stage's tile (the second run is 512 bytes on); wl / ol: shared
+// addresses of the quad's lists of stream words and of rows; members [i0, i1).
 template <int PAT>
 __device__ __forceinline__ void run_bucket(uint32_t (&accp)[8][4], uint32_t (&accn)[8][4], uint32_t ra, uint32_t wl,
                                            uint32_t ol, int i0, int i1, uint32_t row_bytes) {
-    if (i0 >= i1) return;
-    uint4 wn = lds128(wl + i0 * 16);
-    uint32_t on = lds8(ol + i0);
 #pragma unroll 1
     for (int i = i0; i < i1; i++) {
-        const uint4 w = wn;
-        const uint32_t a = imad(on, row_bytes, ra);
+        const uint4 w = lds128(wl + i * 16);
+        const uint32_t a = imad(lds8(ol + i), row_bytes, ra);
         const uint4 x = lds128(a);
         const uint4 y = lds128(a + 512);
-        wn = lds128(wl + (i + 1) * 16);
-        on = lds8(ol + i + 1);
         const uint32_t av[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
