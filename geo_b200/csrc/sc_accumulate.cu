@@ -273,7 +273,9 @@ int launch_accumulate(const Geometry &g, const uint32_t *astream, const uint32_t
         }
     }
     switch (g.NT) {
-    case 16: return g.M <= 2048 ? launch_tile<16, 64>(g, pr, s) : launch_tile<16, 128>(g, pr, s);
+    case 16:   // small launches: one-warp and two-warp CTAs, so that a few hundred positions still spread over the SMs
+        if (g.M <= 512) return launch_tile<16, 32, 16, 4, 12>(g, pr, s);
+        return g.M <= 2048 ? launch_tile<16, 64>(g, pr, s) : launch_tile<16, 128>(g, pr, s);
     case 32: return long_groups ? launch_tile<32, 128, 32, 3>(g, pr, s) : launch_tile<32, 128>(g, pr, s);
     default: return long_groups ? launch_tile<64, 128, 32, 3>(g, pr, s) : launch_tile<64, 128>(g, pr, s);
     }
