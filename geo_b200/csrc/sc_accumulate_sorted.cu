@@ -39,15 +39,27 @@ struct SortedParams {
     int img_words, pack_words, aoff_mul, splits;
 };
 
-// One pattern's members: PAT bit j set = the weight of channel j is negative.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// One pattern's members: PAT bit j set = the weight of channel j is negative.  atile: shared address of the lane's
+// four positions in row 0 of the tile; sw / srow: shared addresses of the quad's lists of stream
+// words and of tile rows.  Explicit 32-bit shared addresses: generic pointers cost the sibling kernels 3-6 %.
 template <int PAT>
-__device__ __forceinline__ void run_bucket(uint32_t (&accp)[4][4], uint32_t (&accn)[4][4], const uint4 *__restrict__ atile,
-                                           const uint4 *__restrict__ sw, const uint16_t *__restrict__ srow, int i0,
-                                           int i1) {
+__device__ __forceinline__ void run_bucket(uint32_t (&accp)[4][4], uint32_t (&accn)[4][4], uint32_t atile, uint32_t sw,
+                                           uint32_t srow, int i0, int i1) {
 #pragma unroll 4
     for (int i = i0; i < i1; i++) {
-        const uint4 w = sw[i];
-        const uint4 a = atile[srow[i]];
+        const uint4 w = lds128(sw + (uint32_t)i * 16);
+        const uint4 a = lds128(atile + lds16(srow + (uint32_t)i * 2) * 16);   // list entries are in units of 16 bytes
         const uint32_t av[4] = {a.x, a.y, a.z, a.w};
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -73,9 +85,9 @@ __global__ void __launch_bounds__(NQ * 32, 2) accumulate_sorted_kernel(SortedPar
     const uint32_t sw_base = smem_base + (uint32_t)pr.KCH * 128 * 4;
     const uint32_t srow_base = sw_base + (uint32_t)NQ * pr.SL * 16;
     const uint32_t sbeg_base = srow_base + (uint32_t)NQ * pr.SL * 2;
-    const uint4 *atile = (const uint4 *)smem + lane;
-    const uint4 *swl = (const uint4 *)(smem + pr.KCH * 128) + warp * pr.SL;
-    const uint16_t *srl = (const uint16_t *)(smem + pr.KCH * 128 + NQ * pr.SL * 4) + warp * pr.SL;
+    const uint32_t atile = smem_base + (uint32_t)lane * 16;
+    const uint32_t swl = sw_base + (uint32_t)(warp * pr.SL) * 16;
+    const uint32_t srl = srow_base + (uint32_t)(warp * pr.SL) * 2;
     const uint16_t *sbl = (const uint16_t *)(smem + pr.KCH * 128 + NQ * pr.SL * 4 + NQ * pr.SL / 2) + warp * 18;
 
     // gather assignment: thread t copies position t % 128 of rows t / 128 + i * (NQ / 4)
