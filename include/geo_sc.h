@@ -175,12 +175,13 @@ int geo_sc_accumulate_kernel(const geo_sc_conv_desc *desc, int *kernel);
  * 1 = negative, base 37), followed by an int32 table [group][member_padded] of activation
  * offsets; members are padded (see geo_sc_group_geometry) with zero streams, c_out_padded = c_out
  * rounded up to the kernel's c_out tile
- * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.  For descriptors with long
- * groups (64 or more padded members, c_out padded to a multiple of 32) a third section follows for the
- * sign-sorted accumulate kernel:
- * per (group, chunk of <= 160 members, quad of four output channels) the members sorted by which of the
- * four weights are negative -- one uint4 with the four non-zero stream words per member and pack, one
- * uint16 tile offset per member and 17 pattern boundaries; geo_sc_weight_prep_bytes covers all three.
+ * (see geo_sc_group_geometry).  Bits are MSB-first inside a word, 32 per pack.  A third section follows for
+ * the sign-sorted accumulate kernel that the layer's geometry selects (geo_sc_accumulate_kernel): per
+ * (group, chunk of members, quad of four output channels) the members sorted by which of the four
+ * weights are negative -- one uint4 with the four non-zero stream words per member and pack, the member's
+ * offset in the kernel's tile and the boundaries of the 16 patterns; the chunking (whole groups of planes,
+ * filter taps x channels, or 16 members) and the widths of the offsets differ per kernel and are
+ * private to the library; geo_sc_weight_prep_bytes covers all three sections.
  * For GEO_SC_MODE_FULL_BIN the third section holds the weight words once more, in the order the binary
  * tensor-core GEMM of that mode reads them (tiles of 32 output channels x 2 polarities x 32 words).
  * Neither the size nor the contents of the prepared buffer depend on `batch`: a buffer prepared once
