@@ -380,6 +380,26 @@ def test_accurate_generator_streams_hold_exactly_their_level(cuda_device, L):
         assert torch.equal(y1, y2) and not torch.equal(y1, y3)
 
 
+@pytest.mark.parametrize("generator", ["acc", "rand"])
+def test_counter_based_generators_do_not_depend_on_the_stream_image_layout(cuda_device, generator):
+    """The streams of the counter-based generators are a function of (seed, element, bit): the batch-innermost
+    image of a 64-channel layer holds the same words as the batch-major image that another mode gets for the
+    same activations."""
+    from geo_b200 import _lib, ops
+
+    a, w = _rand((7, 64, 5, 4), (32, 64, 3, 3), 4242)
+    kw = dict(generator=generator, seed=5)
+    d_batch = ops.desc_for(a, w, 128, "1d_bin", (1, 1), **kw)
+    d_major = ops.desc_for(a, w, 128, "z_bin", (1, 1), **kw)
+    assert _lib.act_stream_layout(d_batch)[0] and not _lib.act_stream_layout(d_major)[0]
+    s1 = ops.act_streams_canonical(ops.generate_act_streams(a.to(cuda_device), d_batch), d_batch)
+    s2 = ops.act_streams_canonical(ops.generate_act_streams(a.to(cuda_device), d_major), d_major)
+    assert torch.equal(s1, s2)
+    if generator == "acc":
+        ap = np.pad(a.numpy(), ((0, 0), (0, 0), (1, 1), (1, 1)))
+        assert np.array_equal(_popcount(s1.cpu().numpy()).sum(-1), np.ceil(np.clip(ap * 128, 0, 127)).astype(np.int64))
+
+
 def test_random_generator_bits_are_independent_draws_against_shared_thresholds(cuda_device):
     """GEO_SC_GEN_RAND (utils_functional.py:92-102): a bit is one when the level exceeds a uniform integer below
     L, so the ones of a stream average level (not exactly, unlike 'acc'); the integers are shared like the
