@@ -201,6 +201,58 @@ def test_dense_kernel_on_the_batch_innermost_image(cuda_device, oracle_lib):
         assert np.array_equal(y, oracle_lib.conv2d(a, w, 128, mode, pad_h=pad[0], pad_w=pad[1], **kw))
 
 
+def test_random_configurations_over_every_kernel_family(cuda_device, oracle_lib):
+    """150 seeded random configurations drawn per kernel family (wide layers -> tap tiles, narrow long-group layers
+    -> row / im2col tiles, short groups, linear layers, anything) with odd batches, ragged c_out, paddings from
+    none to wider than the filter needs and zeroed weights, each against the oracle."""
+    import random
+
+    from geo_b200 import _lib, ops
+
+    rng = random.Random(20240)
+    seen = {}
+    done = 0
+    while done < 150:
+        fam = rng.choice(["taps", "taps", "short", "linear", "rows", "any"])
+        if fam == "linear":
+            mode = rng.choice(["yz_bin", "1d_bin", "full_or"])
+            C, O = rng.choice([16, 48, 64, 100, 256]), rng.choice([10, 16, 40, 64])
+            K2 = K3 = H = W = 1
+            ph = pw = 0
+            B = rng.choice([1, 3, 64, 130, 203, 256, 300])
+        else:
+            mode = rng.choice({"taps": ["1d_bin", "full_or", "2d_bin"], "rows": ["1d_bin", "full_or", "2d_bin"],
+                               "short": ["1d_bin", "z_bin", "yz_bin", "2d_bin"],
+                               "any": ["1d_bin", "full_or", "2d_bin", "yz_bin", "z_bin", "full_bin"]}[fam])
+            C = rng.choice({"taps": [64, 65, 72, 96, 100, 128, 200], "rows": [16, 24, 32, 40], "short": [1, 2, 3, 4, 6, 8],
+                            "any": [3, 8, 20, 64]}[fam])
+            O = rng.choice({"taps": [32, 33, 40, 64, 70, 96, 128], "rows": [32, 64, 96], "short": [3, 16, 17, 32, 40, 64],
+                            "any": [5, 16, 33, 64]}[fam])
+            K2, K3 = rng.choice([(3, 3), (5, 5), (1, 1), (2, 4), (3, 1), (1, 3)])
+            H, W = rng.choice([1, 2, 3, 4, 6, 8, 9, 12, 16]), rng.choice([1, 2, 4, 5, 8, 10, 12, 16])
+            ph, pw = rng.choice([(0, 0), (1, 1), (2, 2), (2, 1), (0, 1), (3, 0)])
+            B = rng.choice([1, 2, 3, 5, 8, 16, 17, 33, 64, 70])
+        if H + 2 * ph < K2 or W + 2 * pw < K3:
+            continue
+        if B * (H + 2 * ph - K2 + 1) * (W + 2 * pw - K3 + 1) * O * C * K2 * K3 > 1.5e8:
+            continue
+        L, z = rng.choice([8, 32, 64, 128, 256]), rng.choice([1, 2, 4, 8, 16])
+        lu, lw = rng.choice([(8, 1), (2, 2), (1, 3)])
+        g = torch.Generator().manual_seed(done)
+        a = q7(torch.rand(B, C, H, W, generator=g))
+        w = q7(torch.rand(O, C, K2, K3, generator=g) * 2 - 1)
+        if rng.random() < 0.5:
+            w.view(-1)[::rng.choice([2, 3, 5])] = 0
+        kw = dict(z_unit=z, total_width=7, load_width=lu, load_wait_w=lw, load_wait_a=lw)
+        k = _lib.accumulate_kernel(ops.desc_for(a, w, L, mode, (ph, pw), **kw))
+        seen[k] = seen.get(k, 0) + 1
+        y = ops.sc_conv2d(a.to(cuda_device), w.to(cuda_device), L, mode, (ph, pw), **kw).cpu().numpy()
+        assert np.array_equal(y, oracle_lib.conv2d(a, w, L, mode, pad_h=ph, pad_w=pw, **kw)), (done, fam, mode, k, a.shape, w.shape)
+        done += 1
+    assert {"dense", "sorted_short", "sorted_taps", "sorted_im2col"} <= set(seen), seen
+    assert _lib.device_error_count() == 0
+
+
 def test_small_stream_lengths(cuda_device, oracle_lib):
     from geo_b200 import ops
 
