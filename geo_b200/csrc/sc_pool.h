@@ -24,6 +24,15 @@ __device__ __forceinline__ float4 load_x4(const XSource &xs, size_t i) {
     return __ldg((const float4 *)xs.p + i);
 }
 
+// Two consecutive values starting at element 2 * i.
+__device__ __forceinline__ float2 load_x2(const XSource &xs, size_t i) {
+    if (xs.counts) {
+        const int2 v = __ldg((const int2 *)xs.p + i);
+        return make_float2((float)v.x * xs.scale, (float)v.y * xs.scale);
+    }
+    return __ldg((const float2 *)xs.p + i);
+}
+
 // Mean over a 2x2 window of (x * w + b): sum the window, then divide by its size (the association of avg_pool2d).
 __device__ __forceinline__ float pooled_value(float x00, float x01, float x10, float x11, float w, float b) {
     return ((x00 * w + b) + (x01 * w + b) + (x10 * w + b) + (x11 * w + b)) / 4.0f;

@@ -343,10 +343,12 @@ __global__ void __launch_bounds__(256) epilogue_streams_kernel(GenParams gp, Loa
     }
 }
 
-// The same pass for a batch-innermost stream image ([pack][c][Hp][Wp][Bp]): a thread owns two adjacent pooled
-// values of FOUR consecutive images, so that the stream words of a (pixel, pack) are one 16-byte store, and
-// consecutive threads own consecutive image quads, so that those stores are consecutive too.  (With one image per
-// thread every stream word was a 4-byte store into a sector of its own: 5 % of the VGG-11-style step at 2048 images.)
+// The same pass for a batch-innermost stream image ([pack][c][Hp][Wp][Bp]).  A CTA turns tiles of 32 images x 32
+// pooled elements through shared memory: with the lanes along the elements it reads the counts (8 bytes per lane
+// and input row, consecutive), evaluates batch norm, pool, hardtanh and rounding and writes the fp32 activation
+// (consecutive); with the lanes along the batch it writes the stream words (consecutive).  (With one image per thread
+// and no turn every stream word was a 4-byte store into a sector of its own: 5 % of the VGG-11-style step at 2048
+// images.)
 __global__ void __launch_bounds__(256) epilogue_streams_batch_kernel(GenParams gp, LoadPlan plan, XSource xs,
                                                                      const float *__restrict__ wq, const float *__restrict__ bq,
                                                                      float qlevels, float qinv, float *__restrict__ act_out,
@@ -354,61 +356,51 @@ __global__ void __launch_bounds__(256) epilogue_streams_batch_kernel(GenParams g
     extern __shared__ uint32_t smem[];
     uint32_t *s_pat = smem;
     uint16_t *s_q0 = (uint16_t *)(smem + gp.L * gp.RWS);
+    __shared__ uint16_t s_level[32][33];
     load_tables(s_pat, s_q0, gp.L, gp.RW, gp.RWS);
 
-    const unsigned Wx = 2u * (unsigned)gp.W;                 // width of the counts
-    const unsigned q = Wx >> 2, nbq = (unsigned)gp.Bp / 4;
-    const unsigned total = nbq * q * (unsigned)gp.H * (unsigned)gp.C;
+    const unsigned HW = (unsigned)(gp.H * gp.W), E = (unsigned)gp.C * HW;   // pooled elements of one image
     const unsigned plane = (unsigned)(gp.Hp * gp.Wp);
+    const unsigned nbt = ((unsigned)gp.Bp + 31) / 32, net = (E + 31) / 32;
+    const unsigned tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const float fL = (float)gp.L;
-    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const unsigned bqd = i % nbq;
-        unsigned rest = i / nbq;
-        const unsigned j = rest % q;
-        rest /= q;
-        const unsigned oy = rest % (unsigned)gp.H, c = rest / (unsigned)gp.H;
-        const float w = wq[c], sh = bq[c];
-        const int cc = gp.mode == GEO_SC_MODE_YZ ? (int)c % gp.z : (int)c;
-        const unsigned y = oy + (unsigned)gp.pad_h;
-        int q0[2];
+    for (unsigned tile = blockIdx.x; tile < nbt * net; tile += gridDim.x) {
+        const unsigned b0 = (tile % nbt) * 32, e0 = (tile / nbt) * 32;
+        {   // lanes along the pooled elements
+            const unsigned e = e0 + tx, c = e / HW, rem = e % HW, oy = rem / (unsigned)gp.W, ox = rem % (unsigned)gp.W;
+            const float w = e < E ? wq[c] : 0.0f, sh = e < E ? bq[c] : 0.0f;
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            const unsigned x = 2 * j + e + (unsigned)gp.pad_w;
-            q0[e] = s_q0[(unsigned)((cc * gp.Hp + (int)y) * gp.Wp + (int)x) % (unsigned)(gp.L - 1) + 1];
-        }
-        uint32_t words[2][kMaxPacks][4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const unsigned b = bqd * 4 + k;
-            int V[2] = {0, 0};
-            if (b < (unsigned)gp.B) {
-                const unsigned r = (b * (unsigned)gp.C + c) * (unsigned)gp.H + oy;
-                const float4 t = load_x4(xs, ((size_t)(2 * r) * Wx >> 2) + j);
-                const float4 u = load_x4(xs, ((size_t)(2 * r + 1) * Wx >> 2) + j);
-                float v[2] = {pooled_value(t.x, t.y, u.x, u.y, w, sh), pooled_value(t.z, t.w, u.z, u.w, w, sh)};
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    v[e] = quantize_value(fminf(fmaxf(v[e], 0.0f), 1.0f), qlevels, qinv);
-                    V[e] = (int)ceilf(fminf(fmaxf(v[e] * fL, 0.0f), fL - 1.0f));
+            for (int k = 0; k < 4; k++) {
+                const unsigned b = b0 + ty + 8 * k;
+                int V = 0;
+                if (e < E && b < (unsigned)gp.B) {
+                    const size_t r = ((size_t)b * gp.C + c) * gp.H + oy;             // pooled row; counts rows 2r, 2r + 1
+                    const float2 t = load_x2(xs, (size_t)(2 * r) * gp.W + ox);       // counts are 2 W wide: W pairs per row
+                    const float2 u = load_x2(xs, (size_t)(2 * r + 1) * gp.W + ox);
+                    float v = pooled_value(t.x, t.y, u.x, u.y, w, sh);
+                    v = quantize_value(fminf(fmaxf(v, 0.0f), 1.0f), qlevels, qinv);
+                    act_out[(size_t)b * E + e] = v;
+                    V = (int)ceilf(fminf(fmaxf(v * fL, 0.0f), fL - 1.0f));
                 }
-                ((float2 *)(act_out + (size_t)r * gp.W))[j] = make_float2(v[0], v[1]);
+                s_level[ty + 8 * k][tx] = (uint16_t)V;
             }
-#pragma unroll
-            for (int e = 0; e < 2; e++)
-#pragma unroll
-                for (int p = 0; p < kMaxPacks; p++)
-                    if (p < gp.P) words[e][p][k] = V[e] ? stream_word(s_pat, gp.RWS, gp.L, V[e], q0[e], p, plan) : 0u;
         }
+        __syncthreads();
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            const unsigned x = 2 * j + e + (unsigned)gp.pad_w;
-            uint32_t *dst = as + ((size_t)c * plane + y * (unsigned)gp.Wp + x) * gp.pix_stride + bqd * 4;
-#pragma unroll
-            for (int p = 0; p < kMaxPacks; p++)
-                if (p < gp.P)
-                    *(uint4 *)(dst + (size_t)p * gp.pack_stride) =
-                        make_uint4(words[e][p][0], words[e][p][1], words[e][p][2], words[e][p][3]);
+        for (int k = 0; k < 4; k++) {   // lanes along the batch
+            const unsigned e = e0 + ty + 8 * k, b = b0 + tx;
+            if (e < E && b < (unsigned)gp.Bp) {
+                const int V = s_level[tx][ty + 8 * k];
+                const unsigned c = e / HW, rem = e % HW, oy = rem / (unsigned)gp.W, ox = rem % (unsigned)gp.W;
+                const unsigned yx = (oy + (unsigned)gp.pad_h) * (unsigned)gp.Wp + ox + (unsigned)gp.pad_w;
+                const unsigned sidx = (gp.mode == GEO_SC_MODE_YZ ? c % (unsigned)gp.z : c) * plane + yx;
+                const int q0 = s_q0[sidx % (unsigned)(gp.L - 1) + 1];
+                uint32_t *dst = as + ((size_t)c * plane + yx) * gp.pix_stride + b;
+                for (int p = 0; p < gp.P; p++)
+                    dst[(size_t)p * gp.pack_stride] = V ? stream_word(s_pat, gp.RWS, gp.L, V, q0, p, plan) : 0u;
+            }
         }
+        __syncthreads();
     }
 }
 
@@ -558,9 +550,9 @@ int launch_epilogue_streams(const Geometry &g, const XSource &xs, const float *w
     if (g.pad_h || g.pad_w || (g.batch_fast && g.Bp != g.B)) GEO_CUDA_CHECK(cudaMemsetAsync(astream, 0, g.act_stream_words * 4, s));
     const float levels = (float)(1 << prec);
     if (g.batch_fast) {
-        const long long total = (long long)(g.Bp / 4) * g.C * g.H * (g.W / 2);
-        epilogue_streams_batch_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, xs, wq, bq, levels, 1.0f / levels, act_out,
-                                                                         astream);
+        const long long tiles = (long long)((g.Bp + 31) / 32) * (((long long)g.C * g.H * g.W + 31) / 32);
+        epilogue_streams_batch_kernel<<<grid_for(tiles * 256), 256, smem, s>>>(gp, plan, xs, wq, bq, levels, 1.0f / levels, act_out,
+                                                                               astream);
     } else {
         const long long total = (long long)g.B * g.C * g.H * (g.W / 2);
         epilogue_streams_kernel<<<grid_for(total), 256, smem, s>>>(gp, plan, xs, wq, bq, levels, 1.0f / levels, act_out, astream);
